@@ -1,0 +1,547 @@
+// conv2d (groups = 1) and dense as an implicit GEMM on the sm_100a tensor cores.
+//
+//   D[pixel, oc] = sum_{kh,kw,c} X[n, oh*s-p+kh*d, ow*s-p+kw*d, c] * Wt[oc, kh, kw, c]
+//
+// One CTA owns a 128-pixel x BLOCK_N-channel tile of the output and walks K = KH*KW*C in slabs of
+// BLOCK_K bytes.  TMA brings each slab of activations (im2col-mode tensor map: 128 consecutive
+// output pixels of one filter tap, zero-filled outside the image; a plain 2-D map when the conv
+// is a 1x1 / dense) and of weights into a swizzled shared-memory ring; one thread issues
+// tcgen05.mma kind::i8 (int8 x int8 -> int32) into a TMEM accumulator; four warps drain the
+// accumulator with tcgen05.ld, run the fused element chain (bias, relu, round-shift, clip,
+// residual add ...) and store int8 / int32 NHWC.  Two accumulators alternate so the drain of tile
+// i overlaps the MMAs of tile i+1.  The int32 sum never reaches HBM.
+//
+// Reproduces src/runtime/cpu/ops/ops.cc:368-456 (conv2d: im2col_cpu :204-246, matrix_mul
+// :148-200) and :34-75 (dense): int32 accumulation of int8 products is exact, so the order of
+// summation cannot change a bit.
+//
+// Every wait in the kernel is bounded: when one runs out the CTA raises a flag, every role leaves
+// its loop, TMEM is released and the kernel returns with a non-zero word in *status.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+#include "common.cuh"
+
+namespace cvmk {
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int MAX_STAGES = 8;
+constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+struct ConvParams {
+  void* y;
+  int y_dtype;
+  int m_total;
+  int oc;
+  int oh, ow;
+  int c, kh, kw;
+  int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int block_k, block_n, stages, a_im2col;
+  int num_m_tiles, num_n_tiles;
+  int tmem_cols;
+  int* status;
+  DevChain chain;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up (or another role already did).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) {
+      if (*abort_flag) return false;
+      __nanosleep(i > 4096 ? 256 : 32);
+    }
+  }
+  *abort_flag = code;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                                   int c, int w, int h, int n, uint16_t off_w,
+                                                   uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
+      "h"(off_w), "h"(off_h)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(slot)),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on `bar` once every tcgen05.mma issued so far by this thread has finished.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are `row_bytes` long
+// (32, 64 or 128) and stored with the matching TMA swizzle: 8-row groups are 8 * row_bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, int row_bytes) {
+  const uint64_t layout = row_bytes == 128 ? 2 : (row_bytes == 64 ? 4 : 6);
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;                                  // leading byte offset (unused) = 16 B
+  d |= (uint64_t)((8u * (uint32_t)row_bytes) >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;                                  // descriptor version (sm_100)
+  d |= layout << 61;
+  return d;
+}
+// Instruction descriptor: s8 x s8 -> s32, both operands K-major, M = 128, N = block_n.
+__device__ __forceinline__ uint32_t umma_idesc_i8(int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(BLOCK_M >> 4) << 24);
+}
+
+template <int V>
+__device__ __forceinline__ void store_vals(const ConvParams& p, size_t lin, const int32_t* v) {
+  if (p.y_dtype == CVMK_I8) {
+    int8_t* dst = reinterpret_cast<int8_t*>(p.y) + lin;
+    if (V == 32) {
+      uint4 a, b;
+      a.x = pack4(v[0], v[1], v[2], v[3]);     a.y = pack4(v[4], v[5], v[6], v[7]);
+      a.z = pack4(v[8], v[9], v[10], v[11]);   a.w = pack4(v[12], v[13], v[14], v[15]);
+      b.x = pack4(v[16], v[17], v[18], v[19]); b.y = pack4(v[20], v[21], v[22], v[23]);
+      b.z = pack4(v[24], v[25], v[26], v[27]); b.w = pack4(v[28], v[29], v[30], v[31]);
+      reinterpret_cast<uint4*>(dst)[0] = a;
+      reinterpret_cast<uint4*>(dst)[1] = b;
+    } else {  // V == 8
+      uint2 a;
+      a.x = pack4(v[0], v[1], v[2], v[3]);
+      a.y = pack4(v[4], v[5], v[6], v[7]);
+      *reinterpret_cast<uint2*>(dst) = a;
+    }
+  } else {
+    int32_t* dst = reinterpret_cast<int32_t*>(p.y) + lin;
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q)
+      reinterpret_cast<int4*>(dst)[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[MAX_STAGES];
+  __shared__ uint64_t bar_empty[MAX_STAGES];
+  __shared__ uint64_t bar_acc_full[2];
+  __shared__ uint64_t bar_acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_flag;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int a_bytes = BLOCK_M * p.block_k;
+  const int b_bytes = p.block_n * p.block_k;
+  const int stage_bytes = a_bytes + b_bytes;
+  const int k_per_tap = p.c / p.block_k;
+  const int num_kb = p.kh * p.kw * k_per_tap;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bar_acc_full[a], 1);
+      mbar_init(&bar_acc_empty[a], 4);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool live = true;
+      for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+        const int n_tile = tile % p.num_n_tiles;
+        const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
+        const int img = m0 / (p.oh * p.ow);
+        const int rem = m0 - img * (p.oh * p.ow);
+        const int oy = rem / p.ow;
+        const int ox = rem - oy * p.ow;
+        const int base_w = ox * p.stride_w - p.pad_w;
+        const int base_h = oy * p.stride_h - p.pad_h;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const int tap = kb / k_per_tap;
+          const int cb = kb - tap * k_per_tap;
+          const int fy = tap / p.kw;
+          const int fx = tap - fy * p.kw;
+          if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
+          uint8_t* sa = smem + (size_t)stage * stage_bytes;
+          uint8_t* sb = sa + a_bytes;
+          mbar_expect_tx(&bar_full[stage], (uint32_t)stage_bytes);
+          if (p.a_im2col)
+            tma_load_im2col_4d(sa, &tmap_a, &bar_full[stage], cb * p.block_k, base_w, base_h, img,
+                               (uint16_t)(fx * p.dil_w), (uint16_t)(fy * p.dil_h));
+          else
+            tma_load_2d(sa, &tmap_a, &bar_full[stage], cb * p.block_k, m0);
+          tma_load_2d(sb, &tmap_b, &bar_full[stage], tap * p.c + cb * p.block_k,
+                      n_tile * p.block_n);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_i8(p.block_n);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool live = true;
+      for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1, &abort_flag, 2)) { live = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.block_n);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bar_full[stage], phase, &abort_flag, 3)) { live = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
+          const uint32_t sb = sa + a_bytes;
+          const uint64_t da = umma_desc(sa, p.block_k);
+          const uint64_t db = umma_desc(sb, p.block_k);
+          const int nk = p.block_k / 32;
+          for (int j = 0; j < nk; ++j)
+            mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc,
+                   (kb > 0 || j > 0) ? 1u : 0u);
+          mma_commit(&bar_empty[stage]);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!live) break;
+        mma_commit(&bar_acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. 32*quarter+31 belong to this warp
+    const int row_in_tile = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool live = true;
+    const bool vec_ok = (p.y_dtype == CVMK_I8) ? (p.oc % 16 == 0) : (p.oc % 4 == 0);
+    for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+      const int n0 = (tile % p.num_n_tiles) * p.block_n;
+      const int row = (tile / p.num_n_tiles) * BLOCK_M + row_in_tile;
+      if (!mbar_wait(&bar_acc_full[acc], acc_phase, &abort_flag, 4)) { live = false; break; }
+      tc_fence_after();
+      for (int c0 = 0; c0 < p.block_n; c0 += 32) {
+        const int col0 = n0 + c0;
+        if (col0 >= p.oc) break;  // uniform across the warp
+        int32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n + c0), v);
+        if (row < p.m_total) {
+          const size_t lin = (size_t)row * p.oc + col0;
+          if (col0 + 32 <= p.oc && vec_ok) {
+            apply_chain<32>(p.chain, v, lin, col0);
+            store_vals<32>(p, lin, v);
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 < p.oc) {
+                int32_t t[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t[j] = v[g * 8 + j];
+                apply_chain<8>(p.chain, t, lin + g * 8, col0 + g * 8);
+                store_vals<8>(p, lin + g * 8, t);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    // Give copies that may still be in flight time to land before shared memory is released.
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, 0x100 | abort_flag);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+void* driver_entry(const char* name) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+    set_error("cudaGetDriverEntryPoint(%s) failed: %s", name, cudaGetErrorString(e));
+    return nullptr;
+  }
+  return fn;
+}
+
+CUtensorMapSwizzle swizzle_for(int row_bytes) {
+  return row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+int pick_block_k(int c) { return c % 128 == 0 ? 128 : (c % 64 == 0 ? 64 : 32); }
+
+int pick_block_n(int oc) {
+  if (oc >= 256 && oc % 256 == 0) return 256;
+  if (oc > 128) return (oc % 128 == 0 || oc > 256) ? 128 : 256;
+  int n = 32;
+  while (n < oc) n *= 2;  // 32, 64, 128
+  return n;
+}
+
+bool is_pointwise(const cvmk_conv_desc& d) {
+  return d.KH == 1 && d.KW == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_h == 0 &&
+         d.pad_w == 0;
+}
+
+}  // namespace
+}  // namespace cvmk
+
+using namespace cvmk;
+
+extern "C" int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d) {
+  if (!d) return 0;
+  if (d->C % 32 != 0 || d->OC % 8 != 0) return 0;
+  if (d->pad_h > 127 || d->pad_w > 127) return 0;
+  if ((d->KH - 1) * d->dil_h > 255 || (d->KW - 1) * d->dil_w > 255) return 0;
+  if ((d->KH - 1) * d->dil_h - d->pad_h > 128 || (d->KW - 1) * d->dil_w - d->pad_w > 128) return 0;
+  if (d->stride_h > 8 || d->stride_w > 8) return 0;
+  if ((int64_t)d->N * d->OH * d->OW > (int64_t)INT32_MAX - 256) return 0;
+  return 1;
+}
+
+extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* plan) {
+  if (!d || !plan) { set_error("conv2d_tc_prepare: null argument"); return CVMK_ERR_ARG; }
+  if (!cvmk_conv2d_tc_supported(d)) {
+    set_error("conv2d_tc_prepare: shape not supported by the tensor-core path");
+    return CVMK_ERR_UNSUPPORTED;
+  }
+  if (((uintptr_t)d->x & 15) || ((uintptr_t)d->w & 15) || ((uintptr_t)d->y & 15)) {
+    set_error("conv2d_tc_prepare: operands must be 16-byte aligned");
+    return CVMK_ERR_ARG;
+  }
+  static EncodeTiledFn enc_tiled = (EncodeTiledFn)driver_entry("cuTensorMapEncodeTiled");
+  static EncodeIm2colFn enc_im2col = (EncodeIm2colFn)driver_entry("cuTensorMapEncodeIm2col");
+  if (!enc_tiled || !enc_im2col) return CVMK_ERR_CUDA;
+
+  memset(plan, 0, sizeof(*plan));
+  plan->d = *d;
+  const int bk = pick_block_k(d->C);
+  const int bn = pick_block_n(d->OC);
+  plan->block_k = bk;
+  plan->block_n = bn;
+  plan->a_im2col = is_pointwise(*d) ? 0 : 1;
+  const int stage_bytes = (BLOCK_M + bn) * bk;
+  int stages = SMEM_BUDGET / stage_bytes;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages < 2) { set_error("conv2d_tc_prepare: tile does not fit shared memory"); return CVMK_ERR_UNSUPPORTED; }
+  plan->stages = stages;
+  plan->smem_bytes = stages * stage_bytes + 1024;
+
+  const int64_t m_total = (int64_t)d->N * d->OH * d->OW;
+  const int64_t k_total = (int64_t)d->KH * d->KW * d->C;
+  CUtensorMap* ta = reinterpret_cast<CUtensorMap*>(plan->tmap_a);
+  CUtensorMap* tb = reinterpret_cast<CUtensorMap*>(plan->tmap_b);
+  const CUtensorMapSwizzle sw = swizzle_for(bk);
+  CUresult r;
+  if (plan->a_im2col) {
+    cuuint64_t dims[4] = {(cuuint64_t)d->C, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
+    cuuint64_t strides[3] = {(cuuint64_t)d->C, (cuuint64_t)d->W * d->C,
+                             (cuuint64_t)d->H * d->W * d->C};
+    int lower[2] = {-d->pad_w, -d->pad_h};
+    int upper[2] = {d->pad_w - (d->KW - 1) * d->dil_w, d->pad_h - (d->KH - 1) * d->dil_h};
+    cuuint32_t estr[4] = {1, (cuuint32_t)d->stride_w, (cuuint32_t)d->stride_h, 1};
+    r = enc_im2col(ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d->x, dims, strides, lower, upper,
+                   (cuuint32_t)bk, (cuuint32_t)BLOCK_M, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[2] = {(cuuint64_t)d->C, (cuuint64_t)m_total};
+    cuuint64_t strides[1] = {(cuuint64_t)d->C};
+    cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)BLOCK_M};
+    cuuint32_t estr[2] = {1, 1};
+    r = enc_tiled(ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)d->x, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: activation tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)k_total, (cuuint64_t)d->OC};
+    cuuint64_t strides[1] = {(cuuint64_t)k_total};
+    cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)bn};
+    cuuint32_t estr[2] = {1, 1};
+    r = enc_tiled(tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)d->w, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: weight tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
+  }
+  const int64_t num_m_tiles = (m_total + BLOCK_M - 1) / BLOCK_M;
+  const int64_t num_n_tiles = (d->OC + bn - 1) / bn;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int64_t tiles = num_m_tiles * num_n_tiles;
+  plan->grid = (int)(tiles < sms ? tiles : sms);
+  return CVMK_OK;
+}
+
+extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t stream) {
+  if (!plan) { set_error("conv2d_tc_launch: null plan"); return CVMK_ERR_ARG; }
+  const cvmk_conv_desc& d = plan->d;
+  ConvParams p;
+  memset(&p, 0, sizeof(p));
+  p.y = d.y;
+  p.y_dtype = d.y_dtype;
+  p.m_total = d.N * d.OH * d.OW;
+  p.oc = d.OC;
+  p.oh = d.OH; p.ow = d.OW;
+  p.c = d.C; p.kh = d.KH; p.kw = d.KW;
+  p.stride_h = d.stride_h; p.stride_w = d.stride_w;
+  p.pad_h = d.pad_h; p.pad_w = d.pad_w;
+  p.dil_h = d.dil_h; p.dil_w = d.dil_w;
+  p.block_k = plan->block_k; p.block_n = plan->block_n;
+  p.stages = plan->stages; p.a_im2col = plan->a_im2col;
+  p.num_m_tiles = (p.m_total + BLOCK_M - 1) / BLOCK_M;
+  p.num_n_tiles = (d.OC + plan->block_n - 1) / plan->block_n;
+  int cols = 2 * plan->block_n;
+  int pow2 = 32;
+  while (pow2 < cols) pow2 *= 2;
+  p.tmem_cols = pow2;
+  p.status = d.status;
+  int rc = lower_chain(d.ep, &p.chain);
+  if (rc != CVMK_OK) return rc;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BUDGET + 2048);
+    if (check_cuda(e, "cudaFuncSetAttribute(conv_tc_kernel)")) return CVMK_ERR_CUDA;
+    attr_set = true;
+  }
+  CUtensorMap ta, tb;
+  memcpy(&ta, plan->tmap_a, sizeof(ta));
+  memcpy(&tb, plan->tmap_b, sizeof(tb));
+  conv_tc_kernel<<<plan->grid, NUM_THREADS, plan->smem_bytes, (cudaStream_t)stream>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "conv_tc_kernel launch");
+}
