@@ -1,0 +1,840 @@
+// Lowering of a Graph into kernel launches, and the per-inference replay.
+#include "executor.h"
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+
+namespace cvm {
+
+#define CUDA_OK(expr)                                                                      \
+  do {                                                                                     \
+    cudaError_t e__ = (expr);                                                              \
+    CHECK(e__ == cudaSuccess) << "CUDA: " << #expr << ": " << cudaGetErrorString(e__);     \
+  } while (0)
+
+#define KERNEL_OK(expr)                                                                    \
+  do {                                                                                     \
+    int rc__ = (expr);                                                                     \
+    CHECK(rc__ == CVMK_OK) << "kernel launcher failed (" << rc__ << "): " << cvmk_last_error(); \
+  } while (0)
+
+namespace {
+
+bool nhwc_equiv(const Shape& s) {  // NCHW and NHWC orders coincide
+  return s.size() == 4 && ((s[2] == 1 && s[3] == 1) || s[1] == 1);
+}
+bool wants_nhwc(const Shape& s) { return s.size() == 4 && !nhwc_equiv(s); }
+
+// Element stride of every logical dimension in the buffer's physical layout.
+std::vector<int64_t> phys_strides(const Shape& s, bool nhwc) {
+  std::vector<int64_t> st(s.size(), 1);
+  if (nhwc) {
+    st[1] = 1;
+    st[3] = s[1];
+    st[2] = s[3] * s[1];
+    st[0] = s[2] * s[3] * s[1];
+  } else {
+    for (int i = (int)s.size() - 2; i >= 0; --i) st[i] = st[i + 1] * s[i + 1];
+  }
+  return st;
+}
+// Logical dimensions in physical order, outermost first.
+std::vector<int> phys_order(const Shape& s, bool nhwc) {
+  std::vector<int> o(s.size());
+  for (size_t i = 0; i < s.size(); ++i) o[i] = (int)i;
+  if (nhwc) o = {0, 2, 3, 1};
+  return o;
+}
+
+void plan_deleter(void* p) { free(p); }
+
+}  // namespace
+
+void* Executor::dalloc(size_t bytes) {
+  void* p = nullptr;
+  const size_t sz = std::max<size_t>((bytes + 255) / 256 * 256, 256);
+  CUDA_OK(cudaMalloc(&p, sz));
+  allocs_.push_back(p);
+  device_bytes_ += sz;
+  return p;
+}
+
+struct Lowering {
+  Executor& ex;
+  const Graph& g;
+  std::vector<DevBuf> buf;
+  std::vector<int> uses;
+  std::vector<char> is_head, safe8, absorbed;
+
+  Lowering(Executor& e, const Graph& gr) : ex(e), g(gr) {}
+
+  void add_step(const std::string& label, std::function<int(cudaStream_t)> fn) {
+    ex.steps_.push_back({label, std::move(fn)});
+  }
+
+  // ------------------------------------------------------------------ analysis
+  void analyse() {
+    const uint32_t ne = g.num_entries;
+    buf.assign(ne, DevBuf());
+    uses.assign(ne, 0);
+    is_head.assign(ne, 0);
+    safe8.assign(ne, 0);
+    absorbed.assign(g.nodes.size(), 0);
+    for (const auto& n : g.nodes)
+      for (const auto& e : n.inputs) uses[g.entry_id(e)]++;
+    for (const auto& e : g.outputs) is_head[g.entry_id(e)] = 1;
+    for (uint32_t nid = 0; nid < g.nodes.size(); ++nid) {
+      const Node& n = g.nodes[nid];
+      const uint32_t e0 = g.entry_id(nid, 0);
+      auto in_safe = [&](size_t i) { return (bool)safe8[g.entry_id(n.inputs[i])]; };
+      if (n.is_variable()) { safe8[e0] = g.precision[e0] <= 8; continue; }
+      const std::string& op = n.op->name;
+      bool s = false;
+      if (op == "cvm_clip" || op == "cvm_left_shift") s = n.attrs.i("precision") <= 8;
+      else if (op == "clip") s = n.attrs.i("a_min") >= -127 && n.attrs.i("a_max") <= 127;
+      else if (op == "cvm_right_shift") {
+        const int64_t p = n.attrs.i("precision"), b = n.attrs.i("shift_bit");
+        s = p == 1 || b >= 31 || (p <= 8 && p + b < 32);
+      } else if (op == "relu" || op == "max_pool2d" || op == "upsampling" || op == "flatten" ||
+                 op == "reshape" || op == "squeeze" || op == "expand_dims" || op == "abs" ||
+                 op == "negative" || op == "max") s = in_safe(0);
+      else if (op == "concatenate" || op == "broadcast_max") {
+        s = true;
+        for (size_t i = 0; i < n.inputs.size(); ++i) s = s && in_safe(i);
+      } else if (op == "cvm_precision" || op == "broadcast_greater") s = true;
+      safe8[e0] = s;
+    }
+    for (uint32_t e = 0; e < ne; ++e) {
+      buf[e].shape = g.shape[e];
+      buf[e].dtype = safe8[e] ? CVMK_I8 : CVMK_I32;
+      buf[e].nhwc = wants_nhwc(g.shape[e]);
+    }
+  }
+
+  // ------------------------------------------------------------------ buffers
+  DevBuf& materialize(uint32_t eid) {
+    DevBuf& b = buf[eid];
+    if (b.ptr) return b;
+    auto it = g.params.find(eid);
+    b.ptr = ex.dalloc(b.bytes());
+    if (it != g.params.end()) {
+      // parameter: convert on the host into the entry's dtype and layout, upload once
+      const HostTensor& t = it->second;
+      const int64_t n = shape_size(b.shape);
+      std::vector<int32_t> phys(n);
+      if (b.nhwc) {
+        const int64_t C = b.shape[1], H = b.shape[2], W = b.shape[3];
+        for (int64_t i = 0; i < n; ++i) {
+          const int64_t w = i % W, h = (i / W) % H, c = (i / (W * H)) % C, nn = i / (W * H * C);
+          phys[((nn * H + h) * W + w) * C + c] = t.data[i];
+        }
+      } else {
+        phys = t.data;
+      }
+      if (b.dtype == CVMK_I8) {
+        std::vector<int8_t> p8(n);
+        for (int64_t i = 0; i < n; ++i) p8[i] = (int8_t)phys[i];
+        CUDA_OK(cudaMemcpy(b.ptr, p8.data(), n, cudaMemcpyHostToDevice));
+      } else {
+        CUDA_OK(cudaMemcpy(b.ptr, phys.data(), n * 4, cudaMemcpyHostToDevice));
+      }
+    }
+    return b;
+  }
+
+  // Same logical tensor copied between two buffers that may differ in layout and dtype.
+  void emit_convert(const DevBuf& src, const DevBuf& dst, const std::string& label,
+                    const cvmk_epilogue* ep = nullptr) {
+    cvmk_strided_desc d;
+    memset(&d, 0, sizeof(d));
+    d.op = CVMK_OP_COPY;
+    const Shape& s = dst.shape;
+    const auto order = phys_order(s, dst.nhwc);
+    const auto ss = phys_strides(src.shape, src.nhwc), ds = phys_strides(s, dst.nhwc);
+    d.ndim = (int)s.size();
+    for (int k = 0; k < d.ndim; ++k) {
+      d.extent[k] = s[order[k]];
+      d.a_stride[k] = ss[order[k]];
+      d.y_stride[k] = ds[order[k]];
+    }
+    d.a = src.ptr; d.a_dtype = src.dtype;
+    d.y = dst.ptr; d.y_dtype = dst.dtype;
+    if (ep) d.ep = *ep;
+    add_step(label, [d](cudaStream_t s_) { return cvmk_strided(&d, s_); });
+  }
+
+  // A row-major view of an entry; converts into a temporary when the entry is channels-last.
+  DevBuf canon_view(uint32_t eid, const std::string& label) {
+    DevBuf& b = materialize(eid);
+    if (!b.nhwc) return b;
+    DevBuf t = b;
+    t.nhwc = false;
+    t.ptr = ex.dalloc(t.bytes());
+    emit_convert(b, t, label + ":to_rowmajor");
+    return t;
+  }
+  // int32 row-major view (get_valid_counts / nms operands).
+  DevBuf canon_i32_view(uint32_t eid, const std::string& label) {
+    DevBuf& b = materialize(eid);
+    if (!b.nhwc && b.dtype == CVMK_I32) return b;
+    DevBuf t = b;
+    t.nhwc = false;
+    t.dtype = CVMK_I32;
+    t.ptr = ex.dalloc(t.bytes());
+    emit_convert(b, t, label + ":to_i32");
+    return t;
+  }
+  // int8 view in the entry's own layout; narrows like static_cast<int8_t> when stored as int32.
+  DevBuf i8_view(uint32_t eid, const std::string& label) {
+    DevBuf& b = materialize(eid);
+    if (b.dtype == CVMK_I8) return b;
+    DevBuf t = b;
+    t.dtype = CVMK_I8;
+    t.ptr = ex.dalloc(t.bytes());
+    const DevBuf src = b;
+    const int64_t n = shape_size(b.shape);
+    add_step(label + ":narrow", [src, t, n](cudaStream_t s) {
+      return cvmk_elemwise(src.ptr, src.dtype, t.ptr, t.dtype, n, nullptr, s);
+    });
+    return t;
+  }
+
+  // ------------------------------------------------------------------ chains
+  struct Chain {
+    cvmk_epilogue ep;
+    uint32_t tail_eid;
+    uint32_t tail_nid;
+  };
+
+  bool scalar_param(uint32_t eid, int32_t* v) const {
+    auto it = g.params.find(eid);
+    if (it == g.params.end() || it->second.data.size() != 1) return false;
+    *v = it->second.data[0];
+    return true;
+  }
+
+  // Translate node `nid`, consuming entry `cur`, into one chain step.  False if not expressible.
+  bool node_as_step(uint32_t nid, uint32_t cur, cvmk_ep_step* st) {
+    const Node& n = g.nodes[nid];
+    const std::string& op = n.op->name;
+    memset(st, 0, sizeof(*st));
+    auto alpha = [&](int64_t p) { return (int32_t)((((int64_t)1) << (p - 1)) - 1); };
+    if (op == "relu") st->op = CVMK_EP_RELU;
+    else if (op == "abs") st->op = CVMK_EP_ABS;
+    else if (op == "negative") st->op = CVMK_EP_NEG;
+    else if (op == "cvm_precision") st->op = CVMK_EP_PRECISION;
+    else if (op == "clip") { st->op = CVMK_EP_CLIP; st->a = (int32_t)n.attrs.i("a_min"); st->b = (int32_t)n.attrs.i("a_max"); }
+    else if (op == "cvm_clip") { st->op = CVMK_EP_CLIP; st->b = alpha(n.attrs.i("precision")); st->a = -st->b; }
+    else if (op == "cvm_right_shift") { st->op = CVMK_EP_RSHIFT; st->a = (int32_t)n.attrs.i("shift_bit"); st->b = (int32_t)n.attrs.i("precision"); }
+    else if (op == "cvm_left_shift") { st->op = CVMK_EP_LSHIFT; st->a = (int32_t)n.attrs.i("shift_bit"); st->b = (int32_t)n.attrs.i("precision"); }
+    else if (op == "elemwise_add" || op == "elemwise_sub") {
+      const uint32_t e0 = g.entry_id(n.inputs[0]), e1 = g.entry_id(n.inputs[1]);
+      if (e0 == e1) return false;
+      const uint32_t other = e0 == cur ? e1 : e0;
+      if (op == "elemwise_add") st->op = CVMK_EP_ADD_T;
+      else st->op = e0 == cur ? CVMK_EP_SUB_T : CVMK_EP_RSUB_T;
+      st->ptr = reinterpret_cast<const void*>((uintptr_t)other + 1);  // resolved in bind_chain()
+    } else if (op.compare(0, 10, "broadcast_") == 0) {
+      const uint32_t e0 = g.entry_id(n.inputs[0]), e1 = g.entry_id(n.inputs[1]);
+      if (e0 == e1) return false;
+      const uint32_t other = e0 == cur ? e1 : e0;
+      int32_t v;
+      if (!scalar_param(other, &v)) return false;
+      if (g.shape[g.entry_id(nid, 0)] != g.shape[cur]) return false;
+      const bool lhs = e0 == cur;
+      if (op == "broadcast_add") { st->op = CVMK_EP_ADD_S; st->a = v; }
+      else if (op == "broadcast_sub") {
+        if (lhs) { st->op = CVMK_EP_ADD_S; st->a = (int32_t)(0u - (uint32_t)v); }
+        else { st->op = CVMK_EP_RSUB_S; st->a = v; }
+      } else if (op == "broadcast_mul") { st->op = CVMK_EP_MUL_S; st->a = v; }
+      else if (op == "broadcast_max") { st->op = CVMK_EP_MAX_S; st->a = v; }
+      else if (op == "broadcast_div") { st->op = lhs ? CVMK_EP_DIV_S : CVMK_EP_RDIV_S; st->a = v; }
+      else if (op == "broadcast_greater") { st->op = lhs ? CVMK_EP_GT_S : CVMK_EP_LT_S; st->a = v; }
+      else return false;
+    } else {
+      return false;
+    }
+    return true;
+  }
+
+  // Greedily absorb single-consumer element-wise successors of entry `start`.
+  void extend_chain(Chain* c) {
+    while (c->ep.n < CVMK_MAX_EP_STEPS) {
+      const uint32_t cur = c->tail_eid;
+      if (is_head[cur] || uses[cur] != 1) break;
+      uint32_t consumer = UINT32_MAX;
+      for (uint32_t nid = c->tail_nid + 1; nid < g.nodes.size() && consumer == UINT32_MAX; ++nid)
+        for (const auto& e : g.nodes[nid].inputs)
+          if (g.entry_id(e) == cur) { consumer = nid; break; }
+      if (consumer == UINT32_MAX) break;
+      cvmk_ep_step st;
+      if (!node_as_step(consumer, cur, &st)) break;
+      c->ep.s[c->ep.n++] = st;
+      absorbed[consumer] = 1;
+      c->tail_nid = consumer;
+      c->tail_eid = g.entry_id(consumer, 0);
+    }
+  }
+
+  // Replace the entry placeholders of *_T steps by device pointers.
+  void bind_chain(cvmk_epilogue* ep) {
+    for (int i = 0; i < ep->n; ++i) {
+      cvmk_ep_step& s = ep->s[i];
+      if (s.op == CVMK_EP_ADD_T || s.op == CVMK_EP_SUB_T || s.op == CVMK_EP_RSUB_T) {
+        const uint32_t other = (uint32_t)((uintptr_t)s.ptr - 1);
+        DevBuf& o = materialize(other);
+        s.ptr = o.ptr;
+        s.ptr_dtype = o.dtype;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ operators
+  const int32_t* bias_vector(uint32_t eid) {
+    auto it = g.params.find(eid);
+    if (it != g.params.end()) {  // the usual case: upload the int32 vector once
+      const auto& v = it->second.data;
+      void* p = ex.dalloc(v.size() * 4);
+      CUDA_OK(cudaMemcpy(p, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
+      return reinterpret_cast<const int32_t*>(p);
+    }
+    DevBuf b = canon_i32_view(eid, "bias");
+    return reinterpret_cast<const int32_t*>(b.ptr);
+  }
+
+  void lower_conv_like(uint32_t nid, bool dense) {
+    const Node& n = g.nodes[nid];
+    const uint32_t ex_ = g.entry_id(n.inputs[0]), ew = g.entry_id(n.inputs[1]);
+    const bool use_bias = n.attrs.b("use_bias");
+    const Shape& xs = g.shape[ex_];
+    const Shape& wsh = g.shape[ew];
+    auto wit = g.params.find(ew);
+    CHECK(wit != g.params.end()) << n.op->name << " " << n.name() << ": weights must be a parameter";
+    const HostTensor& wt = wit->second;
+
+    int N, H, W, C, OC, KH, KW, OH, OW, groups, sh, sw, ph, pw, dh, dw;
+    if (dense) {
+      N = (int)xs[0]; H = W = 1; C = (int)xs[1]; OC = (int)wsh[0]; KH = KW = 1; OH = OW = 1; groups = 1;
+      sh = sw = dh = dw = 1; ph = pw = 0;
+    } else {
+      const Shape& os = g.shape[g.entry_id(nid, 0)];
+      N = (int)xs[0]; C = (int)xs[1]; H = (int)xs[2]; W = (int)xs[3];
+      OC = (int)wsh[0]; KH = (int)wsh[2]; KW = (int)wsh[3]; OH = (int)os[2]; OW = (int)os[3];
+      groups = (int)n.attrs.i("groups");
+      sh = (int)n.attrs.t("strides")[0]; sw = (int)n.attrs.t("strides")[1];
+      ph = (int)n.attrs.t("padding")[0]; pw = (int)n.attrs.t("padding")[1];
+      dh = (int)n.attrs.t("dilation")[0]; dw = (int)n.attrs.t("dilation")[1];
+    }
+    const int icg = C / groups;
+
+    Chain ch;
+    memset(&ch.ep, 0, sizeof(ch.ep));
+    ch.tail_eid = g.entry_id(nid, 0);
+    ch.tail_nid = nid;
+    if (use_bias) {
+      ch.ep.s[0].op = CVMK_EP_ADD_C;
+      ch.ep.s[0].ptr = bias_vector(g.entry_id(n.inputs[2]));
+      ch.ep.n = 1;
+    }
+    extend_chain(&ch);
+    bind_chain(&ch.ep);
+    DevBuf& out = materialize(ch.tail_eid);
+    const std::string label = n.op->name + ":" + n.name();
+
+    cvmk_conv_desc probe;
+    memset(&probe, 0, sizeof(probe));
+    probe.N = N; probe.H = H; probe.W = W; probe.C = C; probe.OC = OC; probe.KH = KH; probe.KW = KW;
+    probe.OH = OH; probe.OW = OW; probe.stride_h = sh; probe.stride_w = sw; probe.pad_h = ph; probe.pad_w = pw;
+    probe.dil_h = dh; probe.dil_w = dw;
+    const bool tc = groups == 1 && cvmk_conv2d_tc_supported(&probe) && !getenv("CVM_B200_NO_TC");
+    const bool depthwise = !dense && groups == C && OC == C && C % 16 == 0 && safe8[ex_];
+
+    // weights: OIHW int32 -> int8, [OC, KH, KW, C/groups] (depthwise: [KH, KW, C])
+    std::vector<int8_t> w8((size_t)OC * KH * KW * icg);
+    if (depthwise && !tc) {
+      for (int c = 0; c < C; ++c)
+        for (int k = 0; k < KH * KW; ++k) w8[(size_t)k * C + c] = (int8_t)wt.data[(size_t)c * KH * KW + k];
+    } else {
+      for (int o = 0; o < OC; ++o)
+        for (int i = 0; i < icg; ++i)
+          for (int k = 0; k < KH * KW; ++k)
+            w8[((size_t)o * KH * KW + k) * icg + i] = (int8_t)wt.data[((size_t)o * icg + i) * KH * KW + k];
+    }
+    int8_t* wdev = (int8_t*)ex.dalloc(w8.size());
+    CUDA_OK(cudaMemcpy(wdev, w8.data(), w8.size(), cudaMemcpyHostToDevice));
+
+    if (tc) {
+      DevBuf xin = i8_view(ex_, label);
+      cvmk_conv_desc d = probe;
+      d.x = (const int8_t*)xin.ptr; d.w = wdev; d.y = out.ptr; d.y_dtype = out.dtype;
+      d.status = ex.status_dev_;
+      d.ep = ch.ep;
+      void* mem = nullptr;
+      CHECK(posix_memalign(&mem, 64, sizeof(cvmk_conv_plan)) == 0);
+      ex.plans_.emplace_back((cvmk_conv_plan*)mem, plan_deleter);
+      cvmk_conv_plan* plan = ex.plans_.back().get();
+      KERNEL_OK(cvmk_conv2d_tc_prepare(&d, plan));
+      add_step(label + "[tc]", [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
+    } else {
+      DevBuf& xin = materialize(ex_);
+      cvmk_conv_direct_desc d;
+      memset(&d, 0, sizeof(d));
+      d.x = xin.ptr; d.x_dtype = xin.dtype; d.narrow_x = groups == 1;
+      d.w = wdev; d.y = out.ptr; d.y_dtype = out.dtype;
+      d.N = N; d.H = H; d.W = W; d.C = C; d.OC = OC; d.KH = KH; d.KW = KW; d.OH = OH; d.OW = OW; d.groups = groups;
+      d.stride_h = sh; d.stride_w = sw; d.pad_h = ph; d.pad_w = pw; d.dil_h = dh; d.dil_w = dw;
+      d.depthwise = depthwise;
+      d.ep = ch.ep;
+      add_step(label + (depthwise ? "[dw]" : "[direct]"), [d](cudaStream_t s) { return cvmk_conv2d_direct(&d, s); });
+    }
+  }
+
+  // Element-wise root: unary ops, elemwise_add/sub, broadcast with a scalar parameter.
+  bool lower_elemwise_root(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    uint32_t src = g.entry_id(n.inputs[0]);
+    cvmk_ep_step st;
+    if (!node_as_step(nid, src, &st)) {
+      if (n.inputs.size() == 2) {
+        src = g.entry_id(n.inputs[1]);
+        if (!node_as_step(nid, src, &st)) return false;
+      } else {
+        return false;
+      }
+    }
+    if (g.shape[src] != g.shape[g.entry_id(nid, 0)]) return false;
+    Chain ch;
+    memset(&ch.ep, 0, sizeof(ch.ep));
+    ch.ep.s[0] = st;
+    ch.ep.n = 1;
+    ch.tail_eid = g.entry_id(nid, 0);
+    ch.tail_nid = nid;
+    extend_chain(&ch);
+    bind_chain(&ch.ep);
+    const DevBuf x = materialize(src);
+    const DevBuf y = materialize(ch.tail_eid);
+    const cvmk_epilogue ep = ch.ep;
+    const int64_t cnt = shape_size(x.shape);
+    add_step(n.op->name + ":" + n.name(), [x, y, ep, cnt](cudaStream_t s) {
+      return cvmk_elemwise(x.ptr, x.dtype, y.ptr, y.dtype, cnt, &ep, s);
+    });
+    return true;
+  }
+
+  void lower_broadcast(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const std::string& op = n.op->name;
+    const uint32_t ea = g.entry_id(n.inputs[0]), eb = g.entry_id(n.inputs[1]), eo = g.entry_id(nid, 0);
+    const DevBuf a = materialize(ea), b = materialize(eb);
+    Chain ch;
+    memset(&ch.ep, 0, sizeof(ch.ep));
+    ch.tail_eid = eo;
+    ch.tail_nid = nid;
+    // A fused tail must keep the shape (and with it the layout) of this node's output.
+    extend_chain(&ch);
+    bind_chain(&ch.ep);
+    const DevBuf y = materialize(ch.tail_eid);
+    cvmk_strided_desc d;
+    memset(&d, 0, sizeof(d));
+    d.op = (op == "broadcast_add" || op == "elemwise_add") ? CVMK_OP_ADD
+         : (op == "broadcast_sub" || op == "elemwise_sub") ? CVMK_OP_SUB
+         : op == "broadcast_mul" ? CVMK_OP_MUL : op == "broadcast_max" ? CVMK_OP_MAX
+         : op == "broadcast_div" ? CVMK_OP_DIV : CVMK_OP_GREATER;
+    const Shape& os = y.shape;
+    const auto order = phys_order(os, y.nhwc);
+    const auto ys = phys_strides(os, y.nhwc);
+    const auto as = phys_strides(a.shape, a.nhwc), bs = phys_strides(b.shape, b.nhwc);
+    d.ndim = (int)os.size();
+    const int offa = (int)os.size() - (int)a.shape.size(), offb = (int)os.size() - (int)b.shape.size();
+    for (int k = 0; k < d.ndim; ++k) {
+      const int j = order[k];
+      d.extent[k] = os[j];
+      d.y_stride[k] = ys[j];
+      d.a_stride[k] = (j - offa >= 0 && a.shape[j - offa] != 1) ? as[j - offa] : 0;
+      d.b_stride[k] = (j - offb >= 0 && b.shape[j - offb] != 1) ? bs[j - offb] : 0;
+    }
+    d.a = a.ptr; d.a_dtype = a.dtype; d.b = b.ptr; d.b_dtype = b.dtype; d.y = y.ptr; d.y_dtype = y.dtype;
+    d.ep = ch.ep;
+    add_step(op + ":" + n.name(), [d](cudaStream_t s) { return cvmk_strided(&d, s); });
+  }
+
+  void lower_pool(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const uint32_t ei = g.entry_id(n.inputs[0]), eo = g.entry_id(nid, 0);
+    const DevBuf x = materialize(ei);
+    const DevBuf y = materialize(eo);
+    CHECK(x.dtype == y.dtype);
+    const Shape& pad = n.attrs.t("padding");
+    cvmk_pool_desc d;
+    memset(&d, 0, sizeof(d));
+    d.x = x.ptr; d.y = y.ptr; d.dtype = x.dtype;
+    d.N = (int)x.shape[0]; d.C = (int)x.shape[1]; d.H = (int)x.shape[2]; d.W = (int)x.shape[3];
+    d.OH = (int)y.shape[2]; d.OW = (int)y.shape[3];
+    d.KH = (int)n.attrs.t("pool_size")[0]; d.KW = (int)n.attrs.t("pool_size")[1];
+    d.stride_h = (int)n.attrs.t("strides")[0]; d.stride_w = (int)n.attrs.t("strides")[1];
+    d.pad_h = (int)pad[0]; d.pad_w = (int)(pad.size() == 2 ? pad[1] : pad[0]);
+    add_step("max_pool2d:" + n.name(), [d](cudaStream_t s) { return cvmk_max_pool2d(&d, s); });
+  }
+
+  void lower_upsampling(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const DevBuf x = materialize(g.entry_id(n.inputs[0]));
+    const DevBuf y = materialize(g.entry_id(nid, 0));
+    const int64_t sc = n.attrs.i("scale");
+    const int64_t N = x.shape[0], C = x.shape[1], H = x.shape[2], W = x.shape[3];
+    const auto xs = phys_strides(x.shape, x.nhwc), ys = phys_strides(y.shape, y.nhwc);
+    cvmk_strided_desc d;
+    memset(&d, 0, sizeof(d));
+    d.op = CVMK_OP_COPY;
+    d.ndim = 6;
+    // iteration space (N, H, s, W, s, C); the two s extents do not move the source
+    const int64_t ext[6] = {N, H, sc, W, sc, C};
+    const int64_t as[6] = {xs[0], xs[2], 0, xs[3], 0, xs[1]};
+    const int64_t yst[6] = {ys[0], ys[2] * sc, ys[2], ys[3] * sc, ys[3], ys[1]};
+    for (int k = 0; k < 6; ++k) { d.extent[k] = ext[k]; d.a_stride[k] = as[k]; d.y_stride[k] = yst[k]; }
+    d.a = x.ptr; d.a_dtype = x.dtype; d.y = y.ptr; d.y_dtype = y.dtype;
+    add_step("upsampling:" + n.name(), [d](cudaStream_t s) { return cvmk_strided(&d, s); });
+  }
+
+  void lower_concat(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const DevBuf y = materialize(g.entry_id(nid, 0));
+    const int nd = (int)y.shape.size();
+    int axis = (int)n.attrs.i("axis");
+    if (axis < 0) axis += nd;
+    const auto ys = phys_strides(y.shape, y.nhwc);
+    int64_t offset = 0;
+    for (size_t m = 0; m < n.inputs.size(); ++m) {
+      const DevBuf x = materialize(g.entry_id(n.inputs[m]));
+      const auto order = phys_order(x.shape, y.nhwc);
+      const auto xs = phys_strides(x.shape, x.nhwc);
+      cvmk_strided_desc d;
+      memset(&d, 0, sizeof(d));
+      d.op = CVMK_OP_COPY;
+      d.ndim = nd;
+      for (int k = 0; k < nd; ++k) {
+        d.extent[k] = x.shape[order[k]];
+        d.a_stride[k] = xs[order[k]];
+        d.y_stride[k] = ys[order[k]];
+      }
+      d.a = x.ptr; d.a_dtype = x.dtype; d.y = y.ptr; d.y_dtype = y.dtype;
+      d.y_off = offset * ys[axis];
+      offset += x.shape[axis];
+      add_step("concatenate:" + n.name(), [d](cudaStream_t s) { return cvmk_strided(&d, s); });
+    }
+  }
+
+  // flatten / reshape / squeeze / expand_dims: the row-major element order is preserved.
+  void lower_reshape(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const uint32_t ei = g.entry_id(n.inputs[0]), eo = g.entry_id(nid, 0);
+    DevBuf src = canon_view(ei, n.op->name + ":" + n.name());
+    DevBuf& out = buf[eo];
+    CHECK(out.dtype == src.dtype);
+    if (!out.nhwc) {
+      out.ptr = src.ptr;  // alias
+      return;
+    }
+    materialize(eo);
+    DevBuf as_canon = out;
+    as_canon.nhwc = false;
+    as_canon.ptr = src.ptr;
+    emit_convert(as_canon, out, n.op->name + ":" + n.name() + ":to_nhwc");
+  }
+
+  // sum / max.  The kept-dimension mapping follows cpu/ops/reduce.cc:66-89 literally, including
+  // its pairing of the output's non-unit dimensions with the input's non-reduced ones from the
+  // right.
+  void lower_reduce(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const uint32_t ei = g.entry_id(n.inputs[0]), eo = g.entry_id(nid, 0);
+    const DevBuf x = materialize(ei);
+    const Shape& xs = x.shape;
+    const Shape& ysh = g.shape[eo];
+    const int xnd = (int)xs.size();
+    Shape axis = n.attrs.t("axis");
+    const bool exclude = n.attrs.b("exclude");
+    for (auto& a : axis) if (a < 0) a += xnd;
+    std::vector<int64_t> real;
+    if (!exclude) real.assign(axis.begin(), axis.end());
+    else {
+      for (int i = 0; i < xnd; ++i)
+        if (std::find(axis.begin(), axis.end(), i) == axis.end()) real.push_back(i);
+    }
+    Chain ch;
+    memset(&ch.ep, 0, sizeof(ch.ep));
+    ch.tail_eid = eo;
+    ch.tail_nid = nid;
+    const std::string label = n.op->name + ":" + n.name();
+    if (exclude && real.empty()) {  // plain copy, reduce.cc:38-39
+      extend_chain(&ch);
+      bind_chain(&ch.ep);
+      DevBuf y = materialize(ch.tail_eid);
+      DevBuf srcv = x;
+      srcv.shape = y.shape;  // same element order when both are row-major
+      if (x.nhwc || y.nhwc) {
+        DevBuf c = canon_view(ei, label);
+        c.shape = y.shape;
+        emit_convert(c, y, label, &ch.ep);
+      } else {
+        emit_convert(srcv, y, label, &ch.ep);
+      }
+      return;
+    }
+    const bool out_needs_convert = wants_nhwc(ysh);
+    if (!out_needs_convert) { extend_chain(&ch); bind_chain(&ch.ep); }
+    const auto xst = phys_strides(xs, x.nhwc);
+    cvmk_reduce_desc d;
+    memset(&d, 0, sizeof(d));
+    d.is_max = n.op->name == "max";
+    if (real.empty()) {
+      d.init_zero = 1;
+      d.n_keep = 0;
+      d.n_red = xnd;
+      for (int k = 0; k < xnd; ++k) { d.red_extent[k] = xs[k]; d.red_stride[k] = xst[k]; }
+    } else {
+      std::vector<char> flag(xnd, 0);
+      for (auto a : real) flag[a] = 1;
+      std::sort(real.begin(), real.end());
+      d.n_red = (int)real.size();
+      for (int k = 0; k < d.n_red; ++k) { d.red_extent[k] = xs[real[k]]; d.red_stride[k] = xst[real[k]]; }
+      // every_xdim_size of the reference is the row-major stride; here the physical one is used,
+      // which addresses the same logical element.
+      std::vector<int64_t> ynz;
+      for (auto v : ysh) if (v != 1) ynz.push_back(v);
+      d.n_keep = (int)ynz.size();
+      int xj = xnd - 1;
+      for (int j = d.n_keep - 1; j >= 0; --j) {
+        while (xj >= 0 && flag[xj--]) {}
+        d.keep_extent[j] = ynz[j];
+        d.keep_stride[j] = xj + 1 >= 0 && xj + 1 < xnd ? xst[xj + 1] : 0;
+      }
+    }
+    d.x = x.ptr; d.x_dtype = x.dtype;
+    if (out_needs_convert) {
+      DevBuf tmp = buf[eo];
+      tmp.nhwc = false;
+      tmp.ptr = ex.dalloc(tmp.bytes());
+      d.y = tmp.ptr; d.y_dtype = tmp.dtype;
+      add_step(label, [d](cudaStream_t s) { return cvmk_reduce(&d, s); });
+      emit_convert(tmp, materialize(eo), label + ":to_nhwc");
+    } else {
+      DevBuf y = materialize(ch.tail_eid);
+      d.y = y.ptr; d.y_dtype = y.dtype;
+      d.ep = ch.ep;
+      add_step(label, [d](cudaStream_t s) { return cvmk_reduce(&d, s); });
+    }
+  }
+
+  void lower_gvc(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const std::string label = "get_valid_counts:" + n.name();
+    const DevBuf x = canon_i32_view(g.entry_id(n.inputs[0]), label);
+    const DevBuf vc = materialize(g.entry_id(nid, 0));
+    const DevBuf y = materialize(g.entry_id(nid, 1));
+    CHECK(vc.dtype == CVMK_I32 && y.dtype == CVMK_I32);
+    const int B = (int)x.shape[0], N = (int)x.shape[1], K = (int)x.shape[2];
+    const int thr = (int)n.attrs.i("score_threshold");
+    add_step(label, [x, y, vc, B, N, K, thr](cudaStream_t s) {
+      return cvmk_get_valid_counts((const int32_t*)x.ptr, (int32_t*)y.ptr, (int32_t*)vc.ptr, B, N, K, thr, s);
+    });
+  }
+
+  void lower_nms(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const std::string label = "non_max_suppression:" + n.name();
+    const DevBuf x = canon_i32_view(g.entry_id(n.inputs[0]), label);
+    const DevBuf vc = canon_i32_view(g.entry_id(n.inputs[1]), label);
+    const DevBuf y = materialize(g.entry_id(nid, 0));
+    CHECK(y.dtype == CVMK_I32);
+    cvmk_nms_desc d;
+    memset(&d, 0, sizeof(d));
+    d.x = (const int32_t*)x.ptr; d.valid_count = (const int32_t*)vc.ptr; d.y = (int32_t*)y.ptr;
+    d.B = (int)x.shape[0]; d.N = (int)x.shape[1];
+    d.max_output_size = (int)n.attrs.i("max_output_size");
+    d.iou_threshold = (int)n.attrs.i("iou_threshold");
+    d.top_k = (int)n.attrs.i("top_k");
+    d.force_suppress = n.attrs.b("force_suppress") ? 1 : 0;
+    d.scratch_bytes = cvmk_nms_scratch_bytes(d.B, d.N);
+    d.scratch = ex.dalloc((size_t)d.scratch_bytes);
+    add_step(label, [d](cudaStream_t s) { return cvmk_non_max_suppression(&d, s); });
+  }
+
+  void lower_node(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const std::string& op = n.op->name;
+    if (op == "conv2d") return lower_conv_like(nid, false);
+    if (op == "dense") return lower_conv_like(nid, true);
+    if (op == "max_pool2d") return lower_pool(nid);
+    if (op == "upsampling") return lower_upsampling(nid);
+    if (op == "concatenate") return lower_concat(nid);
+    if (op == "flatten" || op == "reshape" || op == "squeeze" || op == "expand_dims") return lower_reshape(nid);
+    if (op == "sum" || op == "max") return lower_reduce(nid);
+    if (op == "get_valid_counts") return lower_gvc(nid);
+    if (op == "non_max_suppression") return lower_nms(nid);
+    if (lower_elemwise_root(nid)) return;
+    if (op.compare(0, 10, "broadcast_") == 0 || op == "elemwise_add" || op == "elemwise_sub")
+      return lower_broadcast(nid);
+    FATAL() << "function undefined cvm.runtime.gpu." << op;
+  }
+
+  void run() {
+    analyse();
+    // graph input: raw API bytes -> clamp to the declared precision -> entry buffer
+    int data_nid = -1;
+    for (uint32_t nid = 0; nid < g.nodes.size(); ++nid)
+      if (g.nodes[nid].is_data()) data_nid = (int)nid;
+    CHECK(data_nid >= 0) << "can not find input `data`";
+    {
+      const uint32_t eid = g.entry_id(data_nid, 0);
+      const int prec = g.precision[eid];
+      DevBuf& dst = materialize(eid);
+      DevBuf raw;
+      raw.shape = g.shape[eid];
+      raw.dtype = prec > 8 ? CVMK_I32 : CVMK_I8;
+      raw.nhwc = false;
+      ex.in_bytes_ = raw.bytes();
+      ex.in_dev_ = ex.dalloc(ex.in_bytes_);
+      CUDA_OK(cudaMallocHost(&ex.in_host_, ex.in_bytes_));
+      memset(ex.in_host_, 0, ex.in_bytes_);
+      ex.pinned_.push_back(ex.in_host_);
+      raw.ptr = ex.in_dev_;
+      cvmk_epilogue ep;
+      memset(&ep, 0, sizeof(ep));
+      const int32_t range = (int32_t)((1u << (prec - 1)) - 1);
+      ep.n = 1;
+      ep.s[0].op = CVMK_EP_CLIP;
+      ep.s[0].a = -range;
+      ep.s[0].b = range;
+      emit_convert(raw, dst, "input:data", &ep);  // graph_runtime.cc:379-386
+    }
+    // Fused groups are emitted at the position of their last member, so every operand of the
+    // chain already exists when the kernel runs.
+    std::vector<std::pair<uint32_t, uint32_t>> order;  // (schedule position, root)
+    {
+      // A dry pass decides the groups; the step lists of the groups are then ordered by tail.
+      std::vector<std::vector<Step>> per_root(g.nodes.size());
+      std::vector<uint32_t> tail(g.nodes.size(), 0);
+      std::vector<Step> prologue = ex.steps_;
+      ex.steps_.clear();
+      for (uint32_t nid = 0; nid < g.nodes.size(); ++nid) {
+        const Node& n = g.nodes[nid];
+        if (n.is_variable() || absorbed[nid]) continue;
+        const size_t before = ex.steps_.size();
+        uint32_t last = nid;
+        lower_node(nid);
+        for (uint32_t k = nid + 1; k < g.nodes.size(); ++k)
+          if (absorbed[k] == 1) { absorbed[k] = 2; last = std::max(last, k); }
+        per_root[nid].assign(ex.steps_.begin() + before, ex.steps_.end());
+        ex.steps_.resize(before);
+        tail[nid] = last;
+        order.emplace_back(last, nid);
+      }
+      std::stable_sort(order.begin(), order.end());
+      ex.steps_ = prologue;
+      for (const auto& pr : order)
+        for (auto& s : per_root[pr.second]) ex.steps_.push_back(std::move(s));
+    }
+    // heads: row-major staging + pinned host mirrors
+    for (const auto& e : g.outputs) {
+      const uint32_t eid = g.entry_id(e);
+      DevBuf c = canon_view(eid, "head");
+      HeadOut h;
+      h.shape = c.shape;
+      h.dtype = c.dtype;
+      h.dev = c.ptr;
+      h.bytes = c.bytes();
+      CUDA_OK(cudaMallocHost(&h.host, h.bytes));
+      ex.pinned_.push_back(h.host);
+      ex.heads_.push_back(h);
+    }
+  }
+};
+
+Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
+  int count = 0;
+  CUDA_OK(cudaGetDeviceCount(&count));
+  CHECK(device_id >= 0 && device_id < count) << "device_id " << device_id << " out of range (" << count << " GPUs)";
+  CUDA_OK(cudaSetDevice(device_));
+  CUDA_OK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  status_dev_ = (int32_t*)dalloc(256);
+  CUDA_OK(cudaMemset(status_dev_, 0, 256));
+  CUDA_OK(cudaMallocHost((void**)&status_host_, 256));
+  pinned_.push_back(status_host_);
+  *status_host_ = 0;
+  use_graph_ = getenv("CVM_B200_NO_GRAPH") == nullptr;
+  Lowering low(*this, g);
+  low.run();
+  // One eager pass sets per-kernel attributes and surfaces launch errors before capture.
+  Enqueue(stream_);
+  CUDA_OK(cudaStreamSynchronize(stream_));
+  if (use_graph_) {
+    cudaGraph_t graph = nullptr;
+    CUDA_OK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+    Enqueue(stream_);
+    CUDA_OK(cudaStreamEndCapture(stream_, &graph));
+    CUDA_OK(cudaGraphInstantiate(&graph_exec_, graph, 0));
+    CUDA_OK(cudaGraphDestroy(graph));
+  }
+}
+
+Executor::~Executor() {
+  cudaSetDevice(device_);
+  if (stream_) cudaStreamSynchronize(stream_);
+  if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+  for (void* p : allocs_) cudaFree(p);
+  for (void* p : pinned_) cudaFreeHost(p);
+  if (stream_) cudaStreamDestroy(stream_);
+}
+
+void Executor::Enqueue(cudaStream_t s) {
+  CUDA_OK(cudaMemcpyAsync(in_dev_, in_host_, in_bytes_, cudaMemcpyHostToDevice, s));
+  for (auto& st : steps_) {
+    int rc = st.launch(s);
+    CHECK(rc == CVMK_OK) << "step " << st.label << " failed (" << rc << "): " << cvmk_last_error();
+  }
+  for (auto& h : heads_) CUDA_OK(cudaMemcpyAsync(h.host, h.dev, h.bytes, cudaMemcpyDeviceToHost, s));
+  CUDA_OK(cudaMemcpyAsync(status_host_, status_dev_, 4, cudaMemcpyDeviceToHost, s));
+}
+
+void Executor::Run(const void* input, size_t input_bytes) {
+  CHECK(input_bytes == in_bytes_) << "input size " << input_bytes << " vs. " << in_bytes_;
+  CUDA_OK(cudaSetDevice(device_));
+  memcpy(in_host_, input, in_bytes_);
+  if (graph_exec_) CUDA_OK(cudaGraphLaunch(graph_exec_, stream_));
+  else Enqueue(stream_);
+  CUDA_OK(cudaStreamSynchronize(stream_));
+  if (*status_host_ != 0) {
+    const int code = *status_host_;
+    *status_host_ = 0;
+    cudaMemsetAsync(status_dev_, 0, 4, stream_);
+    cudaStreamSynchronize(stream_);
+    FATAL() << "a device-side wait ran out (status word 0x" << std::hex << code << ")";
+  }
+}
+
+std::vector<std::pair<std::string, float>> Executor::ProfileOnce(const void* input, size_t input_bytes) {
+  CHECK(input_bytes == in_bytes_);
+  CUDA_OK(cudaSetDevice(device_));
+  memcpy(in_host_, input, in_bytes_);
+  std::vector<std::pair<std::string, float>> out;
+  std::vector<cudaEvent_t> ev(steps_.size() + 1);
+  for (auto& e : ev) CUDA_OK(cudaEventCreate(&e));
+  CUDA_OK(cudaMemcpyAsync(in_dev_, in_host_, in_bytes_, cudaMemcpyHostToDevice, stream_));
+  CUDA_OK(cudaEventRecord(ev[0], stream_));
+  for (size_t i = 0; i < steps_.size(); ++i) {
+    KERNEL_OK(steps_[i].launch(stream_));
+    CUDA_OK(cudaEventRecord(ev[i + 1], stream_));
+  }
+  CUDA_OK(cudaStreamSynchronize(stream_));
+  for (size_t i = 0; i < steps_.size(); ++i) {
+    float ms = 0;
+    CUDA_OK(cudaEventElapsedTime(&ms, ev[i], ev[i + 1]));
+    out.emplace_back(steps_[i].label, ms);
+  }
+  for (auto& e : ev) cudaEventDestroy(e);
+  return out;
+}
+
+}  // namespace cvm

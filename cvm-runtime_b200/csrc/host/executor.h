@@ -1,0 +1,85 @@
+// Device executor: lowers a validated Graph into a static list of kernel launches on one GPU and
+// replays it per inference.
+//
+// The reference executor (CvmRuntime::SetupStorage / SetupOpExecs / Run,
+// src/runtime/graph_runtime.cc:576-698, :61-68) binds one int32 buffer per entry and runs one
+// operator body per node.  This one keeps the node-by-node semantics but chooses, at load time,
+//   - a storage type per entry: int8 where every value is provably within [-127, 127], else int32;
+//   - a physical layout: 4-D entries are held channels-last (NHWC), everything else row-major;
+//   - fusion: chains of element-wise successors with a single consumer are folded into the
+//     producing kernel (conv2d / dense / reduce / element-wise), so their int32 intermediates are
+//     never written;
+//   - pre-packed int8 weights (OIHW -> OHWI) and TMA tensor maps for the tensor-core convolutions;
+//   - a CUDA graph of the whole step list including the input upload and the output download.
+// There is no CPU fallback: every step is a CUDA kernel from this library.
+#pragma once
+#include <cuda_runtime.h>
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+#include "cvmk_kernels.h"
+#include "graph.h"
+
+namespace cvm {
+
+struct DevBuf {
+  Shape shape;          // logical shape
+  int dtype = CVMK_I32; // CVMK_I8 / CVMK_I32
+  bool nhwc = false;    // 4-D tensor stored as N,H,W,C
+  void* ptr = nullptr;
+  size_t bytes() const { return (size_t)shape_size(shape) * dtype; }
+};
+
+struct Step {
+  std::string label;
+  std::function<int(cudaStream_t)> launch;
+};
+
+struct HeadOut {
+  Shape shape;
+  int dtype;
+  void* dev = nullptr;       // canonical row-major copy on the device
+  void* host = nullptr;      // pinned
+  size_t bytes = 0;
+};
+
+class Executor {
+ public:
+  Executor(const Graph& g, int device_id);
+  ~Executor();
+  // Runs one inference.  `input` holds the `data` tensor in API form (int8 or int32, row-major).
+  // On return heads()[k].host holds head k (row-major, heads()[k].dtype).
+  void Run(const void* input, size_t input_bytes);
+  const std::vector<HeadOut>& heads() const { return heads_; }
+  size_t num_steps() const { return steps_.size(); }
+  size_t device_bytes() const { return device_bytes_; }
+  // Per-step device times of one eager pass (label, milliseconds); used by the profiling table.
+  std::vector<std::pair<std::string, float>> ProfileOnce(const void* input, size_t input_bytes);
+
+ private:
+  struct Impl;
+  const Graph& g_;
+  int device_;
+  cudaStream_t stream_ = nullptr;
+  std::vector<Step> steps_;
+  std::vector<HeadOut> heads_;
+  std::vector<void*> allocs_;
+  std::vector<void*> pinned_;
+  std::vector<std::unique_ptr<cvmk_conv_plan, void (*)(void*)>> plans_;
+  size_t device_bytes_ = 0;
+  // input staging
+  void* in_host_ = nullptr;
+  void* in_dev_ = nullptr;
+  size_t in_bytes_ = 0;
+  int32_t* status_dev_ = nullptr;
+  int32_t* status_host_ = nullptr;
+  cudaGraphExec_t graph_exec_ = nullptr;
+  bool use_graph_ = true;
+
+  void* dalloc(size_t bytes);
+  void Enqueue(cudaStream_t s);
+  friend struct Lowering;
+};
+
+}  // namespace cvm

@@ -1,0 +1,186 @@
+// conv2d on CUDA cores: grouped / depthwise convolutions and the shapes the tensor-core kernel
+// does not take (channel counts that are not a multiple of 32, e.g. a 3-channel stem).
+//
+// Reproduces groupwise_conv2d (src/runtime/cpu/ops/ops.cc:333-366) for groups > 1 and the
+// im2col + matrix_mul path (:204-246, :148-200, :368-456) for groups = 1.  Accumulation is int32
+// and exact, so the summation order is free.
+#include <cuda_runtime.h>
+#include <string.h>
+#include "common.cuh"
+
+namespace cvmk {
+namespace {
+
+struct DirectParams {
+  const void* x; const int8_t* w; void* y;
+  int xd, yd, narrow_x;
+  int N, H, W, C, OC, KH, KW, OH, OW, groups;
+  int sh, sw, ph, pw, dh, dw;
+  int64_t total;
+  DevChain chain;
+};
+
+__device__ __forceinline__ void store_one(void* y, int yd, int64_t i, int32_t v) {
+  if (yd == CVMK_I8) reinterpret_cast<int8_t*>(y)[i] = (int8_t)v;
+  else reinterpret_cast<int32_t*>(y)[i] = v;
+}
+
+// One thread per output element; consecutive threads walk the output channels of one pixel, so
+// activation reads are warp-broadcast and weight reads are contiguous per thread.
+template <int XD>
+__global__ void __launch_bounds__(256) conv_direct_kernel(const __grid_constant__ DirectParams p) {
+  const int icg = p.C / p.groups;
+  const int ocg = p.OC / p.groups;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+    const int oc = (int)(i % p.OC);
+    int64_t pix = i / p.OC;
+    const int ox = (int)(pix % p.OW); pix /= p.OW;
+    const int oy = (int)(pix % p.OH);
+    const int n = (int)(pix / p.OH);
+    const int ic0 = (oc / ocg) * icg;
+    int32_t acc = 0;
+    for (int fy = 0; fy < p.KH; ++fy) {
+      const int iy = oy * p.sh + fy * p.dh - p.ph;
+      if (iy < 0 || iy >= p.H) continue;
+      for (int fx = 0; fx < p.KW; ++fx) {
+        const int ix = ox * p.sw + fx * p.dw - p.pw;
+        if (ix < 0 || ix >= p.W) continue;
+        const int64_t xb = (((int64_t)n * p.H + iy) * p.W + ix) * p.C + ic0;
+        const int8_t* wp = p.w + (((int64_t)oc * p.KH + fy) * p.KW + fx) * icg;
+        if (XD == CVMK_I8) {
+          const int8_t* xp = reinterpret_cast<const int8_t*>(p.x) + xb;
+          int ic = 0;
+          if (((reinterpret_cast<uintptr_t>(xp) | reinterpret_cast<uintptr_t>(wp)) & 3) == 0) {
+            for (; ic + 4 <= icg; ic += 4)
+              acc = __dp4a(*reinterpret_cast<const int*>(xp + ic), *reinterpret_cast<const int*>(wp + ic), acc);
+          }
+          for (; ic < icg; ++ic) acc += (int32_t)xp[ic] * (int32_t)wp[ic];
+        } else {
+          const int32_t* xp = reinterpret_cast<const int32_t*>(p.x) + xb;
+          if (p.narrow_x) {
+            for (int ic = 0; ic < icg; ++ic) acc += (int32_t)(int8_t)xp[ic] * (int32_t)wp[ic];
+          } else {
+            for (int ic = 0; ic < icg; ++ic)
+              acc = (int32_t)((uint32_t)acc + (uint32_t)xp[ic] * (uint32_t)(int32_t)wp[ic]);
+          }
+        }
+      }
+    }
+    int32_t v[1] = {acc};
+    apply_chain<1>(p.chain, v, (size_t)i, oc);
+    store_one(p.y, p.yd, i, v[0]);
+  }
+}
+
+// Depthwise, int8 NHWC, channels a multiple of 16: one thread owns 16 channels of PX consecutive
+// output pixels of a row.  Weights are [KH, KW, C]; the per-channel products come from byte
+// extraction of the packed words.
+template <int PX>
+__global__ void __launch_bounds__(128) depthwise_kernel(const __grid_constant__ DirectParams p) {
+  const int cvec = p.C / 16;
+  const int oxg = (p.OW + PX - 1) / PX;
+  const int64_t total = (int64_t)p.N * p.OH * oxg * cvec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int cv = (int)(i % cvec);
+    int64_t r = i / cvec;
+    const int ox0 = (int)(r % oxg) * PX; r /= oxg;
+    const int oy = (int)(r % p.OH);
+    const int n = (int)(r / p.OH);
+    int32_t acc[PX][16];
+#pragma unroll
+    for (int q = 0; q < PX; ++q)
+#pragma unroll
+      for (int k = 0; k < 16; ++k) acc[q][k] = 0;
+    for (int fy = 0; fy < p.KH; ++fy) {
+      const int iy = oy * p.sh + fy * p.dh - p.ph;
+      if (iy < 0 || iy >= p.H) continue;
+      for (int fx = 0; fx < p.KW; ++fx) {
+        const int4 wv = __ldg(reinterpret_cast<const int4*>(p.w + ((int64_t)fy * p.KW + fx) * p.C) + cv);
+        const int ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int q = 0; q < PX; ++q) {
+          const int ix = (ox0 + q) * p.sw + fx * p.dw - p.pw;
+          if (ix < 0 || ix >= p.W || ox0 + q >= p.OW) continue;
+          const int4 xv = __ldg(reinterpret_cast<const int4*>(reinterpret_cast<const int8_t*>(p.x) +
+                                                                (((int64_t)n * p.H + iy) * p.W + ix) * p.C) + cv);
+          const int xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const int32_t a = (int32_t)(int8_t)(xw[k >> 2] >> ((k & 3) * 8));
+            const int32_t b = (int32_t)(int8_t)(ww[k >> 2] >> ((k & 3) * 8));
+            acc[q][k] += a * b;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < PX; ++q) {
+      if (ox0 + q >= p.OW) continue;
+      const int64_t lin = ((((int64_t)n * p.OH + oy) * p.OW + ox0 + q) * p.C) + cv * 16;
+      apply_chain<16>(p.chain, acc[q], (size_t)lin, cv * 16);
+      if (p.yd == CVMK_I8) {
+        int4 o;
+        o.x = (int)pack4(acc[q][0], acc[q][1], acc[q][2], acc[q][3]);
+        o.y = (int)pack4(acc[q][4], acc[q][5], acc[q][6], acc[q][7]);
+        o.z = (int)pack4(acc[q][8], acc[q][9], acc[q][10], acc[q][11]);
+        o.w = (int)pack4(acc[q][12], acc[q][13], acc[q][14], acc[q][15]);
+        *reinterpret_cast<int4*>(reinterpret_cast<int8_t*>(p.y) + lin) = o;
+      } else {
+        int4* dst = reinterpret_cast<int4*>(reinterpret_cast<int32_t*>(p.y) + lin);
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          dst[g] = make_int4(acc[q][4 * g], acc[q][4 * g + 1], acc[q][4 * g + 2], acc[q][4 * g + 3]);
+      }
+    }
+  }
+}
+
+int grid_sized(int64_t work, int threads) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int64_t blocks = (work + threads - 1) / threads;
+  if (blocks < 1) blocks = 1;
+  const int64_t cap = (int64_t)sms * 16;
+  if (blocks > cap) blocks = cap;
+  else if (blocks > sms) blocks = (blocks + sms - 1) / sms * sms;
+  return (int)blocks;
+}
+
+}  // namespace
+}  // namespace cvmk
+
+using namespace cvmk;
+
+extern "C" int cvmk_conv2d_direct(const cvmk_conv_direct_desc* d, cvmk_stream_t stream) {
+  if (!d || !d->x || !d->w || !d->y || d->groups < 1 || d->C % d->groups || d->OC % d->groups) {
+    set_error("conv2d_direct: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  DirectParams p;
+  memset(&p, 0, sizeof(p));
+  p.x = d->x; p.w = d->w; p.y = d->y;
+  p.xd = d->x_dtype; p.yd = d->y_dtype; p.narrow_x = d->narrow_x;
+  p.N = d->N; p.H = d->H; p.W = d->W; p.C = d->C; p.OC = d->OC; p.KH = d->KH; p.KW = d->KW;
+  p.OH = d->OH; p.OW = d->OW; p.groups = d->groups;
+  p.sh = d->stride_h; p.sw = d->stride_w; p.ph = d->pad_h; p.pw = d->pad_w; p.dh = d->dil_h; p.dw = d->dil_w;
+  p.total = (int64_t)d->N * d->OH * d->OW * d->OC;
+  int rc = lower_chain(d->ep, &p.chain);
+  if (rc != CVMK_OK) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (d->depthwise) {
+    if (d->groups != d->C || d->OC != d->C || d->C % 16 || d->x_dtype != CVMK_I8 ||
+        ((uintptr_t)d->x & 15) || ((uintptr_t)d->w & 15) || ((uintptr_t)d->y & 15)) {
+      set_error("conv2d_direct: depthwise path needs int8 NHWC, C %% 16 == 0, 16-byte aligned operands");
+      return CVMK_ERR_UNSUPPORTED;
+    }
+    const int64_t work = (int64_t)d->N * d->OH * ((d->OW + 3) / 4) * (d->C / 16);
+    depthwise_kernel<4><<<grid_sized(work, 128), 128, 0, s>>>(p);
+    return check_cuda(cudaGetLastError(), "depthwise_kernel launch");
+  }
+  if (d->x_dtype == CVMK_I8) conv_direct_kernel<CVMK_I8><<<grid_sized(p.total, 256), 256, 0, s>>>(p);
+  else conv_direct_kernel<CVMK_I32><<<grid_sized(p.total, 256), 256, 0, s>>>(p);
+  return check_cuda(cudaGetLastError(), "conv_direct_kernel launch");
+}

@@ -532,7 +532,10 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   int rc = lower_chain(d.ep, &p.chain);
   if (rc != CVMK_OK) return rc;
 
-  static bool attr_set = false;
+  static bool attr_set_dev[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& attr_set = attr_set_dev[dev & 63];
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_BUDGET + 2048);

@@ -1,0 +1,398 @@
+// Bandwidth-bound operators: element chains, strided copies / broadcasts, reductions, max pooling.
+// All are coalesced grid-stride kernels sized to the SM count; the int8 paths move 16 bytes per
+// thread per access.
+#include <cuda_runtime.h>
+#include <string.h>
+#include "common.cuh"
+
+namespace cvmk {
+namespace {
+
+int sm_count() {
+  static thread_local int cached_dev = -1, cached = 148;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != cached_dev) {
+    cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+    cached_dev = dev;
+  }
+  return cached;
+}
+
+// Grid for a grid-stride loop over `work` items with `threads` per block: whole multiples of the
+// SM count, at most 8 blocks per SM.
+int grid_for(int64_t work, int threads) {
+  const int sms = sm_count();
+  int64_t blocks = (work + threads - 1) / threads;
+  if (blocks < 1) blocks = 1;
+  const int64_t cap = (int64_t)sms * 8;
+  if (blocks > cap) blocks = cap;
+  else if (blocks > sms) blocks = (blocks + sms - 1) / sms * sms;
+  return (int)blocks;
+}
+
+__device__ __forceinline__ void unpack16(const int4& raw, int32_t* v) {
+  const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int k = 0; k < 16; ++k) v[k] = (int32_t)(int8_t)(w[k >> 2] >> ((k & 3) * 8));
+}
+__device__ __forceinline__ int4 pack16(const int32_t* v) {
+  int4 r;
+  r.x = (int)pack4(v[0], v[1], v[2], v[3]);
+  r.y = (int)pack4(v[4], v[5], v[6], v[7]);
+  r.z = (int)pack4(v[8], v[9], v[10], v[11]);
+  r.w = (int)pack4(v[12], v[13], v[14], v[15]);
+  return r;
+}
+
+// y = chain(x), 16 elements per thread per step.
+template <int XD, int YD>
+__global__ void __launch_bounds__(256) elemwise_kernel(const void* __restrict__ x, void* __restrict__ y,
+                                                       int64_t n, const __grid_constant__ DevChain chain) {
+  const int64_t nvec = n / 16;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    int32_t v[16];
+    if (XD == CVMK_I8) {
+      unpack16(__ldg(reinterpret_cast<const int4*>(x) + i), v);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        int4 r = __ldg(reinterpret_cast<const int4*>(x) + i * 4 + q);
+        v[4 * q] = r.x; v[4 * q + 1] = r.y; v[4 * q + 2] = r.z; v[4 * q + 3] = r.w;
+      }
+    }
+    apply_chain<16>(chain, v, (size_t)i * 16, 0, 0);
+    if (YD == CVMK_I8) {
+      reinterpret_cast<int4*>(y)[i] = pack16(v);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        reinterpret_cast<int4*>(y)[i * 4 + q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
+  }
+  // tail (n % 16 elements)
+  const int64_t tail0 = nvec * 16;
+  for (int64_t i = tail0 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    int32_t v[1];
+    v[0] = XD == CVMK_I8 ? (int32_t) reinterpret_cast<const int8_t*>(x)[i] : reinterpret_cast<const int32_t*>(x)[i];
+    apply_chain<1>(chain, v, (size_t)i, 0, 0);
+    if (YD == CVMK_I8) reinterpret_cast<int8_t*>(y)[i] = (int8_t)v[0];
+    else reinterpret_cast<int32_t*>(y)[i] = v[0];
+  }
+}
+
+struct StridedParams {
+  int op, ndim;
+  int64_t total;
+  int64_t extent[6];
+  int64_t as[6], bs[6], ys[6];
+  const void* a; const void* b; void* y;
+  int ad, bd, yd;
+  int64_t a_off, b_off, y_off;
+  DevChain chain;
+};
+
+__device__ __forceinline__ int32_t load_elem(const void* p, int dt, int64_t off) {
+  return dt == CVMK_I8 ? (int32_t) reinterpret_cast<const int8_t*>(p)[off]
+                       : reinterpret_cast<const int32_t*>(p)[off];
+}
+
+__global__ void __launch_bounds__(256) strided_kernel(const __grid_constant__ StridedParams p) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+    int64_t rem = i, ao = p.a_off, bo = p.b_off, yo = p.y_off;
+#pragma unroll
+    for (int k = 5; k >= 0; --k) {
+      if (k < p.ndim) {
+        const int64_t c = rem % p.extent[k];
+        rem /= p.extent[k];
+        ao += c * p.as[k];
+        bo += c * p.bs[k];
+        yo += c * p.ys[k];
+      }
+    }
+    int32_t v[1];
+    const int32_t a = load_elem(p.a, p.ad, ao);
+    if (p.op == CVMK_OP_COPY) {
+      v[0] = a;
+    } else {
+      const int32_t b = load_elem(p.b, p.bd, bo);
+      switch (p.op) {
+        case CVMK_OP_ADD: v[0] = (int32_t)((uint32_t)a + (uint32_t)b); break;
+        case CVMK_OP_SUB: v[0] = (int32_t)((uint32_t)a - (uint32_t)b); break;
+        case CVMK_OP_MUL: v[0] = (int32_t)((uint32_t)a * (uint32_t)b); break;
+        case CVMK_OP_MAX: v[0] = a > b ? a : b; break;
+        case CVMK_OP_DIV: v[0] = b == 0 ? 0 : (b == -1 ? (int32_t)(0u - (uint32_t)a) : a / b); break;
+        default: v[0] = a > b ? 1 : 0; break;
+      }
+    }
+    apply_chain<1>(p.chain, v, (size_t)yo, 0, 0);
+    if (p.yd == CVMK_I8) reinterpret_cast<int8_t*>(p.y)[yo] = (int8_t)v[0];
+    else reinterpret_cast<int32_t*>(p.y)[yo] = v[0];
+  }
+}
+
+// COPY fast path: the innermost extent is contiguous in a and y, dtypes equal, everything 16-byte
+// aligned: move 16-byte vectors.
+struct StridedVecParams {
+  int ndim;
+  int64_t total_vec;
+  int64_t extent[6];   // innermost extent counted in vectors
+  int64_t as[6], ys[6];  // strides in vectors (innermost = 1)
+  const int4* a; int4* y;
+};
+__global__ void __launch_bounds__(256) strided_vec_kernel(const __grid_constant__ StridedVecParams p) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total_vec; i += stride) {
+    int64_t rem = i, ao = 0, yo = 0;
+#pragma unroll
+    for (int k = 5; k >= 0; --k) {
+      if (k < p.ndim) {
+        const int64_t c = rem % p.extent[k];
+        rem /= p.extent[k];
+        ao += c * p.as[k];
+        yo += c * p.ys[k];
+      }
+    }
+    p.y[yo] = __ldg(p.a + ao);
+  }
+}
+
+struct ReduceParams {
+  int is_max, init_zero, n_keep, n_red;
+  int64_t total, red_total;
+  int64_t ke[6], ks[6], re[6], rs[6];
+  const void* x; void* y;
+  int xd, yd;
+  DevChain chain;
+};
+__global__ void __launch_bounds__(256) reduce_kernel(const __grid_constant__ ReduceParams p) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+    int64_t rem = i, base = 0;
+#pragma unroll
+    for (int k = 5; k >= 0; --k) {
+      if (k < p.n_keep) {
+        base += (rem % p.ke[k]) * p.ks[k];
+        rem /= p.ke[k];
+      }
+    }
+    int32_t acc = p.init_zero ? 0 : load_elem(p.x, p.xd, base);
+    for (int64_t r = p.init_zero ? 0 : 1; r < p.red_total; ++r) {
+      int64_t rr = r, off = base;
+#pragma unroll
+      for (int k = 5; k >= 0; --k) {
+        if (k < p.n_red) {
+          off += (rr % p.re[k]) * p.rs[k];
+          rr /= p.re[k];
+        }
+      }
+      const int32_t val = load_elem(p.x, p.xd, off);
+      if (p.is_max) acc = acc < val ? val : acc;
+      else acc = (int32_t)((uint32_t)acc + (uint32_t)val);
+    }
+    int32_t v[1] = {acc};
+    apply_chain<1>(p.chain, v, (size_t)i, 0, 0);
+    if (p.yd == CVMK_I8) reinterpret_cast<int8_t*>(p.y)[i] = (int8_t)v[0];
+    else reinterpret_cast<int32_t*>(p.y)[i] = v[0];
+  }
+}
+
+// max_pool2d, NHWC.  int8: one thread owns 16 channels of one output pixel (vmax4 on packed
+// bytes); int32: 4 channels.  Taps outside the image are skipped, which equals a max with INT_MIN
+// because the reference guarantees at least one tap inside (pad < pool size).
+struct PoolParams {
+  const void* x; void* y;
+  int N, H, W, C, OH, OW, KH, KW, sh, sw, ph, pw;
+  int64_t total;  // output vectors
+  int cvec;       // vectors per pixel
+};
+template <int DT>
+__global__ void __launch_bounds__(256) pool_vec_kernel(const __grid_constant__ PoolParams p) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+    const int cv = (int)(i % p.cvec);
+    int64_t pix = i / p.cvec;
+    const int ox = (int)(pix % p.OW); pix /= p.OW;
+    const int oy = (int)(pix % p.OH);
+    const int n = (int)(pix / p.OH);
+    int4 m;
+    if (DT == CVMK_I8) m = make_int4(0x80808080, 0x80808080, 0x80808080, 0x80808080);
+    else m = make_int4(INT32_MIN, INT32_MIN, INT32_MIN, INT32_MIN);
+    for (int fy = 0; fy < p.KH; ++fy) {
+      const int iy = oy * p.sh + fy - p.ph;
+      if (iy < 0 || iy >= p.H) continue;
+      for (int fx = 0; fx < p.KW; ++fx) {
+        const int ix = ox * p.sw + fx - p.pw;
+        if (ix < 0 || ix >= p.W) continue;
+        const int4 v = __ldg(reinterpret_cast<const int4*>(p.x) + (((int64_t)n * p.H + iy) * p.W + ix) * p.cvec + cv);
+        if (DT == CVMK_I8) {
+          m.x = (int)__vmaxs4((unsigned)m.x, (unsigned)v.x); m.y = (int)__vmaxs4((unsigned)m.y, (unsigned)v.y);
+          m.z = (int)__vmaxs4((unsigned)m.z, (unsigned)v.z); m.w = (int)__vmaxs4((unsigned)m.w, (unsigned)v.w);
+        } else {
+          m.x = max(m.x, v.x); m.y = max(m.y, v.y); m.z = max(m.z, v.z); m.w = max(m.w, v.w);
+        }
+      }
+    }
+    reinterpret_cast<int4*>(p.y)[i] = m;
+  }
+}
+// Any channel count: one thread per output element.
+__global__ void __launch_bounds__(256) pool_scalar_kernel(const __grid_constant__ PoolParams p, int dt) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t total = (int64_t)p.N * p.OH * p.OW * p.C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % p.C);
+    int64_t pix = i / p.C;
+    const int ox = (int)(pix % p.OW); pix /= p.OW;
+    const int oy = (int)(pix % p.OH);
+    const int n = (int)(pix / p.OH);
+    int32_t m = INT32_MIN;
+    for (int fy = 0; fy < p.KH; ++fy) {
+      const int iy = oy * p.sh + fy - p.ph;
+      if (iy < 0 || iy >= p.H) continue;
+      for (int fx = 0; fx < p.KW; ++fx) {
+        const int ix = ox * p.sw + fx - p.pw;
+        if (ix < 0 || ix >= p.W) continue;
+        m = max(m, load_elem(p.x, dt, (((int64_t)n * p.H + iy) * p.W + ix) * p.C + c));
+      }
+    }
+    if (dt == CVMK_I8) reinterpret_cast<int8_t*>(p.y)[i] = (int8_t)m;
+    else reinterpret_cast<int32_t*>(p.y)[i] = m;
+  }
+}
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+}  // namespace cvmk
+
+using namespace cvmk;
+
+extern "C" int cvmk_elemwise(const void* x, int x_dtype, void* y, int y_dtype, int64_t n,
+                             const cvmk_epilogue* ep, cvmk_stream_t stream) {
+  if (!x || !y || n < 0 || (x_dtype != CVMK_I8 && x_dtype != CVMK_I32) ||
+      (y_dtype != CVMK_I8 && y_dtype != CVMK_I32)) {
+    set_error("elemwise: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  if (n == 0) return CVMK_OK;
+  DevChain chain;
+  cvmk_epilogue none;
+  memset(&none, 0, sizeof(none));
+  int rc = lower_chain(ep ? *ep : none, &chain);
+  if (rc != CVMK_OK) return rc;
+  if (!aligned16(x) || !aligned16(y)) {
+    // Unaligned views go through the strided kernel (one element per thread).
+    cvmk_strided_desc d;
+    memset(&d, 0, sizeof(d));
+    d.op = CVMK_OP_COPY; d.ndim = 1; d.extent[0] = n;
+    d.a = x; d.a_dtype = x_dtype; d.a_stride[0] = 1;
+    d.y = y; d.y_dtype = y_dtype; d.y_stride[0] = 1;
+    if (ep) d.ep = *ep;
+    return cvmk_strided(&d, stream);
+  }
+  const int threads = 256;
+  const int grid = grid_for((n + 15) / 16, threads);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (x_dtype == CVMK_I8 && y_dtype == CVMK_I8) elemwise_kernel<CVMK_I8, CVMK_I8><<<grid, threads, 0, s>>>(x, y, n, chain);
+  else if (x_dtype == CVMK_I8) elemwise_kernel<CVMK_I8, CVMK_I32><<<grid, threads, 0, s>>>(x, y, n, chain);
+  else if (y_dtype == CVMK_I8) elemwise_kernel<CVMK_I32, CVMK_I8><<<grid, threads, 0, s>>>(x, y, n, chain);
+  else elemwise_kernel<CVMK_I32, CVMK_I32><<<grid, threads, 0, s>>>(x, y, n, chain);
+  return check_cuda(cudaGetLastError(), "elemwise_kernel launch");
+}
+
+extern "C" int cvmk_strided(const cvmk_strided_desc* d, cvmk_stream_t stream) {
+  if (!d || !d->a || !d->y || d->ndim < 1 || d->ndim > 6 || (d->op != CVMK_OP_COPY && !d->b)) {
+    set_error("strided: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  int64_t total = 1;
+  for (int k = 0; k < d->ndim; ++k) {
+    if (d->extent[k] < 1) { set_error("strided: empty extent"); return CVMK_ERR_ARG; }
+    total *= d->extent[k];
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = 256;
+  const int in = d->ndim - 1;
+  const int es = d->a_dtype;
+  const int vec = 16 / es;
+  bool fast = d->op == CVMK_OP_COPY && d->ep.n == 0 && d->a_dtype == d->y_dtype &&
+              d->a_stride[in] == 1 && d->y_stride[in] == 1 && d->extent[in] % vec == 0 &&
+              d->a_off % vec == 0 && d->y_off % vec == 0 && aligned16(d->a) && aligned16(d->y);
+  for (int k = 0; fast && k < in; ++k) fast = d->a_stride[k] % vec == 0 && d->y_stride[k] % vec == 0;
+  if (fast) {
+    StridedVecParams p;
+    memset(&p, 0, sizeof(p));
+    p.ndim = d->ndim;
+    p.total_vec = total / vec;
+    for (int k = 0; k < d->ndim; ++k) {
+      p.extent[k] = k == in ? d->extent[k] / vec : d->extent[k];
+      p.as[k] = k == in ? 1 : d->a_stride[k] / vec;
+      p.ys[k] = k == in ? 1 : d->y_stride[k] / vec;
+    }
+    p.a = reinterpret_cast<const int4*>(reinterpret_cast<const char*>(d->a) + d->a_off * es);
+    p.y = reinterpret_cast<int4*>(reinterpret_cast<char*>(d->y) + d->y_off * es);
+    strided_vec_kernel<<<grid_for(p.total_vec, threads), threads, 0, s>>>(p);
+    return check_cuda(cudaGetLastError(), "strided_vec_kernel launch");
+  }
+  StridedParams p;
+  memset(&p, 0, sizeof(p));
+  p.op = d->op; p.ndim = d->ndim; p.total = total;
+  for (int k = 0; k < d->ndim; ++k) {
+    p.extent[k] = d->extent[k];
+    p.as[k] = d->a_stride[k]; p.bs[k] = d->b_stride[k]; p.ys[k] = d->y_stride[k];
+  }
+  p.a = d->a; p.b = d->b; p.y = d->y;
+  p.ad = d->a_dtype; p.bd = d->b_dtype; p.yd = d->y_dtype;
+  p.a_off = d->a_off; p.b_off = d->b_off; p.y_off = d->y_off;
+  int rc = lower_chain(d->ep, &p.chain);
+  if (rc != CVMK_OK) return rc;
+  strided_kernel<<<grid_for(total, threads), threads, 0, s>>>(p);
+  return check_cuda(cudaGetLastError(), "strided_kernel launch");
+}
+
+extern "C" int cvmk_reduce(const cvmk_reduce_desc* d, cvmk_stream_t stream) {
+  if (!d || !d->x || !d->y || d->n_keep < 0 || d->n_keep > 6 || d->n_red < 0 || d->n_red > 6) {
+    set_error("reduce: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  ReduceParams p;
+  memset(&p, 0, sizeof(p));
+  p.is_max = d->is_max; p.init_zero = d->init_zero; p.n_keep = d->n_keep; p.n_red = d->n_red;
+  p.total = 1; p.red_total = 1;
+  for (int k = 0; k < d->n_keep; ++k) { p.ke[k] = d->keep_extent[k]; p.ks[k] = d->keep_stride[k]; p.total *= p.ke[k]; }
+  for (int k = 0; k < d->n_red; ++k) { p.re[k] = d->red_extent[k]; p.rs[k] = d->red_stride[k]; p.red_total *= p.re[k]; }
+  p.x = d->x; p.y = d->y; p.xd = d->x_dtype; p.yd = d->y_dtype;
+  int rc = lower_chain(d->ep, &p.chain);
+  if (rc != CVMK_OK) return rc;
+  const int threads = 256;
+  reduce_kernel<<<grid_for(p.total, threads), threads, 0, (cudaStream_t)stream>>>(p);
+  return check_cuda(cudaGetLastError(), "reduce_kernel launch");
+}
+
+extern "C" int cvmk_max_pool2d(const cvmk_pool_desc* d, cvmk_stream_t stream) {
+  if (!d || !d->x || !d->y || (d->dtype != CVMK_I8 && d->dtype != CVMK_I32)) {
+    set_error("max_pool2d: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  PoolParams p;
+  p.x = d->x; p.y = d->y;
+  p.N = d->N; p.H = d->H; p.W = d->W; p.C = d->C; p.OH = d->OH; p.OW = d->OW;
+  p.KH = d->KH; p.KW = d->KW; p.sh = d->stride_h; p.sw = d->stride_w; p.ph = d->pad_h; p.pw = d->pad_w;
+  const int vec = 16 / d->dtype;
+  const int threads = 256;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (d->C % vec == 0 && aligned16(d->x) && aligned16(d->y)) {
+    p.cvec = d->C / vec;
+    p.total = (int64_t)d->N * d->OH * d->OW * p.cvec;
+    if (d->dtype == CVMK_I8) pool_vec_kernel<CVMK_I8><<<grid_for(p.total, threads), threads, 0, s>>>(p);
+    else pool_vec_kernel<CVMK_I32><<<grid_for(p.total, threads), threads, 0, s>>>(p);
+  } else {
+    p.cvec = 0;
+    p.total = (int64_t)d->N * d->OH * d->OW * d->C;
+    pool_scalar_kernel<<<grid_for(p.total, threads), threads, 0, s>>>(p, d->dtype);
+  }
+  return check_cuda(cudaGetLastError(), "max_pool2d launch");
+}

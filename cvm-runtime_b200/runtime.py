@@ -1,0 +1,149 @@
+"""ctypes binding of libcvm_runtime.so, mirroring the reference's Python binding
+(python/cvm/_ctypes/runtime.py:12-159): same function names, same argument meaning, a raised
+error for every non-zero status.  The library is loaded from this directory; there is no
+fallback when it (or a GPU) is missing.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcvm_runtime.so")
+
+SUCCEED, ERROR_LOGIC, ERROR_RUNTIME = 0, 1, 2
+
+API_SYMBOLS = [
+    "CVMAPILoadModel", "CVMAPIFreeModel", "CVMAPIInference", "CVMAPIGetVersion",
+    "CVMAPIGetPreprocessMethod", "CVMAPIGetInputLength", "CVMAPIGetOutputLength",
+    "CVMAPIGetInputTypeSize", "CVMAPIGetOutputTypeSize", "CVMAPIGetStorageSize",
+    "CVMAPIGetGasFromModel", "CVMAPIGetGasFromGraphFile",
+]
+KERNEL_SYMBOLS = [
+    "cvmk_conv2d_tc_supported", "cvmk_conv2d_tc_prepare", "cvmk_conv2d_tc_launch", "cvmk_elemwise",
+    "cvmk_strided", "cvmk_reduce", "cvmk_max_pool2d", "cvmk_conv2d_direct", "cvmk_get_valid_counts",
+    "cvmk_nms_scratch_bytes", "cvmk_non_max_suppression", "cvmk_last_error",
+]
+
+
+class CVMError(RuntimeError):
+    """A C-ABI call returned ERROR_LOGIC (1) or ERROR_RUNTIME (2)."""
+
+    def __init__(self, status, what):
+        super().__init__("%s returned status %d" % (what, status))
+        self.status = status
+
+
+_LIB = None
+
+
+def lib():
+    """The loaded shared library (raises if it has not been built)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise OSError("%s not found: build it with `python cvm-runtime_b200/build.py`" % LIB_PATH)
+        _LIB = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+        _LIB.cvmk_last_error.restype = ctypes.c_char_p
+        _LIB.cvmk_nms_scratch_bytes.restype = ctypes.c_int64
+    return _LIB
+
+
+def check_call(status, what="CVMAPI call"):
+    if status != SUCCEED:
+        raise CVMError(status, what)
+
+
+NetworkHandle = ctypes.c_void_p
+
+
+def CVMAPILoadModel(json_str, param_bytes, device_id=0, device_type=1):
+    """Load a model from its graph JSON and params blob onto GPU `device_id`."""
+    net = NetworkHandle()
+    if isinstance(json_str, str):
+        json_str = json_str.encode("utf-8")
+    check_call(lib().CVMAPILoadModel(
+        ctypes.c_char_p(json_str), ctypes.c_int(len(json_str)),
+        ctypes.c_char_p(param_bytes), ctypes.c_int(len(param_bytes)),
+        ctypes.byref(net), ctypes.c_int(device_type), ctypes.c_int(device_id)), "CVMAPILoadModel")
+    return net
+
+
+def CVMAPIFreeModel(net):
+    check_call(lib().CVMAPIFreeModel(net), "CVMAPIFreeModel")
+
+
+def _get_ull(name, net):
+    size = ctypes.c_ulonglong()
+    check_call(getattr(lib(), name)(net, ctypes.byref(size)), name)
+    return size.value
+
+
+def CVMAPIGetInputLength(net):
+    return _get_ull("CVMAPIGetInputLength", net)
+
+
+def CVMAPIGetInputTypeSize(net):
+    return _get_ull("CVMAPIGetInputTypeSize", net)
+
+
+def CVMAPIGetOutputLength(net):
+    return _get_ull("CVMAPIGetOutputLength", net)
+
+
+def CVMAPIGetOutputTypeSize(net):
+    return _get_ull("CVMAPIGetOutputTypeSize", net)
+
+
+def CVMAPIGetStorageSize(net):
+    return _get_ull("CVMAPIGetStorageSize", net)
+
+
+def CVMAPIGetGasFromModel(net):
+    return _get_ull("CVMAPIGetGasFromModel", net)
+
+
+def CVMAPIGetGasFromGraphFile(json_str):
+    if isinstance(json_str, str):
+        json_str = json_str.encode("utf-8")
+    gas = ctypes.c_ulonglong()
+    check_call(lib().CVMAPIGetGasFromGraphFile(ctypes.c_char_p(json_str), ctypes.byref(gas)),
+               "CVMAPIGetGasFromGraphFile")
+    return gas.value
+
+
+def CVMAPIGetVersion(net):
+    buf = ctypes.create_string_buffer(64)
+    check_call(lib().CVMAPIGetVersion(net, buf), "CVMAPIGetVersion")
+    return buf.value.decode()
+
+
+def CVMAPIGetPreprocessMethod(net):
+    buf = ctypes.create_string_buffer(64)
+    check_call(lib().CVMAPIGetPreprocessMethod(net, buf), "CVMAPIGetPreprocessMethod")
+    return buf.value.decode()
+
+
+def inference_bytes(net, input_data, out=None):
+    """CVMAPIInference on raw bytes (or a contiguous numpy array); returns the output bytes as a
+    numpy uint8 array (written into `out` when given)."""
+    if isinstance(input_data, np.ndarray):
+        arr = np.ascontiguousarray(input_data)
+        in_ptr = arr.ctypes.data_as(ctypes.c_char_p)
+        in_len = arr.nbytes
+    else:
+        arr = input_data
+        in_ptr = ctypes.c_char_p(input_data)
+        in_len = len(input_data)
+    if out is None:
+        out = np.empty(CVMAPIGetOutputLength(net), dtype=np.uint8)
+    check_call(lib().CVMAPIInference(net, in_ptr, ctypes.c_int(in_len),
+                                     out.ctypes.data_as(ctypes.c_char_p)), "CVMAPIInference")
+    return out
+
+
+def CVMAPIInference(net, input_data):
+    """Reference-compatible form: returns the outputs as a list of Python ints."""
+    raw = inference_bytes(net, input_data)
+    otype = CVMAPIGetOutputTypeSize(net)
+    return raw.view(np.int8 if otype == 1 else np.int32).astype(np.int64).tolist()

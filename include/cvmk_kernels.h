@@ -132,6 +132,109 @@ CVMK_API int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d);
 CVMK_API int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* plan);
 CVMK_API int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t stream);
 
+
+/* ------------------------------------------------------------------------------------------------
+ * y = chain(x) over n contiguous elements (any layout, x and y share it).
+ * Stand-alone form of relu (ops.cc:12-26), clip / cvm_clip / cvm_right_shift / cvm_left_shift
+ * (elemwise.cc:47-62, :88-193), abs / negative / cvm_precision (ops.cc:525-553, :632-642) and,
+ * through the chain's *_T steps, elemwise_add / elemwise_sub (elemwise.cc:8-45).
+ * ---------------------------------------------------------------------------------------------- */
+CVMK_API int cvmk_elemwise(const void* x, int x_dtype, void* y, int y_dtype, int64_t n,
+                           const cvmk_epilogue* ep, cvmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Strided element kernel: for every point c of an iteration space of up to 6 extents,
+ *     y[y_off + sum c_k * ys_k] = chain( op( a[a_off + sum c_k * as_k], b[b_off + sum c_k * bs_k] ) )
+ * Strides are in elements; a stride of 0 broadcasts.  With op = COPY (b unused) it is the layout
+ * converter (NCHW <-> NHWC, int8 <-> int32), flatten / reshape of a channels-last tensor
+ * (elemwise.cc:64-86), concatenate (ops.cc:567-602; one call per input), upsampling
+ * (ops.cc:958-989; iteration space N,H,s,W,s,C) and expand_dims / squeeze.  With a binary op it
+ * is broadcast_add/sub/mul/max/div/greater (cpu/ops/broadcast.cc:6-124).
+ * ---------------------------------------------------------------------------------------------- */
+enum { CVMK_OP_COPY = 0, CVMK_OP_ADD, CVMK_OP_SUB, CVMK_OP_MUL, CVMK_OP_MAX, CVMK_OP_DIV, CVMK_OP_GREATER };
+typedef struct {
+  int32_t op;
+  int32_t ndim;
+  int64_t extent[6];
+  const void* a; int32_t a_dtype; int32_t pad0; int64_t a_off; int64_t a_stride[6];
+  const void* b; int32_t b_dtype; int32_t pad1; int64_t b_off; int64_t b_stride[6];
+  void* y;       int32_t y_dtype; int32_t pad2; int64_t y_off; int64_t y_stride[6];
+  cvmk_epilogue ep;
+} cvmk_strided_desc;
+CVMK_API int cvmk_strided(const cvmk_strided_desc* d, cvmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * sum / max reduce (cpu/ops/reduce.cc:34-140).  Output point c (up to 6 kept extents, strides into
+ * x given per extent) reduces over up to 6 reduced extents.  init_zero = 1 reproduces the
+ * reduce-over-everything path, whose accumulator starts at 0 (reduce.cc:41-47); otherwise the
+ * accumulator starts at the first element (reduce.cc:90-100).  y is written contiguously.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t is_max;
+  int32_t init_zero;
+  int32_t n_keep, n_red;
+  int64_t keep_extent[6], keep_stride[6];
+  int64_t red_extent[6], red_stride[6];
+  const void* x; int32_t x_dtype; int32_t pad0;
+  void* y;       int32_t y_dtype; int32_t pad1;
+  cvmk_epilogue ep;
+} cvmk_reduce_desc;
+CVMK_API int cvmk_reduce(const cvmk_reduce_desc* d, cvmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * max_pool2d on channels-last tensors (cpu/ops/ops.cc:466-523): window max, taps outside the image
+ * count as INT32_MIN.  x: NHWC [N,H,W,C], y: NHWC [N,OH,OW,C], same dtype for both.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x; void* y; int32_t dtype;
+  int32_t N, H, W, C, OH, OW, KH, KW, stride_h, stride_w, pad_h, pad_w;
+} cvmk_pool_desc;
+CVMK_API int cvmk_max_pool2d(const cvmk_pool_desc* d, cvmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * conv2d on CUDA cores for the shapes the tensor-core path does not take: groups > 1
+ * (groupwise_conv2d, cpu/ops/ops.cc:333-366), depthwise, and small or odd channel counts.
+ *   x : NHWC [N,H,W,C], int8 or int32 (x_dtype)
+ *   w : int8 [OC, KH, KW, C/groups]   (depthwise = 1: int8 [KH, KW, C])
+ *   y : NHWC [N,OH,OW,OC] int8 or int32, chain applied (ADD_C carries the bias)
+ * With x_dtype = CVMK_I32 and narrow_x = 1 each input is truncated like static_cast<int8_t>
+ * (ops.cc:234), which is what the groups = 1 reference path does; the grouped path multiplies the
+ * int32 values as they are.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x; int32_t x_dtype; int32_t narrow_x;
+  const int8_t* w;
+  void* y; int32_t y_dtype;
+  int32_t N, H, W, C, OC, KH, KW, OH, OW, groups;
+  int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int32_t depthwise;
+  cvmk_epilogue ep;
+} cvmk_conv_direct_desc;
+CVMK_API int cvmk_conv2d_direct(const cvmk_conv_direct_desc* d, cvmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * get_valid_counts (cpu/ops/nms.cc:42-63): per batch keep rows with row[1] > score_threshold in
+ * their original order, write their number to valid_count[b], fill the remaining rows with -1.
+ * x, y: int32 [B, N, K]; valid_count: int32 [B].
+ * non_max_suppression (cpu/ops/nms.cc:65-140, iou :4-40), K = 6, corner boxes at columns 2..5,
+ * score at column 1, class id at column 0.  x is read only; `scratch` needs
+ * cvmk_nms_scratch_bytes(B, N) bytes (16-byte aligned) and is clobbered.
+ * ---------------------------------------------------------------------------------------------- */
+CVMK_API int cvmk_get_valid_counts(const int32_t* x, int32_t* y, int32_t* valid_count, int32_t B,
+                                   int32_t N, int32_t K, int32_t score_threshold,
+                                   cvmk_stream_t stream);
+typedef struct {
+  const int32_t* x;
+  const int32_t* valid_count;
+  int32_t* y;
+  int32_t B, N;
+  int32_t max_output_size, iou_threshold, top_k, force_suppress;
+  void* scratch;
+  int64_t scratch_bytes;
+} cvmk_nms_desc;
+CVMK_API int64_t cvmk_nms_scratch_bytes(int32_t B, int32_t N);
+CVMK_API int cvmk_non_max_suppression(const cvmk_nms_desc* d, cvmk_stream_t stream);
+
 /* Text of the last CUDA / argument error seen by a launcher on this thread. */
 CVMK_API const char* cvmk_last_error(void);
 
