@@ -267,7 +267,7 @@ struct Lowering {
       for (uint32_t nid = c->tail_nid + 1; nid < g.nodes.size() && consumer == UINT32_MAX; ++nid)
         for (const auto& e : g.nodes[nid].inputs)
           if (g.entry_id(e) == cur) { consumer = nid; break; }
-      if (consumer == UINT32_MAX) break;
+      if (consumer == UINT32_MAX || absorbed[consumer]) break;  // e.g. a join taken by its other branch
       cvmk_ep_step st;
       if (!node_as_step(consumer, cur, &st)) break;
       c->ep.s[c->ep.n++] = st;
