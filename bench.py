@@ -1,0 +1,338 @@
+"""Benchmark of the operator hot path: int8 ResNet-50 images/s through the C-ABI on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload resnet50|mobilenet|vgg19|conv_chain|ssd_tail] [--batch B]
+
+One step = one inference of the per-GPU batch (default: synthetic MRT-style quantized ResNet-50
+v1, batch 256).  With N > 1 (launched through torch.distributed.run) every rank holds its own
+weight replica and its own batch: no collective is on the data path, throughput scales weakly.
+
+Printed JSON (rank 0): `value` = images/s with the input resident in device memory (CUDA events
+around K kernel-only replays, max over ranks); `e2e` = images/s through CVMAPIInference with host
+buffers, upload and download inside the timed region; `roofline` for the dominant kernel (the
+tcgen05 convolution); `cpu_baseline` = the reference CPU runtime timed on this machine's cores.
+`--impl reference` times the reference's own CPU runtime (oracle/_ref) instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as ge  # noqa: E402
+
+METRIC = "int8 ResNet-50 images/s"
+UNITS = {"resnet50": "images/s", "mobilenet": "images/s", "vgg19": "images/s", "conv_chain": "images/s",
+         "ssd_tail": "boxes/s"}
+
+
+def make_workload(wl, name, batch):
+    if name == "resnet50":
+        return wl.resnet50(batch)
+    if name == "mobilenet":
+        return wl.mobilenet_v1(batch)
+    if name == "vgg19":
+        return wl.vgg19(batch)
+    if name == "conv_chain":
+        return wl.conv_chain(batch)
+    if name == "ssd_tail":
+        return wl.ssd_tail(batch)
+    raise SystemExit("unknown workload " + name)
+
+
+def units_per_step(name, batch, wl):
+    return batch * wl.SSD_ANCHORS if name == "ssd_tail" else batch
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([t.strip() for t in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def cpu_baseline(oracle, wl, workload, sample_batch, repeats=1):
+    """Reference CPU runtime (oracle/_ref, else the numpy port) on a bounded sample."""
+    js, pb, x = make_workload(wl, workload, sample_batch)
+    cores = os.cpu_count() or 1
+    if oracle.ref_lib.available():
+        os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+        m = oracle.ref_lib.RefModel(js, pb, 0)
+        if not m.loaded:
+            raise RuntimeError("reference refused the sample model")
+        m.infer(x)  # warm (first touch of the pool)
+        t0 = time.perf_counter()
+        for _ in range(repeats):
+            st, _ = m.infer(x)
+        dt = (time.perf_counter() - t0) / repeats
+        m.free()
+        kind = "reference"
+    else:
+        t0 = time.perf_counter()
+        for _ in range(repeats):
+            oracle.run_model(js, pb, x)
+        dt = (time.perf_counter() - t0) / repeats
+        kind = "port"
+        cores = 1
+    units = units_per_step(workload, sample_batch, wl)
+    return {"value": units / dt, "unit": UNITS[workload], "cores": cores, "kind": kind,
+            "sample": "%s batch %d, %d timed inference(s) after 1 warm-up, OpenMP threads = cores"
+                      % (workload, sample_batch, repeats), "seconds_per_step": dt}
+
+
+def run_reference(args, wl, oracle, rank, world):
+    if rank != 0:
+        return
+    sample_batch = {"resnet50": 8, "mobilenet": 16, "vgg19": 2, "conv_chain": 32, "ssd_tail": 8}[args.workload]
+    vals = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(oracle, wl, args.workload, sample_batch)
+        if i >= args.warmup:
+            vals.append(base["seconds_per_step"])
+    dt = sum(vals) / len(vals)
+    value = units_per_step(args.workload, sample_batch, wl) / dt
+    line = {
+        "impl": "reference", "metric": METRIC if args.workload == "resnet50" else args.workload,
+        "value": value, "unit": UNITS[args.workload], "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int32 storage, int8 products (reference CPU)", "data": "synthetic",
+        "config": {"workload": "%s batch %d per GPU" % (args.workload, args.batch),
+                   "sample": "each step = one batch-%d inference on the host cores" % sample_batch},
+        "cpu_baseline": {"value": value, "unit": UNITS[args.workload], "cores": base["cores"],
+                         "kind": base["kind"], "sample": base["sample"]},
+        "e2e": {"value": value, "unit": UNITS[args.workload], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="resnet50", choices=sorted(UNITS))
+    ap.add_argument("--batch", type=int, default=None, help="images per GPU (default 256; ssd_tail 64)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.batch is None:
+        args.batch = 64 if args.workload == "ssd_tail" else 256
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    pkg = ge.load_package()
+    wl, rt = pkg.workloads, pkg.runtime
+
+    if args.impl == "reference":
+        run_reference(args, wl, ge.load_oracle(), rank, world)
+        return
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if not dist:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    js, pb, x = make_workload(wl, args.workload, args.batch)
+    net = rt.CVMAPILoadModel(js, pb, local_rank)
+    out = np.empty(rt.CVMAPIGetOutputLength(net), dtype=np.uint8)
+    launches = rt.step_count(net)
+    units = units_per_step(args.workload, args.batch, wl)
+
+    # ---- end to end through the C-ABI (host buffers, upload + download inside the timed region)
+    for _ in range(args.warmup):
+        rt.inference_bytes(net, x, out)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        rt.inference_bytes(net, x, out)
+    torch.cuda.synchronize()
+    e2e_dt = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+
+    # ---- device-resident: CUDA events around K kernel-only replays, clocks sampled meanwhile
+    rt.replay_device(net, args.warmup)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    dev_ms = rt.replay_device(net, args.steps)
+    barrier()
+    if args.steps * dev_ms < 1500 and rank == 0:   # keep the region long enough for clock samples
+        pass
+    dev_ms = max_over_ranks(dev_ms)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- per-kernel attribution for the roofline (launch by launch, CUDA events in between)
+    roofline = None
+    if rank == 0:
+        agg = {}
+        reps = 3
+        for _ in range(reps):
+            for label, ms in rt.profile_steps(net, x):
+                kind = label[label.rfind("[") + 1:-1] if label.endswith("]") else label.split(":")[0]
+                a = agg.setdefault(kind, [0, 0.0])
+                a[0] += 1
+                a[1] += ms
+        total = sum(v[1] for v in agg.values())
+        kernels = {k: {"launches_per_step": v[0] // reps, "ms_per_step": v[1] / reps,
+                       "share": v[1] / total if total else 0.0} for k, v in agg.items()}
+        peaks = measured_peaks()
+        if "tc" in kernels:
+            tc_ops = tc_conv_ops(js)
+            tc_ms = kernels["tc"]["ms_per_step"]
+            achieved = tc_ops / (tc_ms * 1e-3) / 1e12
+            peak = 2.0 * peaks["bf16_sustained"]
+            roofline = {
+                "kernel": "conv_tc_kernel (tcgen05 kind::i8 implicit GEMM, all groups=1 conv2d + dense)",
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None,
+                "note": "int8 multiply-accumulates counted as 2 ops (TOP/s); peak = 2 x the %s sustained bf16 "
+                        "cuBLAS figure (%.1f), int8 dense rate being twice bf16; against 2 x burst (%.1f) the "
+                        "fraction is %.3f; launches_per_step=%d, avg launch %.1f us" % (
+                            peaks["source"], peaks["bf16_sustained"], peaks["bf16"],
+                            achieved / (2.0 * peaks["bf16"]), kernels["tc"]["launches_per_step"],
+                            1e3 * tc_ms / max(1, kernels["tc"]["launches_per_step"])),
+                "kernels": kernels,
+            }
+        elif "non_max_suppression" in kernels:
+            b = args.batch
+            n = wl.SSD_ANCHORS
+            nbytes = 2.0 * b * n * 6 * 4
+            ms = kernels["non_max_suppression"]["ms_per_step"]
+            achieved = nbytes / (ms * 1e-3) / 1e9
+            roofline = {"kernel": "nms_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                        "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernels": kernels}
+
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        sample = {"resnet50": 16, "mobilenet": 32, "vgg19": 4, "conv_chain": 64, "ssd_tail": 16}[args.workload]
+        cpu = cpu_baseline(ge.load_oracle(), wl, args.workload, sample, repeats=2)
+        cpu.pop("seconds_per_step", None)
+
+    if rank == 0:
+        total_units = units * world * args.steps
+        line = {
+            "metric": METRIC if args.workload == "resnet50" else args.workload + " " + UNITS[args.workload],
+            "value": total_units / (dev_ms * 1e-3), "unit": UNITS[args.workload], "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 operands, int32 accumulate", "data": "synthetic",
+            "config": {"workload": "%s batch %d per GPU (global batch %d), seeded synthetic int8 weights/inputs"
+                                   % (args.workload, args.batch, args.batch * world),
+                       "parallelism": "batch-sharded replicas x%d, no collective" % world,
+                       "l2": "inputs larger than L2: every step streams >126 MB of activations"},
+            "e2e": {"value": total_units / e2e_dt, "unit": UNITS[args.workload],
+                    "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(out.nbytes) + 4,
+                    "ms_per_step": 1e3 * e2e_dt / args.steps},
+            "gpu_launches": int(launches) * args.steps,
+            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    rt.CVMAPIFreeModel(net)
+    if dist:
+        dist.destroy_process_group()
+
+
+def tc_conv_ops(graph_json):
+    """2 * MACs of the conv2d / dense nodes that run on the tensor-core kernel (groups = 1,
+    input channels a multiple of 32, output channels a multiple of 8)."""
+    gj = json.loads(graph_json)
+    shapes = gj["attrs"]["shape"][1]
+    row_ptr = gj["node_row_ptr"]
+    attrs = gj["attrs"]["op_attrs"][1]
+    total = 0
+    for nid, nd in enumerate(gj["nodes"]):
+        if nd["op"] == "null" or nd["attrs"]["func_name"] not in ("conv2d", "dense"):
+            continue
+        w = shapes[row_ptr[nd["inputs"][1][0]]]
+        xs = shapes[row_ptr[nd["inputs"][0][0]]]
+        o = shapes[row_ptr[nid]]
+        groups = int(json.loads(attrs[nid]).get("groups", "1"))
+        if groups == 1 and xs[1] % 32 == 0 and w[0] % 8 == 0:
+            total += 2 * int(np.prod(o)) * int(np.prod(w[1:]))
+    return total
+
+
+if __name__ == "__main__":
+    main()

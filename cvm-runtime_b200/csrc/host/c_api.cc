@@ -1,5 +1,6 @@
 // The model wrapper (CVMModel, src/core/model.cc) and the C entry points (src/core/c_api.cc).
 #include "cvm/c_api.h"
+#include "cvm/c_api_ext.h"
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -83,6 +84,10 @@ class Model {
     SaveTensor(output);
   }
 
+  Executor& executor() {
+    CHECK(exec_) << "model parameters have not been loaded";
+    return *exec_;
+  }
   int64_t GetStorageSize() const { return g_.GetStorageSize(); }
   int64_t GetOps() const { return g_.GetOps(); }
   int input_bytes() const { return input_bytes_; }
@@ -271,6 +276,45 @@ int CVMAPIGetGasFromGraphFile(const char* graph_json, unsigned long long* gas) {
   cvm::Graph g;
   g.Init(json);
   *gas = (unsigned long long)g.GetOps();
+  API_END();
+}
+
+// ---- measurement helpers (include/cvm/c_api_ext.h); not part of the reference ABI ----------
+
+int CVMXStepCount(void* net, unsigned long long* n) {
+  API_BEGIN();
+  CHECK(net != nullptr); CHECK(n != nullptr);
+  *n = (unsigned long long)static_cast<Model*>(net)->executor().num_steps();
+  API_END();
+}
+
+int CVMXDeviceBytes(void* net, unsigned long long* n) {
+  API_BEGIN();
+  CHECK(net != nullptr); CHECK(n != nullptr);
+  *n = (unsigned long long)static_cast<Model*>(net)->executor().device_bytes();
+  API_END();
+}
+
+int CVMXReplayDevice(void* net, int iters, float* total_ms) {
+  API_BEGIN();
+  CHECK(net != nullptr); CHECK(total_ms != nullptr);
+  *total_ms = static_cast<Model*>(net)->executor().ReplayDevice(iters);
+  API_END();
+}
+
+int CVMXProfileSteps(void* net, const char* input_data, int input_len, char* text, int text_len) {
+  API_BEGIN();
+  CHECK(net != nullptr); CHECK(input_data != nullptr); CHECK(text != nullptr); CHECK(text_len > 0);
+  auto rows = static_cast<Model*>(net)->executor().ProfileOnce(input_data, (size_t)input_len);
+  std::string out;
+  char line[64];
+  for (const auto& r : rows) {
+    snprintf(line, sizeof(line), "\t%.6f\n", r.second);
+    out += r.first;
+    out += line;
+  }
+  CHECK((int)out.size() < text_len) << "profile text needs " << out.size() + 1 << " bytes";
+  memcpy(text, out.c_str(), out.size() + 1);
   API_END();
 }
 

@@ -783,6 +783,7 @@ Executor::~Executor() {
   cudaSetDevice(device_);
   if (stream_) cudaStreamSynchronize(stream_);
   if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+  if (kernels_exec_) cudaGraphExecDestroy(kernels_exec_);
   for (void* p : allocs_) cudaFree(p);
   for (void* p : pinned_) cudaFreeHost(p);
   if (stream_) cudaStreamDestroy(stream_);
@@ -812,6 +813,34 @@ void Executor::Run(const void* input, size_t input_bytes) {
     cudaStreamSynchronize(stream_);
     FATAL() << "a device-side wait ran out (status word 0x" << std::hex << code << ")";
   }
+}
+
+float Executor::ReplayDevice(int iters) {
+  CHECK(iters > 0);
+  CUDA_OK(cudaSetDevice(device_));
+  if (use_graph_ && !kernels_exec_) {
+    cudaGraph_t graph = nullptr;
+    CUDA_OK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+    for (auto& st : steps_) KERNEL_OK(st.launch(stream_));
+    CUDA_OK(cudaStreamEndCapture(stream_, &graph));
+    CUDA_OK(cudaGraphInstantiate(&kernels_exec_, graph, 0));
+    CUDA_OK(cudaGraphDestroy(graph));
+  }
+  cudaEvent_t e0, e1;
+  CUDA_OK(cudaEventCreate(&e0));
+  CUDA_OK(cudaEventCreate(&e1));
+  CUDA_OK(cudaEventRecord(e0, stream_));
+  for (int i = 0; i < iters; ++i) {
+    if (kernels_exec_) CUDA_OK(cudaGraphLaunch(kernels_exec_, stream_));
+    else for (auto& st : steps_) KERNEL_OK(st.launch(stream_));
+  }
+  CUDA_OK(cudaEventRecord(e1, stream_));
+  CUDA_OK(cudaEventSynchronize(e1));
+  float ms = 0;
+  CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return ms;
 }
 
 std::vector<std::pair<std::string, float>> Executor::ProfileOnce(const void* input, size_t input_bytes) {

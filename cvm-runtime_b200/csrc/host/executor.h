@@ -56,6 +56,9 @@ class Executor {
   size_t device_bytes() const { return device_bytes_; }
   // Per-step device times of one eager pass (label, milliseconds); used by the profiling table.
   std::vector<std::pair<std::string, float>> ProfileOnce(const void* input, size_t input_bytes);
+  // Replays only the kernels (input already in device memory, no upload / download) `iters`
+  // times and returns the device time in milliseconds measured with CUDA events on the stream.
+  float ReplayDevice(int iters);
 
  private:
   struct Impl;
@@ -75,6 +78,7 @@ class Executor {
   int32_t* status_dev_ = nullptr;
   int32_t* status_host_ = nullptr;
   cudaGraphExec_t graph_exec_ = nullptr;
+  cudaGraphExec_t kernels_exec_ = nullptr;
   bool use_graph_ = true;
 
   void* dalloc(size_t bytes);

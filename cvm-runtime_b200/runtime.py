@@ -147,3 +147,33 @@ def CVMAPIInference(net, input_data):
     raw = inference_bytes(net, input_data)
     otype = CVMAPIGetOutputTypeSize(net)
     return raw.view(np.int8 if otype == 1 else np.int32).astype(np.int64).tolist()
+
+
+# ---- measurement helpers (include/cvm/c_api_ext.h) --------------------------------------------
+def step_count(net):
+    """Kernel launches per inference."""
+    return _get_ull("CVMXStepCount", net)
+
+
+def device_bytes(net):
+    return _get_ull("CVMXDeviceBytes", net)
+
+
+def replay_device(net, iters):
+    """Device milliseconds for `iters` kernel-only replays (input of the last inference)."""
+    ms = ctypes.c_float()
+    check_call(lib().CVMXReplayDevice(net, ctypes.c_int(iters), ctypes.byref(ms)), "CVMXReplayDevice")
+    return ms.value
+
+
+def profile_steps(net, input_data):
+    """[(operator label, milliseconds)] of one launch-by-launch pass."""
+    arr = np.ascontiguousarray(input_data)
+    buf = ctypes.create_string_buffer(1 << 20)
+    check_call(lib().CVMXProfileSteps(net, arr.ctypes.data_as(ctypes.c_char_p), ctypes.c_int(arr.nbytes),
+                                      buf, ctypes.c_int(len(buf))), "CVMXProfileSteps")
+    rows = []
+    for line in buf.value.decode().splitlines():
+        label, ms = line.rsplit("\t", 1)
+        rows.append((label, float(ms)))
+    return rows
