@@ -349,6 +349,16 @@ struct Lowering {
     probe.dil_h = dh; probe.dil_w = dw;
     const bool tc = groups == 1 && cvmk_conv2d_tc_supported(&probe) && !getenv("CVM_B200_NO_TC");
     const bool depthwise = !dense && groups == C && OC == C && C % 16 == 0 && safe8[ex_];
+    // Few-channel convolutions (image stems): gather patches into a [M, Kp] matrix, then run the
+    // tensor-core kernel on it as a 1x1 convolution.
+    const int kflat = KH * KW * icg, kp = (kflat + 31) / 32 * 32;
+    cvmk_conv_desc packed = probe;
+    packed.N = N * OH * OW; packed.H = packed.W = 1; packed.C = kp; packed.KH = packed.KW = 1;
+    packed.OH = packed.OW = 1; packed.stride_h = packed.stride_w = 1; packed.pad_h = packed.pad_w = 0;
+    packed.dil_h = packed.dil_w = 1;
+    const bool via_pack = !tc && !dense && groups == 1 && safe8[ex_] && C <= 255 && kflat <= 8192 &&
+                          (KW - 1) * dw <= 4095 && (KH - 1) * dh <= 2047 &&
+                          cvmk_conv2d_tc_supported(&packed) && !getenv("CVM_B200_NO_TC");
 
     // weights: OIHW int32 -> int8, [OC, KH, KW, C/groups] (depthwise: [KH, KW, C])
     std::vector<int8_t> w8((size_t)OC * KH * KW * icg);
@@ -361,8 +371,36 @@ struct Lowering {
           for (int k = 0; k < KH * KW; ++k)
             w8[((size_t)o * KH * KW + k) * icg + i] = (int8_t)wt.data[((size_t)o * icg + i) * KH * KW + k];
     }
+    if (via_pack) {  // rows padded with zeros from K to Kp
+      std::vector<int8_t> wp((size_t)OC * kp, 0);
+      for (int o = 0; o < OC; ++o) memcpy(&wp[(size_t)o * kp], &w8[(size_t)o * kflat], kflat);
+      w8.swap(wp);
+    }
     int8_t* wdev = (int8_t*)ex.dalloc(w8.size());
     CUDA_OK(cudaMemcpy(wdev, w8.data(), w8.size(), cudaMemcpyHostToDevice));
+
+    if (via_pack) {
+      DevBuf& xin = materialize(ex_);
+      int8_t* amat = (int8_t*)ex.dalloc((size_t)packed.N * kp);
+      cvmk_im2col_desc pk;
+      memset(&pk, 0, sizeof(pk));
+      pk.x = (const int8_t*)xin.ptr; pk.a = amat;
+      pk.N = N; pk.H = H; pk.W = W; pk.C = C; pk.KH = KH; pk.KW = KW; pk.OH = OH; pk.OW = OW;
+      pk.stride_h = sh; pk.stride_w = sw; pk.pad_h = ph; pk.pad_w = pw; pk.dil_h = dh; pk.dil_w = dw;
+      pk.Kp = kp;
+      add_step(label + "[pack]", [pk](cudaStream_t s) { return cvmk_im2col_pack(&pk, s); });
+      cvmk_conv_desc d = packed;
+      d.x = amat; d.w = wdev; d.y = out.ptr; d.y_dtype = out.dtype;
+      d.status = ex.status_dev_;
+      d.ep = ch.ep;
+      void* mem = nullptr;
+      CHECK(posix_memalign(&mem, 64, sizeof(cvmk_conv_plan)) == 0);
+      ex.plans_.emplace_back((cvmk_conv_plan*)mem, plan_deleter);
+      cvmk_conv_plan* plan = ex.plans_.back().get();
+      KERNEL_OK(cvmk_conv2d_tc_prepare(&d, plan));
+      add_step(label + "[tc]", [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
+      return;
+    }
 
     if (tc) {
       DevBuf xin = i8_view(ex_, label);

@@ -137,6 +137,50 @@ __global__ void __launch_bounds__(128) depthwise_kernel(const __grid_constant__ 
   }
 }
 
+
+// Patch gather: one thread builds 16 consecutive bytes of one row of A.  The (fy, fx, c) split
+// of every k is looked up in a shared-memory table built once per block.
+struct PackParams {
+  const int8_t* x; int8_t* a;
+  int N, H, W, C, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw, Kp, K;
+  int64_t total;  // rows * Kp / 16
+};
+__global__ void __launch_bounds__(256) im2col_pack_kernel(const __grid_constant__ PackParams p) {
+  extern __shared__ int lut[];  // per k: (fy*dh) << 20 | (fx*dw) << 8 | c
+  for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
+    const int fy = k / (p.KW * p.C), r = k - fy * (p.KW * p.C);
+    const int fx = r / p.C, c = r - fx * p.C;
+    lut[k] = ((fy * p.dh) << 20) | ((fx * p.dw) << 8) | c;
+  }
+  __syncthreads();
+  const int chunks = p.Kp / 16;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+    const int q = (int)(i % chunks);
+    int64_t m = i / chunks;
+    const int ox = (int)(m % p.OW);
+    int64_t t = m / p.OW;
+    const int oy = (int)(t % p.OH);
+    const int n = (int)(t / p.OH);
+    const int iy0 = oy * p.sh - p.ph, ix0 = ox * p.sw - p.pw;
+    const int8_t* xn = p.x + (int64_t)n * p.H * p.W * p.C;
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int k = q * 16 + j;
+      if (k < p.K) {
+        const int e = lut[k];
+        const int iy = iy0 + (e >> 20), ix = ix0 + ((e >> 8) & 0xfff), c = e & 0xff;
+        if (iy >= 0 && iy < p.H && ix >= 0 && ix < p.W) {
+          const uint32_t b = (uint8_t)__ldg(xn + ((int64_t)iy * p.W + ix) * p.C + c);
+          w[j >> 2] |= b << ((j & 3) * 8);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(p.a + m * p.Kp + q * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 int grid_sized(int64_t work, int threads) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -183,4 +227,21 @@ extern "C" int cvmk_conv2d_direct(const cvmk_conv_direct_desc* d, cvmk_stream_t 
   if (d->x_dtype == CVMK_I8) conv_direct_kernel<CVMK_I8><<<grid_sized(p.total, 256), 256, 0, s>>>(p);
   else conv_direct_kernel<CVMK_I32><<<grid_sized(p.total, 256), 256, 0, s>>>(p);
   return check_cuda(cudaGetLastError(), "conv_direct_kernel launch");
+}
+
+extern "C" int cvmk_im2col_pack(const cvmk_im2col_desc* d, cvmk_stream_t stream) {
+  if (!d || !d->x || !d->a || d->Kp % 16 || d->C > 255 || (d->KW - 1) * d->dil_w > 4095 ||
+      (d->KH - 1) * d->dil_h > 2047 || d->KH * d->KW * d->C > d->Kp || d->KH * d->KW * d->C > 8192 ||
+      ((uintptr_t)d->a & 15)) {
+    set_error("im2col_pack: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  PackParams p;
+  p.x = d->x; p.a = d->a;
+  p.N = d->N; p.H = d->H; p.W = d->W; p.C = d->C; p.KH = d->KH; p.KW = d->KW; p.OH = d->OH; p.OW = d->OW;
+  p.sh = d->stride_h; p.sw = d->stride_w; p.ph = d->pad_h; p.pw = d->pad_w; p.dh = d->dil_h; p.dw = d->dil_w;
+  p.Kp = d->Kp; p.K = d->KH * d->KW * d->C;
+  p.total = (int64_t)d->N * d->OH * d->OW * (d->Kp / 16);
+  im2col_pack_kernel<<<grid_sized(p.total, 256), 256, p.K * sizeof(int), (cudaStream_t)stream>>>(p);
+  return check_cuda(cudaGetLastError(), "im2col_pack_kernel launch");
 }

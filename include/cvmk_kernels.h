@@ -212,6 +212,23 @@ typedef struct {
 } cvmk_conv_direct_desc;
 CVMK_API int cvmk_conv2d_direct(const cvmk_conv_direct_desc* d, cvmk_stream_t stream);
 
+
+/* ------------------------------------------------------------------------------------------------
+ * Patch gather for convolutions whose channel count is not a multiple of 32 (image stems):
+ * writes A[m][k], m = (n, oy, ox) row-major, k = (fy, fx, c) row-major, zero outside the image
+ * and for K <= k < Kp, so that the convolution becomes a [M, Kp] x [OC, Kp]^T product for the
+ * tensor-core kernel (weights padded the same way).  Same values as im2col_cpu
+ * (cpu/ops/ops.cc:204-246), transposed.  x: int8 NHWC; a: int8 [N*OH*OW, Kp], Kp % 16 == 0.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const int8_t* x;
+  int8_t* a;
+  int32_t N, H, W, C, KH, KW, OH, OW;
+  int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int32_t Kp;
+} cvmk_im2col_desc;
+CVMK_API int cvmk_im2col_pack(const cvmk_im2col_desc* d, cvmk_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * get_valid_counts (cpu/ops/nms.cc:42-63): per batch keep rows with row[1] > score_threshold in
  * their original order, write their number to valid_count[b], fill the remaining rows with -1.
