@@ -137,7 +137,7 @@ def inference_bytes(net, input_data, out=None):
         in_ptr = ctypes.c_char_p(input_data)
         in_len = len(input_data)
     if out is None:
-        out = np.empty(CVMAPIGetOutputLength(net), dtype=np.uint8)
+        out = np.zeros(CVMAPIGetOutputLength(net), dtype=np.uint8)  # argmax mode leaves a tail unwritten
     check_call(lib().CVMAPIInference(net, in_ptr, ctypes.c_int(in_len),
                                      out.ctypes.data_as(ctypes.c_char_p)), "CVMAPIInference")
     return out

@@ -1,0 +1,319 @@
+"""Seeded parity cases shared by the golden-fixture generator and the tests.
+
+Every case is (graph_json, params_blob, input ndarray).  Single-operator graphs follow the
+reference's op-level harness (tests/test_op.cc:478-661: attributes + inputs -> outputs, including
+expected failures); model cases follow its model-level harness (tests/test_model.cc:94-235).
+"""
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+import __graft_entry__ as ge  # noqa: E402
+
+pkg = ge.load_package()
+wl = pkg.workloads
+
+
+def single_op(func, data, data_prec, attrs, out_shapes, params=(), seed=0, head=None):
+    """Graph `data (+ params) -> func -> heads`.  `params` is a list of (ndarray, precision);
+    `head` selects one output of a multi-output operator."""
+    g = wl.GraphBuilder(seed)
+    ins = [g.var("data", data.shape, data_prec)]
+    for i, (arr, prec) in enumerate(params):
+        ins.append(g.var("p%d" % i, arr.shape, prec, arr))
+    out = g.op(func, ins, out_shapes, attrs)
+    heads = out if isinstance(out, list) else [out]
+    if head is not None:
+        heads = [heads[head]]
+    js, pb = g.finish(heads)
+    return js, pb, data
+
+
+def rnd(rng, shape, prec):
+    a = (1 << (prec - 1)) - 1
+    arr = rng.randint(-a, a + 1, size=shape)
+    return arr.astype(np.int8 if prec <= 8 else np.int32)
+
+
+def conv_case(seed, n, c, h, w, oc, k, stride=1, pad=0, dil=1, groups=1, bias=True, shift=None, relu=False):
+    rng = np.random.RandomState(seed)
+    g = wl.GraphBuilder(seed)
+    x = rnd(rng, (n, c, h, w), 8)
+    d = g.var("data", x.shape, 8)
+    y = g.conv(d, oc, k, stride, pad, groups=groups, relu=relu, shift=shift if shift else 0, dilation=dil, bias=bias)
+    js, pb = g.finish(y)
+    return js, pb, x
+
+
+def model_cases():
+    """name -> thunk; small enough for the CPU oracle to finish in seconds."""
+    return {
+        "conv_chain_s14": lambda: wl.conv_chain(batch=1, channels=32, size=14),
+        "conv_chain_b3": lambda: wl.conv_chain(batch=3, channels=64, size=20),
+        "resnet50_s64": lambda: wl.resnet50(batch=1, size=64),
+        "mobilenet_s64": lambda: wl.mobilenet_v1(batch=2, size=64),
+        "vgg19_s32": lambda: wl.vgg19(batch=2, size=32, fc=64),
+        "ssd_backbone_s128": lambda: wl.ssd_backbone(batch=1, size=128),
+        "ssd_tail_b2": lambda: wl.ssd_tail(batch=2, anchors=600, top_k=50),
+        "ssd_tail_mos": lambda: wl.ssd_tail(batch=2, anchors=500, top_k=-1, max_output_size=20),
+        "ssd_tail_force": lambda: wl.ssd_tail(batch=1, anchors=700, top_k=200, force_suppress=True, score_threshold=100),
+        "ssd_tail_none_valid": lambda: wl.ssd_tail(batch=1, anchors=300, top_k=10, score_threshold=1 << 15),
+    }
+
+
+def op_cases():
+    """name -> thunk for single-operator graphs, edge cases included."""
+    c = {}
+    r = np.random.RandomState(1234)
+
+    def add(name, thunk):
+        c[name] = thunk
+
+    # conv2d: tensor-core shapes, strides, dilation, padding, odd channel counts, groups
+    add("conv_tc_3x3", lambda: conv_case(1, 2, 32, 9, 11, 64, 3, 1, 1, shift=9))
+    add("conv_tc_1x1_s2", lambda: conv_case(2, 3, 64, 10, 10, 32, 1, 2, 0, shift=8))
+    add("conv_tc_dil2", lambda: conv_case(3, 1, 32, 12, 12, 48, 3, 1, 2, dil=2, shift=9))
+    add("conv_tc_5x5_s2_nobias", lambda: conv_case(4, 2, 32, 13, 13, 40, 5, 2, 2, bias=False, shift=10))
+    add("conv_tc_int32_out", lambda: conv_case(5, 1, 64, 6, 6, 24, 3, 1, 1, shift=0))
+    add("conv_stem_7x7", lambda: conv_case(6, 2, 3, 30, 30, 16, 7, 2, 3, shift=8, relu=True))
+    add("conv_odd_channels", lambda: conv_case(7, 1, 5, 8, 8, 7, 3, 1, 1, shift=7))
+    add("conv_depthwise", lambda: conv_case(8, 2, 32, 10, 10, 32, 3, 1, 1, groups=32, shift=6, relu=True))
+    add("conv_depthwise_s2", lambda: conv_case(9, 1, 48, 9, 9, 48, 3, 2, 1, groups=48, shift=6))
+    add("conv_grouped", lambda: conv_case(10, 1, 12, 7, 7, 8, 3, 1, 0, groups=4, shift=7))
+
+    def dense_case(seed, m, k, units, bias=True):
+        def f():
+            g = wl.GraphBuilder(seed)
+            x = rnd(np.random.RandomState(seed), (m, k), 8)
+            d = g.var("data", x.shape, 8)
+            y = g.dense(d, units, bias=bias)
+            js, pb = g.finish(y)
+            return js, pb, x
+        return f
+    add("dense_tc", dense_case(11, 5, 64, 24))
+    add("dense_odd", dense_case(12, 3, 50, 10, bias=False))
+
+    def unary(func, attrs, prec=16, shape=(2, 3, 5, 7), seed=20, special=None):
+        def f():
+            rng = np.random.RandomState(seed)
+            x = rnd(rng, shape, prec)
+            if special is not None:
+                flat = x.reshape(-1)
+                flat[:len(special)] = special
+            return single_op(func, x, prec, attrs, [list(shape)])
+        return f
+    big = [(1 << 31) - 1, -(1 << 31) + 1, 0, 1, -1, 255, -256, 1 << 30]
+    add("relu", unary("relu", None))
+    add("abs", unary("abs", None, prec=32, special=big))
+    add("negative", unary("negative", None, prec=32, special=big))
+    add("cvm_precision", unary("cvm_precision", None, prec=32, special=big))
+    add("clip", unary("clip", {"a_min": -100, "a_max": 77}))
+    add("clip_wide", unary("clip", {"a_min": -100000, "a_max": 5}, prec=32, special=big))
+    add("cvm_clip_8", unary("cvm_clip", {"precision": 8}))
+    add("cvm_clip_1", unary("cvm_clip", {"precision": 1}))
+    add("cvm_clip_20", unary("cvm_clip", {"precision": 20}, prec=32, special=big))
+    add("rshift_8_8", unary("cvm_right_shift", {"precision": 8, "shift_bit": 8}, prec=24))
+    add("rshift_1_8", unary("cvm_right_shift", {"precision": 8, "shift_bit": 1}, prec=32, special=big))
+    add("rshift_p1", unary("cvm_right_shift", {"precision": 1, "shift_bit": 3}, prec=32, special=big))
+    add("rshift_b31", unary("cvm_right_shift", {"precision": 8, "shift_bit": 31}, prec=32, special=big))
+    add("rshift_b32", unary("cvm_right_shift", {"precision": 8, "shift_bit": 32}, prec=32, special=big))
+    add("rshift_noclip", unary("cvm_right_shift", {"precision": 8, "shift_bit": 24}, prec=32, special=big))
+    add("rshift_noclip_b1", unary("cvm_right_shift", {"precision": 31, "shift_bit": 1}, prec=32, special=big))
+    add("rshift_16_5", unary("cvm_right_shift", {"precision": 16, "shift_bit": 5}, prec=32, special=big))
+
+    def binary(func, shape_a, shape_b, out_shape, pa=8, pb_=8, seed=30, zero_b=False):
+        def f():
+            rng = np.random.RandomState(seed)
+            a = rnd(rng, shape_a, pa)
+            b = rnd(rng, shape_b, pb_)
+            if zero_b:
+                b.reshape(-1)[::3] = 0
+            return single_op(func, a, pa, None, [list(out_shape)], params=[(b, pb_)])
+        return f
+    add("elemwise_add", binary("elemwise_add", (2, 4, 3, 5), (2, 4, 3, 5), (2, 4, 3, 5), 16, 16))
+    add("elemwise_sub", binary("elemwise_sub", (3, 7), (3, 7), (3, 7), 30, 30))
+    for op in ("add", "sub", "mul", "max", "div", "greater"):
+        add("broadcast_%s_scalar" % op, binary("broadcast_" + op, (2, 3, 4, 5), (1,), (2, 3, 4, 5), 12, 12, zero_b=False))
+        add("broadcast_%s_chan" % op, binary("broadcast_" + op, (2, 6, 4, 5), (6, 1, 1), (2, 6, 4, 5), 12, 12, zero_b=(op == "div")))
+        add("broadcast_%s_nd" % op, binary("broadcast_" + op, (3, 1, 5), (2, 1, 4, 1), (2, 3, 4, 5), 10, 10, zero_b=(op == "div")))
+    add("broadcast_div_zero_scalar", lambda: single_op(
+        "broadcast_div", rnd(np.random.RandomState(3), (4, 5), 16), 16, None, [[4, 5]],
+        params=[(np.zeros((1,), np.int32), 16)]))
+
+    def pool(seed, shape, k, s, p, ceil=False, prec=8, pad1=False):
+        def f():
+            rng = np.random.RandomState(seed)
+            x = rnd(rng, shape, prec)
+            n, ch, h, w = shape
+            if ceil:
+                oh, ow = -(-(h + 2 * p - k) // s) + 1, -(-(w + 2 * p - k) // s) + 1
+            else:
+                oh, ow = (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
+            attrs = {"pool_size": (k, k), "strides": (s, s), "padding": (p,) if pad1 else (p, p), "ceil_mode": ceil}
+            return single_op("max_pool2d", x, prec, attrs, [[n, ch, oh, ow]])
+        return f
+    add("max_pool_3x3_s2", pool(40, (2, 16, 11, 11), 3, 2, 1))
+    add("max_pool_2x2", pool(41, (1, 5, 8, 6), 2, 2, 0))
+    add("max_pool_ceil", pool(42, (1, 16, 10, 10), 3, 2, 0, ceil=True))
+    add("max_pool_int32", pool(43, (1, 4, 9, 9), 3, 1, 1, prec=20, pad1=True))
+
+    add("upsampling", lambda: single_op("upsampling", rnd(np.random.RandomState(50), (2, 16, 4, 5), 8), 8,
+                                        {"scale": 2}, [[2, 16, 8, 10]]))
+    add("upsampling_x3_int32", lambda: single_op("upsampling", rnd(np.random.RandomState(51), (1, 3, 3, 2), 20), 20,
+                                                 {"scale": 3}, [[1, 3, 9, 6]]))
+
+    def concat(seed, shapes, axis, prec=8):
+        def f():
+            rng = np.random.RandomState(seed)
+            arrs = [rnd(rng, s, prec) for s in shapes]
+            out = list(shapes[0])
+            ax = axis if axis >= 0 else axis + len(out)
+            out[ax] = sum(s[ax] for s in shapes)
+            return single_op("concatenate", arrs[0], prec, {"axis": axis}, [out],
+                             params=[(a, prec) for a in arrs[1:]])
+        return f
+    add("concat_channels", concat(60, [(2, 16, 4, 4), (2, 32, 4, 4), (2, 16, 4, 4)], 1))
+    add("concat_anchor_axis", concat(61, [(2, 10, 6), (2, 7, 6)], 1, prec=16))
+    add("concat_last_neg", concat(62, [(3, 4, 2), (3, 4, 5)], -1, prec=12))
+    add("concat_h", concat(63, [(1, 3, 4, 5), (1, 3, 2, 5)], 2))
+
+    def red(func, seed, shape, axis, keepdims=False, exclude=False, prec=8, out=None):
+        def f():
+            rng = np.random.RandomState(seed)
+            x = rnd(rng, shape, prec)
+            nd = len(shape)
+            ax = sorted(a + nd if a < 0 else a for a in axis)
+            real = ax if not exclude else [i for i in range(nd) if i not in ax]
+            if not ax and not exclude:
+                real = list(range(nd))
+            if len(real) == nd:
+                oshape = [1] * nd if keepdims else [1]
+            elif not real:
+                oshape = list(shape)
+            elif keepdims:
+                oshape = [1 if i in real else shape[i] for i in range(nd)]
+            else:
+                oshape = [shape[i] for i in range(nd) if i not in real]
+            return single_op(func, x, prec, {"axis": tuple(axis), "keepdims": keepdims, "exclude": exclude}, [oshape])
+        return f
+    add("sum_hw", red("sum", 70, (2, 32, 7, 7), (2, 3)))
+    add("sum_hw_keep", red("sum", 71, (2, 16, 3, 3), (2, 3), keepdims=True))
+    add("sum_all", red("sum", 72, (3, 4, 5), ()))
+    add("max_all_negative", lambda: single_op("max", -np.abs(rnd(np.random.RandomState(73), (4, 6), 8)) - 1, 8,
+                                              {"axis": (), "keepdims": False, "exclude": False}, [[1]]))
+    add("max_axis1", red("max", 74, (3, 5, 4), (1,)))
+    add("sum_exclude", red("sum", 75, (2, 3, 4, 5), (1,), exclude=True))
+    add("sum_channel_keep", red("sum", 76, (2, 6, 4, 4), (1,), keepdims=True))
+    add("sum_size1_quirk", red("sum", 77, (3, 2, 1), (1,)))       # cpu index-map quirk, reduce.cc:66-89
+    add("max_axes_neg", red("max", 78, (2, 3, 4), (-1, 0)))
+
+    def reshape_like(func, seed, shape, attrs, out, prec=8):
+        def f():
+            return single_op(func, rnd(np.random.RandomState(seed), shape, prec), prec, attrs, [out])
+        return f
+    add("flatten_4d", reshape_like("flatten", 80, (2, 16, 3, 5), None, [2, 240]))
+    add("reshape_4d_to_3d", reshape_like("reshape", 81, (2, 8, 3, 5), {"shape": (0, -1, 5)}, [2, 24, 5]))
+    add("reshape_2d_to_4d", reshape_like("reshape", 82, (2, 60), {"shape": (2, 4, 3, 5)}, [2, 4, 3, 5]))
+    add("expand_dims", reshape_like("expand_dims", 83, (3, 4), {"axis": 1, "num_newaxis": 2}, [3, 1, 1, 4], prec=12))
+    add("squeeze", reshape_like("squeeze", 84, (3, 1, 4, 1), {"axis": (1, 3)}, [3, 4], prec=12))
+
+    def gvc(seed, b, n, k, thr, head=1):
+        def f():
+            rng = np.random.RandomState(seed)
+            x = rng.randint(-50, 1000, size=(b, n, k)).astype(np.int32)
+            return single_op("get_valid_counts", x, 16, {"score_threshold": thr}, [[b], [b, n, k]], head=head)
+        return f
+    add("gvc_k6", gvc(90, 3, 257, 6, 400))
+    add("gvc_k6_count", gvc(90, 3, 257, 6, 400, head=0))
+    add("gvc_k5_all", gvc(91, 2, 40, 5, -100))
+    add("gvc_none", gvc(92, 2, 33, 6, 5000))
+    add("gvc_big", gvc(93, 2, 3000, 6, 300))
+
+    def nms_direct(seed, b, n, vcs, **kw):
+        """non_max_suppression fed by parameters, so valid_count and ids can be arbitrary."""
+        def f():
+            rng = np.random.RandomState(seed)
+            rows = wl.ssd_boxes(b, n, seed, classes=4, image=64)
+            if kw.pop("neg_ids", False):
+                rows[:, ::5, 0] = -1
+            if kw.pop("ties", False):
+                rows[:, :, 1] = rng.randint(0, 6, size=(b, n))
+            g = wl.GraphBuilder(seed)
+            d = g.var("data", rows.shape, 16)
+            vc = g.var("vc", (b,), 16, np.array(vcs, np.int32))
+            attrs = {"iou_threshold": 30, "top_k": -1, "max_output_size": -1, "force_suppress": False,
+                     "id_index": 0, "score_index": 1, "coord_start": 2, "return_indices": False,
+                     "invalid_to_bottom": True}
+            attrs.update(kw)
+            y = g.op("non_max_suppression", [d, vc], rows.shape, attrs)
+            js, pb = g.finish(y)
+            return js, pb, rows
+        return f
+    add("nms_basic", nms_direct(100, 2, 300, [300, 150]))
+    add("nms_neg_ids", nms_direct(101, 2, 200, [200, 120], neg_ids=True))
+    add("nms_neg_ids_force", nms_direct(102, 1, 200, [180], neg_ids=True, force_suppress=True))
+    add("nms_ties_topk", nms_direct(103, 2, 700, [700, 650], ties=True, top_k=600))
+    add("nms_topk0", nms_direct(104, 1, 50, [40], top_k=0))
+    add("nms_mos", nms_direct(105, 2, 120, [100, 120], max_output_size=7, iou_threshold=60))
+    add("nms_vc_over_n", nms_direct(106, 1, 64, [1000], iou_threshold=101))
+    add("nms_large_block", nms_direct(107, 1, 1300, [1300], iou_threshold=70))
+    return c
+
+
+def malformed_cases():
+    """name -> (graph_json, params_blob): models the loader must refuse, with the reference's
+    status class.  Derived from the conv chain by editing its JSON."""
+    js, pb, _ = wl.conv_chain(batch=1, channels=32, size=8)
+    base = json.loads(js)
+    out = {}
+
+    def mut(name, fn, params=pb):
+        g = json.loads(json.dumps(base))
+        fn(g)
+        out[name] = (json.dumps(g).encode(), params)
+
+    out["not_json"] = (b"{nodes: [", pb)
+    mut("unknown_top_key", lambda g: g.update({"bogus": 1}))
+    mut("missing_heads", lambda g: g.pop("heads"))
+    mut("unknown_op", lambda g: g["nodes"][3]["attrs"].update({"func_name": "conv3d"}))
+    mut("bad_op_type", lambda g: g["nodes"][3].update({"op": "tvm_op"}))
+    mut("unknown_attr", lambda g: g["attrs"]["op_attrs"][1].__setitem__(4, json.dumps({"precision": "8", "shift_bit": "8", "foo": "1"})))
+    mut("missing_required_attr", lambda g: g["attrs"]["op_attrs"][1].__setitem__(4, json.dumps({"precision": "8"})))
+    mut("bad_int_attr", lambda g: g["attrs"]["op_attrs"][1].__setitem__(5, json.dumps({"precision": "eight"})))
+    mut("attrs_on_plain_op", lambda g: g["attrs"]["op_attrs"][1].__setitem__(0, "{}") or g["nodes"][5]["attrs"].update({"func_name": "relu"}))
+    mut("wrong_num_inputs", lambda g: g["nodes"][3]["inputs"].pop())
+    mut("storage_alias_conv", lambda g: g["attrs"]["storage_id"][1].__setitem__(3, 0))
+    mut("negative_storage_id", lambda g: g["attrs"]["storage_id"][1].__setitem__(4, -1))
+    mut("shape_too_many_dims", lambda g: g["attrs"]["shape"][1].__setitem__(2, [1] * 7))
+    mut("wrong_output_shape", lambda g: g["attrs"]["shape"][1].__setitem__(3, [1, 32, 9, 8]))
+    mut("wrong_bias_shape", lambda g: g["attrs"]["shape"][1].__setitem__(2, [31]))
+    mut("precision_too_big", lambda g: g["attrs"]["precision"][1].__setitem__(0, 33))
+    mut("input_precision_9", lambda g: g["attrs"]["precision"][1].__setitem__(0, 9))
+    mut("variable_without_precision", lambda g: g["attrs"]["precision"][1].__setitem__(1, -1))
+    mut("device_index_set", lambda g: g["attrs"].update({"device_index": ["list_int", [0] * 6]}))
+    mut("dltype_int8", lambda g: g["attrs"]["dltype"][1].__setitem__(0, "int8"))
+    mut("bad_row_ptr", lambda g: g["node_row_ptr"].__setitem__(2, 5))
+    mut("bad_arg_nodes", lambda g: g.update({"arg_nodes": [0, 1]}))
+    mut("version_unknown", lambda g: g.update({"version": "cvm_2.0.0"}))
+    mut("not_topological", lambda g: g["nodes"][3]["inputs"].__setitem__(0, [4, 0, 0]))
+    mut("duplicate_names", lambda g: g["nodes"][1].update({"name": "data"}))
+    mut("shift_bit_0", lambda g: g["attrs"]["op_attrs"][1].__setitem__(4, json.dumps({"precision": "8", "shift_bit": "0"})))
+    mut("kernel_exceeds_input", lambda g: (g["attrs"]["op_attrs"][1].__setitem__(3, g["attrs"]["op_attrs"][1][3].replace('"[3, 3]"', '"[30, 30]"'))))
+    mut("params_missing", lambda g: None, params=wl.params_blob({}))
+    mut("params_bad_magic", lambda g: None, params=b"\x00" * 64)
+    big = np.full((32,), 1 << 20, np.int32)
+    w = np.zeros((32, 32, 3, 3), np.int8)
+    mut("param_out_of_range", lambda g: None, params=wl.params_blob({"w": w, "b": big}))
+    mut("param_wrong_shape", lambda g: None, params=wl.params_blob({"w": w[:, :, :2], "b": big // 8192}))
+    mut("param_unknown_name", lambda g: None, params=wl.params_blob({"w": w, "b": big // 8192, "zz": w}))
+    mut("version_1_1_0_ok", lambda g: g.update({"version": "cvm_1.1.0"}))
+    # cvm_1.1.0 recomputes both tables; the reference indexes the missing one before that and
+    # crashes, so this case has no golden status (recorded as -11).
+    mut("version_1_1_0_no_tables", lambda g: (g.update({"version": "cvm_1.1.0"}), g.pop("node_row_ptr"), g.pop("arg_nodes")))
+    mut("postprocess_argmax_ok", lambda g: g.update({"postprocess": "argmax"}))
+    return out

@@ -1,0 +1,201 @@
+"""Parity of the CUDA path, through the C-ABI, against the oracle: bit-exact on every case.
+
+Small cases are checked three ways (committed fixtures from the reference CPU runtime, the numpy
+restatement, and the reference library itself when it travelled with the repository); full-size
+configurations are checked through batch independence and other size-independent properties."""
+import numpy as np
+import pytest
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+MODELS = list(cases.model_cases())
+OPS = list(cases.op_cases())
+
+
+@pytest.mark.parametrize("name", MODELS)
+def test_models_match_golden_and_oracle(name, gpu_run, oracle, golden):
+    js, pb, x = cases.model_cases()[name]()
+    got = gpu_run(js, pb, x)
+    assert np.array_equal(got, golden["model/%s/out" % name]), "differs from the reference fixture"
+    assert np.array_equal(got, oracle.run_model(js, pb, x)), "differs from the oracle"
+
+
+@pytest.mark.parametrize("name", OPS)
+def test_ops_match_golden_and_oracle(name, gpu_run, oracle, golden):
+    js, pb, x = cases.op_cases()[name]()
+    got = gpu_run(js, pb, x)
+    assert np.array_equal(got, golden["op/%s/out" % name]), "differs from the reference fixture"
+    assert np.array_equal(got, oracle.run_model(js, pb, x)), "differs from the oracle"
+
+
+def test_queries_match_reference(rt, golden):
+    for name in ("conv_chain_s14", "resnet50_s64", "ssd_tail_b2"):
+        js, pb, x = cases.model_cases()[name]()
+        meta = golden["model/%s/meta" % name]
+        net = rt.CVMAPILoadModel(js, pb, 0)
+        try:
+            assert rt.CVMAPIGetInputLength(net) == meta[0]
+            assert rt.CVMAPIGetOutputLength(net) == meta[1]
+            assert rt.CVMAPIGetStorageSize(net) == meta[2]
+            if meta[3] == 0:
+                assert rt.CVMAPIGetGasFromModel(net) == meta[4]
+            assert rt.CVMAPIGetVersion(net) == "cvm_1.0.0"
+            assert rt.CVMAPIGetPreprocessMethod(net) == ""
+            assert rt.CVMAPIGetInputTypeSize(net) in (1, 4)
+        finally:
+            rt.CVMAPIFreeModel(net)
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+@pytest.mark.parametrize("batch", [1, 5])
+def test_conv_chain_seeds(seed, batch, gpu_run, oracle, wl):
+    """Config 1 (64 -> 64 channels, 3x3, 56x56) over seeds and batch sizes."""
+    js, pb, x = wl.conv_chain(batch=batch, seed=seed)
+    assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x))
+
+
+def test_random_conv_shapes(gpu_run, oracle):
+    """Random strides / dilations / paddings / channel counts, tensor-core and CUDA-core paths."""
+    rng = np.random.RandomState(2024)
+    for i in range(24):
+        c = int(rng.choice([3, 8, 32, 64, 96, 128]))
+        groups = 1 if rng.rand() < 0.7 else int(rng.choice([g for g in (2, 4, c) if c % g == 0]))
+        oc = int(rng.choice([8, 16, 24, 32, 64, 136])) // groups * groups or groups
+        k = int(rng.choice([1, 2, 3, 5]))
+        dil = int(rng.choice([1, 1, 2]))
+        stride = int(rng.choice([1, 1, 2, 3]))
+        pad = int(rng.randint(0, k * dil // 2 + 1))
+        h, w = int(rng.randint(6, 19)), int(rng.randint(6, 19))
+        if dil * (k - 1) + 1 > min(h, w) + 2 * pad:
+            continue
+        js, pb, x = cases.conv_case(100 + i, int(rng.randint(1, 4)), c, h, w, oc, k, stride, pad, dil,
+                                    groups=groups, bias=bool(rng.rand() < 0.7), shift=int(rng.randint(0, 12)),
+                                    relu=bool(rng.rand() < 0.5))
+        assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x)), (i, c, oc, k, stride, pad, dil, groups)
+
+
+def test_input_is_clamped_to_its_precision(gpu_run, oracle, wl):
+    """graph_runtime.cc:379-386: -128 enters the network as -127."""
+    js, pb, x = wl.conv_chain(batch=1, channels=32, size=8)
+    x = x.copy()
+    x.reshape(-1)[::7] = -128
+    assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x))
+
+
+def test_postprocess_argmax(gpu_run, oracle, wl):
+    g = wl.GraphBuilder(5)
+    d = g.var("data", (6, 64), 8)
+    y = g.dense(d, 40, shift=9)
+    js, pb = g.finish(y, postprocess="argmax")
+    x = np.random.RandomState(5).randint(-127, 128, size=(6, 64)).astype(np.int8)
+    assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x))
+
+
+def test_multi_head_detection_interleave(gpu_run, oracle, wl):
+    """model.cc:200-246: heads with equal row counts are interleaved row-wise."""
+    g = wl.GraphBuilder(6)
+    d = g.var("data", (4, 32), 8)
+    a = g.dense(d, 8, shift=8)
+    b = g.dense(d, 16)
+    js, pb = g.finish([a, b], postprocess="detection")
+    x = np.random.RandomState(6).randint(-127, 128, size=(4, 32)).astype(np.int8)
+    assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x))
+
+
+def test_api_errors_on_a_loaded_model(rt, wl):
+    import ctypes
+    js, pb, x = wl.conv_chain(batch=1, channels=32, size=8)
+    net = rt.CVMAPILoadModel(js, pb, 0)
+    try:
+        out = np.zeros(rt.CVMAPIGetOutputLength(net), np.uint8)
+        lib = rt.lib()
+        st = lib.CVMAPIInference(net, x.ctypes.data_as(ctypes.c_char_p), x.nbytes - 1, out.ctypes.data_as(ctypes.c_char_p))
+        assert st == rt.ERROR_LOGIC          # wrong input length, model.cc:155
+        assert lib.CVMAPIInference(net, None, x.nbytes, out.ctypes.data_as(ctypes.c_char_p)) == rt.ERROR_RUNTIME
+        assert lib.CVMAPIInference(net, x.ctypes.data_as(ctypes.c_char_p), x.nbytes, out.ctypes.data_as(ctypes.c_char_p)) == 0
+    finally:
+        rt.CVMAPIFreeModel(net)
+    with pytest.raises(rt.CVMError) as e:
+        rt.CVMAPILoadModel(js, pb, 99)       # no such GPU
+    assert e.value.status == rt.ERROR_RUNTIME
+
+
+def test_accepted_variants_load(rt, golden_status):
+    for name in ("version_1_1_0_ok", "version_1_1_0_no_tables", "postprocess_argmax_ok"):
+        js, pb = cases.malformed_cases()[name]
+        net = rt.CVMAPILoadModel(js, pb, 0)
+        rt.CVMAPIFreeModel(net)
+
+
+# ---------------------------------------------------------------------------------------------
+# full-size configurations: size-independent properties
+# ---------------------------------------------------------------------------------------------
+def test_resnet50_batch256_batch_independence(rt, gpu_run, oracle, wl):
+    """ResNet-50 at the benchmark batch: image i of the batch-256 run equals the same image run in
+    a batch of 4, and that small batch equals the oracle."""
+    js, pb, x = wl.resnet50(batch=256)
+    big = gpu_run(js, pb, x).view(np.int32).reshape(256, 1000)
+    js4, pb4, _ = wl.resnet50(batch=4)
+    for lo in (0, 124, 252):
+        small = gpu_run(js4, pb4, x[lo:lo + 4]).view(np.int32).reshape(4, 1000)
+        assert np.array_equal(big[lo:lo + 4], small)
+    assert np.array_equal(gpu_run(js4, pb4, x[:4]), oracle.run_model(js4, pb4, x[:4]))
+    # replays are deterministic
+    net = rt.CVMAPILoadModel(js, pb, 0)
+    try:
+        a = rt.inference_bytes(net, x).copy()
+        b = rt.inference_bytes(net, x).copy()
+        assert np.array_equal(a, b) and np.array_equal(a.view(np.int32).reshape(256, 1000), big)
+    finally:
+        rt.CVMAPIFreeModel(net)
+
+
+@pytest.mark.parametrize("builder,batch,small", [("mobilenet_v1", 64, 2), ("vgg19", 16, 1)])
+def test_large_batch_matches_small_batches(builder, batch, small, gpu_run, oracle, wl):
+    js, pb, x = getattr(wl, builder)(batch=batch)
+    big = gpu_run(js, pb, x).view(np.int32).reshape(batch, 1000)
+    jss, pbs, _ = getattr(wl, builder)(batch=small)
+    for lo in (0, batch - small):
+        got = gpu_run(jss, pbs, x[lo:lo + small])
+        assert np.array_equal(big[lo:lo + small], got.view(np.int32).reshape(small, 1000))
+    assert np.array_equal(gpu_run(jss, pbs, x[:small]), oracle.run_model(jss, pbs, x[:small]))
+
+
+def test_ssd_tail_full_size_properties(gpu_run, wl):
+    """24564 anchors, batch 64: per image the kept rows are sorted by score, come from the input,
+    respect top_k, are padded with -1, and running NMS on its own output changes nothing."""
+    b, n = 64, wl.SSD_ANCHORS
+    js, pb, x = wl.ssd_tail(batch=b)
+    y = gpu_run(js, pb, x).view(np.int32).reshape(b, n, 6)
+    for i in (0, 31, 63):
+        kept = y[i][y[i, :, 0] >= 0]
+        assert 0 < len(kept) <= 400
+        assert np.all(y[i, len(kept):] == -1)
+        assert np.all(np.diff(kept[:, 1]) <= 0)
+        rows = {tuple(r) for r in x[i].tolist()}
+        assert all(tuple(r) in rows for r in kept.tolist())
+        assert kept[:, 1].min() > (1 << 14)
+    again = gpu_run(js, pb, np.where(y < 0, 0, y).astype(np.int32)).view(np.int32).reshape(b, n, 6)
+    for i in (0, 63):
+        k0 = y[i][y[i, :, 0] >= 0]
+        k1 = again[i][again[i, :, 0] >= 0]
+        assert np.array_equal(k0, k1)
+
+
+def test_ssd_tail_full_size_against_oracle_batch1(gpu_run, oracle, wl):
+    js, pb, x = wl.ssd_tail(batch=1)
+    assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x))
+
+
+def test_sharded_model_equals_single_handle(pkg, gpu_run, wl):
+    """ShardedModel over one GPU used twice: same bytes as one handle holding the whole batch."""
+    build = lambda b: wl.mobilenet_v1(batch=b, size=64)
+    js, pb, x = build(6)
+    whole = gpu_run(js, pb, x)
+    sm = pkg.sharding.ShardedModel(build, 6, [0, 0])
+    try:
+        assert np.array_equal(sm.infer(x), whole)
+    finally:
+        sm.free()
