@@ -418,3 +418,55 @@ extern "C" int cvmk_non_max_suppression(const cvmk_nms_desc* d, cvmk_stream_t st
   nms_kernel<<<d->B, THREADS, smem, (cudaStream_t)stream>>>(p);
   return check_cuda(cudaGetLastError(), "nms_kernel launch");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the scratch lives in the library's device image.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_nms_static_scratch[CVMK_NMS_STATIC_SCRATCH_BYTES];
+
+extern "C" int cvmk_non_max_suppression_static(const int32_t* x, const int32_t* valid_count, int32_t* y,
+                                               int32_t B, int32_t N, int32_t max_output_size,
+                                               int32_t iou_threshold, int32_t top_k,
+                                               int32_t force_suppress, cvmk_stream_t stream) {
+  if (!x || !valid_count || !y || B < 1 || N < 1 || iou_threshold <= 0) {
+    set_error("non_max_suppression_static: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  const int64_t need = cvmk_nms_scratch_bytes(B, N);
+  if (need > (int64_t)CVMK_NMS_STATIC_SCRATCH_BYTES) {
+    set_error("non_max_suppression_static: B=%d, N=%d needs %lld bytes of scratch, the built-in array "
+              "holds %u; use cvmk_non_max_suppression with a caller-provided buffer",
+              B, N, (long long)need, (unsigned)CVMK_NMS_STATIC_SCRATCH_BYTES);
+    return CVMK_ERR_ARG;
+  }
+  // In host code the array's name is only a handle; the kernel needs its device address, which
+  // differs per GPU.  Resolved once per device, with that device current.
+  static void* scratch_of_device[64] = {nullptr};
+  static bool attr_of_device[64] = {false};
+  int dev = 0;
+  if (check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return CVMK_ERR_CUDA;
+  if (dev < 0 || dev >= 64) { set_error("non_max_suppression_static: device ordinal %d not supported", dev); return CVMK_ERR_ARG; }
+  if (!scratch_of_device[dev]) {
+    void* ptr = nullptr;
+    if (check_cuda(cudaGetSymbolAddress(&ptr, g_nms_static_scratch), "cudaGetSymbolAddress(nms scratch)"))
+      return CVMK_ERR_CUDA;
+    if (!ptr) { set_error("non_max_suppression_static: null scratch address"); return CVMK_ERR_CUDA; }
+    scratch_of_device[dev] = ptr;
+  }
+  const int smem = (int)sizeof(Smem);
+  if (!attr_of_device[dev]) {
+    if (check_cuda(cudaFuncSetAttribute(nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                   "cudaFuncSetAttribute(nms_kernel)"))
+      return CVMK_ERR_CUDA;
+    attr_of_device[dev] = true;
+  }
+  NmsParams p;
+  p.x = x; p.vc = valid_count; p.y = y;
+  p.B = B; p.N = N;
+  p.mos = max_output_size; p.thr = iou_threshold; p.topk = top_k; p.force = force_suppress;
+  p.scratch = reinterpret_cast<uint32_t*>(scratch_of_device[dev]);
+  p.npad = nms_npad(N);
+  p.per_batch_words = 6 * (int64_t)p.npad;
+  nms_kernel<<<B, THREADS, smem, (cudaStream_t)stream>>>(p);
+  return check_cuda(cudaGetLastError(), "nms_kernel launch (static scratch)");
+}

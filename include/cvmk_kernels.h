@@ -252,6 +252,34 @@ typedef struct {
 CVMK_API int64_t cvmk_nms_scratch_bytes(int32_t B, int32_t N);
 CVMK_API int cvmk_non_max_suppression(const cvmk_nms_desc* d, cvmk_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * non_max_suppression for callers that cannot allocate device memory.  No counterpart in the
+ * reference.
+ *
+ * Some callers of this library are not allowed to call cudaMalloc at the point where they need
+ * NMS: code running between cudaStreamBeginCapture and EndCapture, real-time loops that forbid
+ * anything that may synchronise the device, and hosts that hand this library a fixed memory
+ * budget and no allocator.  cvmk_non_max_suppression() asks such callers for a scratch buffer;
+ * this variant brings its own: a fixed array of CVMK_NMS_STATIC_SCRATCH_BYTES that lives in the
+ * library's device image (every GPU that loads the library holds it until the process exits).
+ *
+ *   - The caller still passes x, valid_count and y (device pointers, as for the entry point above).
+ *   - Problems that need more than CVMK_NMS_STATIC_SCRATCH_BYTES of scratch
+ *     (cvmk_nms_scratch_bytes(B, N) tells how much) are refused with CVMK_ERR_ARG and a message in
+ *     cvmk_last_error(); nothing is launched.
+ *   - The first call on each device resolves the device address of the array (one
+ *     cudaGetSymbolAddress); make that first call before starting a stream capture.  No call
+ *     allocates or frees memory.
+ *   - All calls on a device share the one array and it keeps whatever the previous call left.
+ *     The kernel writes every scratch word before reading it, so nothing has to be cleared, but
+ *     two calls whose kernels overlap on the GPU (different streams) race on it: serialise them.
+ * ---------------------------------------------------------------------------------------------- */
+#define CVMK_NMS_STATIC_SCRATCH_BYTES (8u << 20)
+CVMK_API int cvmk_non_max_suppression_static(const int32_t* x, const int32_t* valid_count, int32_t* y,
+                                             int32_t B, int32_t N, int32_t max_output_size,
+                                             int32_t iou_threshold, int32_t top_k,
+                                             int32_t force_suppress, cvmk_stream_t stream);
+
 /* Text of the last CUDA / argument error seen by a launcher on this thread. */
 CVMK_API const char* cvmk_last_error(void);
 
