@@ -42,10 +42,13 @@ __device__ __forceinline__ int32_t precision_of(int32_t x) {
 //   lin0  linear index (in the output tensor's physical layout) of v[0]; v[j] is lin0 + j
 //   ch0   channel index of v[0] when the V elements run along the channel axis
 //         (ADD_C uses ch0 + j); pass cstride = 0 if all V elements share channel ch0.
-template <int V>
+//   pre / pre_step: when PRE, the tensor operand of step `pre_step` has already been fetched by
+//         the caller (e.g. from a shared-memory tile) into pre[0..V).
+template <int V, bool PRE = false>
 __device__ __forceinline__ void apply_chain(const DevChain& c, int32_t (&v)[V], size_t lin0,
-                                            int ch0, int cstride = 1) {
-  for (int si = 0; si < c.n; ++si) {
+                                            int ch0, int cstride = 1, const int32_t* pre = nullptr,
+                                            int pre_step = -1, int first_step = 0) {
+  for (int si = first_step; si < c.n; ++si) {
     const DevStep st = c.s[si];
     switch (st.op) {
       case K_RELU:
@@ -94,7 +97,10 @@ __device__ __forceinline__ void apply_chain(const DevChain& c, int32_t (&v)[V], 
       case K_SUB_T:
       case K_RSUB_T: {
         int32_t t[V];
-        if (st.dt == CVMK_I8) {
+        if (PRE && si == pre_step) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) t[j] = pre[j];
+        } else if (st.dt == CVMK_I8) {
           const int8_t* p = reinterpret_cast<const int8_t*>(st.ptr) + lin0;
           if (V % 16 == 0 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
 #pragma unroll

@@ -11,6 +11,12 @@
 // residual add ...) and store int8 / int32 NHWC.  Two accumulators alternate so the drain of tile
 // i overlaps the MMAs of tile i+1.  The int32 sum never reaches HBM.
 //
+// int8 outputs leave through shared memory: eight epilogue warps write their packed results into
+// a swizzled staging panel (128 rows x up to 128 bytes) that one thread hands to a TMA store, and
+// the int8 operand of a residual join arrives in the same panel by a TMA load issued one tile
+// ahead, so neither direction costs per-thread global accesses.  int32 outputs (logits, heads)
+// and odd channel counts keep plain vector stores.
+//
 // Reproduces src/runtime/cpu/ops/ops.cc:368-456 (conv2d: im2col_cpu :204-246, matrix_mul
 // :148-200) and :34-75 (dense): int32 accumulation of int8 products is exact, so the order of
 // summation cannot change a bit.
@@ -28,9 +34,11 @@ namespace {
 
 constexpr int BLOCK_M = 128;
 constexpr int MAX_STAGES = 8;
-constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: epilogue
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_DYNAMIC_MAX = 227 * 1024 - 8704;  // 227 KB per CTA minus the static part (bias, barriers)
+constexpr int MAX_BIAS = 2048;          // bias vectors up to this length are staged in shared memory
 
 struct ConvParams {
   void* y;
@@ -44,6 +52,14 @@ struct ConvParams {
   int num_m_tiles, num_n_tiles;
   int tmem_cols;
   int* status;
+  const int32_t* bias;  // per-channel add applied first (nullptr: none)
+  int first_step;       // chain steps before this one are already covered by `bias`
+  int tma_out;          // 1: int8 output staged in shared memory and written with TMA
+  int res_step;         // chain step whose int8 tensor operand is fetched with TMA (-1: none)
+  int panels;           // 128-column panels per tile (1 or 2) on the TMA output path
+  int panel_bytes;      // row length of a panel in bytes: min(block_n, 128)
+  int io_bufs;          // staging buffers per panel: 1 or 2
+  int ring_bytes;       // bytes of the operand ring (the staging buffers follow it)
   DevChain chain;
 };
 
@@ -203,16 +219,48 @@ __device__ __forceinline__ void store_vals(const ConvParams& p, size_t lin, cons
   }
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void named_barrier(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+// Byte offset of 16-byte chunk `j` of row `row` inside a staging panel whose rows are `pw` bytes
+// long and stored with the TMA swizzle of that width (address bits [4,7) ^= bits [7,10), cut to
+// the width).
+__device__ __forceinline__ uint32_t panel_offset(int row, int j, int pw) {
+  const uint32_t lin = (uint32_t)row * (uint32_t)pw + (uint32_t)j * 16u;
+  const uint32_t mask = ((uint32_t)pw - 1u) >> 4;  // 7, 3 or 1 chunks
+  return lin ^ (((lin >> 7) & mask) << 4);
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
                const __grid_constant__ ConvParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[MAX_STAGES];
   __shared__ uint64_t bar_empty[MAX_STAGES];
   __shared__ uint64_t bar_acc_full[2];
   __shared__ uint64_t bar_acc_empty[2];
+  __shared__ uint64_t bar_res[2][2];  // [panel group][staging buffer]
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
+  __shared__ volatile int group_stop[2][2];  // [panel group][tile parity]: leave after this tile
+  __shared__ int32_t bias_s[MAX_BIAS];
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -224,6 +272,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int k_per_tap = p.c / p.block_k;
   const int num_kb = p.kh * p.kw * k_per_tap;
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const bool bias_in_smem = p.bias != nullptr && p.oc <= MAX_BIAS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -232,10 +281,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bar_acc_full[a], 1);
-      mbar_init(&bar_acc_empty[a], 4);
+      mbar_init(&bar_acc_empty[a], NUM_EPI_WARPS);
+      mbar_init(&bar_res[a][0], 1);
+      mbar_init(&bar_res[a][1], 1);
     }
     abort_flag = 0;
+    group_stop[0][0] = group_stop[0][1] = group_stop[1][0] = group_stop[1][1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (bias_in_smem) {
+    const int padded = min(MAX_BIAS, (p.oc + 31) & ~31);
+    for (int i = threadIdx.x; i < padded; i += NUM_THREADS) bias_s[i] = i < p.oc ? __ldg(p.bias + i) : 0;
   }
   if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
   tc_fence_before();
@@ -313,36 +369,119 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
-    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. 32*quarter+31 belong to this warp
+    const int ew = warp - 2;         // 0..7
+    const int quarter = warp & 3;    // TMEM lanes 32*quarter .. +31 belong to this warp
+    const int half = ew >> 2;        // two warps share a quarter and split the columns
     const int row_in_tile = quarter * 32 + lane;
+    const bool has_res = p.tma_out && p.res_step >= 0;
+    const int pw = p.panel_bytes;
+    // column range of this warp inside the tile, and the staging panel it writes
+    int c_begin, c_end, group;
+    if (p.tma_out && p.panels == 2) {
+      group = half;
+      c_begin = half * 128;
+      c_end = c_begin + 128;
+    } else {
+      group = 0;
+      const int width = p.tma_out ? pw : p.block_n;
+      const int hw = max(32, width / 2);
+      c_begin = half * hw;
+      c_end = min(width, c_begin + hw);
+    }
+    const int group_threads = (p.tma_out && p.panels == 2) ? 128 : 256;
+    const bool leader = lane == 0 && ((p.tma_out && p.panels == 2) ? (ew & 3) == 0 : ew == 0);
+    const int panel_size = BLOCK_M * pw;
+    uint8_t* io_base = smem + p.ring_bytes + (size_t)group * p.io_bufs * panel_size;
+    const bool vec_ok = (p.y_dtype == CVMK_I8) ? (p.oc % 16 == 0) : (p.oc % 4 == 0);
     int acc = 0;
     uint32_t acc_phase = 0;
-    bool live = true;
-    const bool vec_ok = (p.y_dtype == CVMK_I8) ? (p.oc % 16 == 0) : (p.oc % 4 == 0);
-    for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int n0 = (tile % p.num_n_tiles) * p.block_n;
-      const int row = (tile / p.num_n_tiles) * BLOCK_M + row_in_tile;
-      if (!mbar_wait(&bar_acc_full[acc], acc_phase, &abort_flag, 4)) { live = false; break; }
+      const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
+      const int row = m0 + row_in_tile;
+      const int buf = p.io_bufs == 2 ? (it & 1) : 0;
+      uint8_t* pb = io_base + (size_t)buf * panel_size;
+      bool ok = true;
+      if (p.tma_out) {
+        if (leader) {
+          if (it > 0) tma_store_wait_read();  // every earlier store has left shared memory
+          if (has_res && !abort_flag) {
+            const int pcol = group * 128;
+            if (it == 0 || p.io_bufs == 1) {
+              mbar_expect_tx(&bar_res[group][buf], (uint32_t)panel_size);
+              tma_load_2d(pb, &tmap_r, &bar_res[group][buf], n0 + pcol, m0);
+            }
+            const int nt = tile + gridDim.x;
+            if (p.io_bufs == 2 && nt < num_tiles) {  // fetch the next tile's operand one tile ahead
+              const int nb = buf ^ 1;
+              mbar_expect_tx(&bar_res[group][nb], (uint32_t)panel_size);
+              tma_load_2d(io_base + (size_t)nb * panel_size, &tmap_r, &bar_res[group][nb],
+                          (nt % p.num_n_tiles) * p.block_n + pcol, (nt / p.num_n_tiles) * BLOCK_M);
+            }
+          }
+        }
+        if (!has_res) named_barrier(1 + group, group_threads);  // staging buffer is free again
+      }
+      ok = mbar_wait(&bar_acc_full[acc], acc_phase, &abort_flag, 4);
       tc_fence_after();
-      for (int c0 = 0; c0 < p.block_n; c0 += 32) {
-        const int col0 = n0 + c0;
-        if (col0 >= p.oc) break;  // uniform across the warp
-        int32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n + c0), v);
-        if (row < p.m_total) {
+      if (ok && has_res) {
+        const uint32_t use = (uint32_t)(p.io_bufs == 2 ? (it >> 1) : it);
+        ok = mbar_wait(&bar_res[group][buf], use & 1, &abort_flag, 5);
+      }
+      if (ok) {
+        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+          const int col0 = n0 + c0;
+          if (col0 >= p.oc) break;  // uniform across the warp
+          int32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n + c0), v);
+          if (p.bias) {
+            if (bias_in_smem) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += bias_s[col0 + j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += (col0 + j < p.oc) ? __ldg(p.bias + col0 + j) : 0;
+            }
+          }
           const size_t lin = (size_t)row * p.oc + col0;
-          if (col0 + 32 <= p.oc && vec_ok) {
-            apply_chain<32>(p.chain, v, lin, col0);
-            store_vals<32>(p, lin, v);
-          } else {
+          if (p.tma_out) {
+            const int j0 = (c0 & 127) >> 4;  // first 16-byte chunk of this thread inside the panel row
+            uint4* q0 = reinterpret_cast<uint4*>(pb + panel_offset(row_in_tile, j0, pw));
+            uint4* q1 = reinterpret_cast<uint4*>(pb + panel_offset(row_in_tile, j0 + 1, pw));
+            if (row < p.m_total) {
+              if (has_res) {
+                int32_t rv[32];
+                const uint4 r0 = *q0, r1 = *q1;
+                const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (col0 + g * 8 < p.oc) {
-                int32_t t[8];
+                for (int k = 0; k < 32; ++k) rv[k] = (int32_t)(int8_t)(w[k >> 2] >> ((k & 3) * 8));
+                apply_chain<32, true>(p.chain, v, lin, col0, 1, rv, p.res_step, p.first_step);
+              } else {
+                apply_chain<32>(p.chain, v, lin, col0, 1, nullptr, -1, p.first_step);
+              }
+            }
+            uint4 a, b;
+            a.x = pack4(v[0], v[1], v[2], v[3]);     a.y = pack4(v[4], v[5], v[6], v[7]);
+            a.z = pack4(v[8], v[9], v[10], v[11]);   a.w = pack4(v[12], v[13], v[14], v[15]);
+            b.x = pack4(v[16], v[17], v[18], v[19]); b.y = pack4(v[20], v[21], v[22], v[23]);
+            b.z = pack4(v[24], v[25], v[26], v[27]); b.w = pack4(v[28], v[29], v[30], v[31]);
+            *q0 = a;
+            *q1 = b;
+          } else if (row < p.m_total) {
+            if (col0 + 32 <= p.oc && vec_ok) {
+              apply_chain<32>(p.chain, v, lin, col0, 1, nullptr, -1, p.first_step);
+              store_vals<32>(p, lin, v);
+            } else {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = v[g * 8 + j];
-                apply_chain<8>(p.chain, t, lin + g * 8, col0 + g * 8);
-                store_vals<8>(p, lin + g * 8, t);
+              for (int g = 0; g < 4; ++g) {
+                if (col0 + g * 8 < p.oc) {
+                  int32_t t[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) t[j] = v[g * 8 + j];
+                  apply_chain<8>(p.chain, t, lin + g * 8, col0 + g * 8, 1, nullptr, -1, p.first_step);
+                  store_vals<8>(p, lin + g * 8, t);
+                }
               }
             }
           }
@@ -351,9 +490,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
+      if (p.tma_out) {
+        fence_async_smem();  // make the staged bytes visible to the TMA engine
+        // One thread decides for the whole group whether to go on, so that nobody is left alone
+        // at the next barrier.
+        if (leader) group_stop[group][it & 1] = abort_flag;
+        named_barrier(1 + group, group_threads);
+        const int stop = group_stop[group][it & 1];
+        if (leader && !stop) tma_store_2d(&tmap_y, pb, n0 + group * 128, m0);
+        if (stop) break;
+      } else if (abort_flag) {
+        break;
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (p.tma_out && leader) tma_store_wait_all();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -416,6 +568,18 @@ bool is_pointwise(const cvmk_conv_desc& d) {
          d.pad_w == 0;
 }
 
+// 2-D int8 tensor map over a row-major [rows, cols] matrix with a {box_cols, box_rows} box.
+CUresult encode_rows(EncodeTiledFn enc, CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
+                     int box_cols, int box_rows, CUtensorMapL2promotion promo) {
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(box_cols), promo,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
 }  // namespace
 }  // namespace cvmk
 
@@ -453,18 +617,37 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   plan->block_k = bk;
   plan->block_n = bn;
   plan->a_im2col = is_pointwise(*d) ? 0 : 1;
+
+  // Output path: int8 tiles leave through shared memory and a TMA store; the first int8 tensor
+  // operand of the chain (a residual join) comes in by TMA as well.
+  plan->tma_out = d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !getenv("CVM_B200_NO_TMA_STORE");
+  plan->res_step = -1;
+  if (plan->tma_out) {
+    for (int i = 0; i < d->ep.n; ++i) {
+      const cvmk_ep_step& s = d->ep.s[i];
+      if ((s.op == CVMK_EP_ADD_T || s.op == CVMK_EP_SUB_T || s.op == CVMK_EP_RSUB_T) &&
+          s.ptr_dtype == CVMK_I8 && s.ptr && ((uintptr_t)s.ptr & 15) == 0) {
+        plan->res_step = i;
+        break;
+      }
+    }
+  }
+  plan->panels = bn == 256 ? 2 : 1;
+  plan->panel_bytes = bn < 128 ? bn : 128;
+  plan->io_bufs = plan->res_step >= 0 ? 2 : 1;
+  const int io_bytes = plan->tma_out ? plan->panels * plan->io_bufs * BLOCK_M * plan->panel_bytes : 0;
   const int stage_bytes = (BLOCK_M + bn) * bk;
-  int stages = SMEM_BUDGET / stage_bytes;
+  int stages = (SMEM_DYNAMIC_MAX - 1024 - io_bytes) / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) { set_error("conv2d_tc_prepare: tile does not fit shared memory"); return CVMK_ERR_UNSUPPORTED; }
   plan->stages = stages;
-  plan->smem_bytes = stages * stage_bytes + 1024;
+  plan->ring_bytes = stages * stage_bytes;
+  plan->smem_bytes = plan->ring_bytes + io_bytes + 1024;
 
   const int64_t m_total = (int64_t)d->N * d->OH * d->OW;
   const int64_t k_total = (int64_t)d->KH * d->KW * d->C;
   CUtensorMap* ta = reinterpret_cast<CUtensorMap*>(plan->tmap_a);
   CUtensorMap* tb = reinterpret_cast<CUtensorMap*>(plan->tmap_b);
-  const CUtensorMapSwizzle sw = swizzle_for(bk);
   CUresult r;
   if (plan->a_im2col) {
     cuuint64_t dims[4] = {(cuuint64_t)d->C, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
@@ -474,27 +657,23 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
     int upper[2] = {d->pad_w - (d->KW - 1) * d->dil_w, d->pad_h - (d->KH - 1) * d->dil_h};
     cuuint32_t estr[4] = {1, (cuuint32_t)d->stride_w, (cuuint32_t)d->stride_h, 1};
     r = enc_im2col(ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)d->x, dims, strides, lower, upper,
-                   (cuuint32_t)bk, (cuuint32_t)BLOCK_M, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   (cuuint32_t)bk, (cuuint32_t)BLOCK_M, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle_for(bk), CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   } else {
-    cuuint64_t dims[2] = {(cuuint64_t)d->C, (cuuint64_t)m_total};
-    cuuint64_t strides[1] = {(cuuint64_t)d->C};
-    cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)BLOCK_M};
-    cuuint32_t estr[2] = {1, 1};
-    r = enc_tiled(ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)d->x, dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    r = encode_rows(enc_tiled, ta, d->x, m_total, d->C, bk, BLOCK_M, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
   }
   if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: activation tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)k_total, (cuuint64_t)d->OC};
-    cuuint64_t strides[1] = {(cuuint64_t)k_total};
-    cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)bn};
-    cuuint32_t estr[2] = {1, 1};
-    r = enc_tiled(tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)d->w, dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: weight tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
+  r = encode_rows(enc_tiled, tb, d->w, d->OC, k_total, bk, bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+  if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: weight tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
+  if (plan->tma_out) {
+    r = encode_rows(enc_tiled, reinterpret_cast<CUtensorMap*>(plan->tmap_y), d->y, m_total, d->OC,
+                    plan->panel_bytes, BLOCK_M, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: output tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
+    if (plan->res_step >= 0) {
+      r = encode_rows(enc_tiled, reinterpret_cast<CUtensorMap*>(plan->tmap_r), d->ep.s[plan->res_step].ptr,
+                      m_total, d->OC, plan->panel_bytes, BLOCK_M, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+      if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: operand tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
+    }
   }
   const int64_t num_m_tiles = (m_total + BLOCK_M - 1) / BLOCK_M;
   const int64_t num_n_tiles = (d->OC + bn - 1) / bn;
@@ -529,8 +708,18 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   while (pow2 < cols) pow2 *= 2;
   p.tmem_cols = pow2;
   p.status = d.status;
+  p.tma_out = plan->tma_out; p.res_step = plan->res_step;
+  p.panels = plan->panels; p.panel_bytes = plan->panel_bytes;
+  p.io_bufs = plan->io_bufs; p.ring_bytes = plan->ring_bytes;
   int rc = lower_chain(d.ep, &p.chain);
   if (rc != CVMK_OK) return rc;
+  // A leading per-channel add is the bias: the kernel keeps it in shared memory.
+  p.bias = nullptr;
+  p.first_step = 0;
+  if (p.chain.n > 0 && p.chain.s[0].op == K_ADD_C) {
+    p.bias = reinterpret_cast<const int32_t*>(p.chain.s[0].ptr);
+    p.first_step = 1;
+  }
 
   static bool attr_set_dev[64] = {false};
   int dev = 0;
@@ -538,13 +727,15 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   bool& attr_set = attr_set_dev[dev & 63];
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SMEM_BUDGET + 2048);
+                                         SMEM_DYNAMIC_MAX);
     if (check_cuda(e, "cudaFuncSetAttribute(conv_tc_kernel)")) return CVMK_ERR_CUDA;
     attr_set = true;
   }
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, ty, tr;
   memcpy(&ta, plan->tmap_a, sizeof(ta));
   memcpy(&tb, plan->tmap_b, sizeof(tb));
-  conv_tc_kernel<<<plan->grid, NUM_THREADS, plan->smem_bytes, (cudaStream_t)stream>>>(ta, tb, p);
+  memcpy(&ty, plan->tmap_y, sizeof(ty));
+  memcpy(&tr, plan->tmap_r, sizeof(tr));
+  conv_tc_kernel<<<plan->grid, NUM_THREADS, plan->smem_bytes, (cudaStream_t)stream>>>(ta, tb, ty, tr, p);
   return check_cuda(cudaGetLastError(), "conv_tc_kernel launch");
 }

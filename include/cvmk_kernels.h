@@ -118,6 +118,8 @@ typedef struct {
 typedef struct __attribute__((aligned(64))) {
   unsigned char tmap_a[128];
   unsigned char tmap_b[128];
+  unsigned char tmap_y[128];   /* output tiles, when they leave through shared memory + TMA */
+  unsigned char tmap_r[128];   /* int8 operand of a fused tensor add/sub, fetched with TMA */
   cvmk_conv_desc d;
   int32_t block_k;    /* bytes of K per pipeline stage: 32, 64 or 128 */
   int32_t block_n;    /* output channels per tile: 32..256 */
@@ -125,7 +127,10 @@ typedef struct __attribute__((aligned(64))) {
   int32_t stages;
   int32_t grid;
   int32_t smem_bytes;
-  int32_t reserved[10];
+  int32_t tma_out;    /* 1: int8 output staged in shared memory and stored with TMA */
+  int32_t res_step;   /* chain step served by tmap_r, -1 if none */
+  int32_t panels, panel_bytes, io_bufs, ring_bytes;
+  int32_t reserved[4];
 } cvmk_conv_plan;
 
 CVMK_API int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d);
