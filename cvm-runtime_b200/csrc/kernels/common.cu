@@ -1,6 +1,7 @@
 // Host-side helpers shared by the launchers: error text, CUDA status mapping, chain lowering.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdint.h>
 #include "common.cuh"
 
 namespace cvmk {
@@ -20,6 +21,42 @@ int check_cuda(cudaError_t e, const char* what) {
   return CVMK_ERR_CUDA;
 }
 
+// Peephole simplification of a lowered chain.  Every rewrite is an identity on int32 values:
+//   relu ; clip(a, b), b >= 0             ->  clip(max(a, 0), b)
+//   rshift_clip(b, alpha)                 ->  rs_clamp: ((clamp(x, lo, hi) + 2^(b-1)) >> b) with
+//                                             lo = -2*alpha << (b-1), hi = (2*alpha-1) << (b-1)
+//   relu ; rs_clamp(lo, hi)               ->  rs_clamp(max(lo, 0), hi)
+//   rs_clamp(.., alpha) ; clip(a, b) with [-alpha, alpha] inside [a, b]  ->  rs_clamp
+static void simplify_chain(DevChain* c) {
+  DevStep out[CVMK_MAX_EP_STEPS];
+  int alpha_of[CVMK_MAX_EP_STEPS];
+  int n = 0;
+  for (int i = 0; i < c->n; ++i) {
+    DevStep s = c->s[i];
+    int alpha = -1;
+    if (s.op == K_RS_CLIP) {
+      const int b = s.a;
+      alpha = s.b;
+      const long long lo = (-2LL * alpha) * (1LL << (b - 1)), hi = (2LL * alpha - 1) * (1LL << (b - 1));
+      if (lo >= INT32_MIN && hi <= INT32_MAX && hi + (1LL << (b - 1)) <= INT32_MAX) {
+        s.op = K_RS_CLAMP;
+        s.a = (int)lo; s.b = (int)hi; s.c = (int)(1LL << (b - 1)); s.d = b;
+      }
+    }
+    if (n > 0 && out[n - 1].op == K_RELU) {
+      if (s.op == K_CLIP && s.b >= 0) { s.a = s.a > 0 ? s.a : 0; --n; }
+      else if (s.op == K_RS_CLAMP && s.b >= 0) { s.a = s.a > 0 ? s.a : 0; --n; }
+    }
+    if (n > 0 && out[n - 1].op == K_RS_CLAMP && s.op == K_CLIP && alpha_of[n - 1] >= 0 &&
+        s.a <= -alpha_of[n - 1] && s.b >= alpha_of[n - 1])
+      continue;  // the clip cannot change anything
+    alpha_of[n] = alpha;
+    out[n++] = s;
+  }
+  c->n = n;
+  for (int i = 0; i < n; ++i) c->s[i] = out[i];
+}
+
 int lower_chain(const cvmk_epilogue& in, DevChain* out) {
   if (in.n < 0 || in.n > CVMK_MAX_EP_STEPS) {
     set_error("element chain has %d steps (max %d)", in.n, CVMK_MAX_EP_STEPS);
@@ -30,7 +67,7 @@ int lower_chain(const cvmk_epilogue& in, DevChain* out) {
   for (int i = 0; i < in.n; ++i) {
     const cvmk_ep_step& s = in.s[i];
     DevStep d;
-    d.op = K_NOP; d.a = s.a; d.b = s.b; d.dt = s.ptr_dtype; d.ptr = s.ptr;
+    d.op = K_NOP; d.a = s.a; d.b = s.b; d.dt = s.ptr_dtype; d.c = 0; d.d = 0; d.ptr = s.ptr;
     switch (s.op) {
       case CVMK_EP_RELU: d.op = K_RELU; break;
       case CVMK_EP_RSHIFT: {
@@ -76,6 +113,7 @@ int lower_chain(const cvmk_epilogue& in, DevChain* out) {
     }
     out->s[i] = d;
   }
+  simplify_chain(out);
   return CVMK_OK;
 }
 

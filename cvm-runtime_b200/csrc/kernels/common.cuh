@@ -13,7 +13,7 @@ int check_cuda(cudaError_t e, const char* what);
 enum : int {
   K_NOP = 0, K_RELU, K_RS_ZERO, K_RS_SIGN, K_RS_NOCLIP, K_RS_CLIP, K_LSHIFT, K_CLIP,
   K_ADD_T, K_SUB_T, K_RSUB_T, K_ADD_C, K_MUL_S, K_ADD_S, K_RSUB_S, K_MAX_S, K_DIV_S, K_RDIV_S,
-  K_GT_S, K_LT_S, K_ABS, K_NEG, K_PRECISION
+  K_GT_S, K_LT_S, K_ABS, K_NEG, K_PRECISION, K_RS_CLAMP
 };
 
 struct DevStep {
@@ -21,6 +21,8 @@ struct DevStep {
   int a;
   int b;
   int dt;
+  int c;   // K_RS_CLAMP: rounding addend
+  int d;   // K_RS_CLAMP: shift
   const void* ptr;
 };
 struct DevChain {
@@ -80,6 +82,13 @@ __device__ __forceinline__ void apply_chain(const DevChain& c, int32_t (&v)[V], 
           t = (t >> 1) + (t & 1);  // == (t + 1) >> 1 without overflow
           v[j] = min(max(t, lo), hi);
         }
+      } break;
+      case K_RS_CLAMP: {
+        // clip(round_shift(x)) == round_shift(clamp(x, a, b)) because the rounding shift is
+        // monotone; the clamp also keeps the addition below from overflowing.
+        const int lo = st.a, hi = st.b, add = st.c, sh = st.d;
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[j] = (min(max(v[j], lo), hi) + add) >> sh;
       } break;
       case K_LSHIFT: {
         const int hi = st.b, lo = -st.b;
@@ -198,8 +207,9 @@ __device__ __forceinline__ void apply_chain(const DevChain& c, int32_t (&v)[V], 
 // Pack four int32 (already within int8 range, or to be truncated like static_cast<int8_t>) into
 // one 32-bit word, element 0 in the low byte.
 __device__ __forceinline__ uint32_t pack4(int32_t a, int32_t b, int32_t c, int32_t d) {
-  return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
-         ((uint32_t)d << 24);
+  const uint32_t lo = __byte_perm((uint32_t)a, (uint32_t)b, 0x0040);  // a.b0, b.b0
+  const uint32_t hi = __byte_perm((uint32_t)c, (uint32_t)d, 0x0040);  // c.b0, d.b0
+  return __byte_perm(lo, hi, 0x5410);
 }
 
 }  // namespace cvmk

@@ -36,7 +36,7 @@ constexpr int BLOCK_M = 128;
 constexpr int MAX_STAGES = 8;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: epilogue
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t SPIN_LIMIT = 1u << 19;  // x 2 us per hardware wait
 constexpr int SMEM_DYNAMIC_MAX = 227 * 1024 - 8704;  // 227 KB per CTA minus the static part (bias, barriers)
 constexpr int MAX_BIAS = 2048;          // bias vectors up to this length are staged in shared memory
 
@@ -80,28 +80,28 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+// One bounded hardware wait: returns true once the phase with `parity` has completed, false if
+// the barrier is still pending after about `ns` nanoseconds.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_t ns) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when it gave up (or another role already did).
+// Bounded wait (about a second in all).  Returns false when it gave up, or when another role of
+// this CTA already did.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int code) {
   for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) {
-      if (*abort_flag) return false;
-      __nanosleep(i > 4096 ? 256 : 32);
-    }
+    if (mbar_try(bar, parity, 2000u)) return true;
+    if (*abort_flag) return false;
   }
   *abort_flag = code;
   return false;
@@ -256,11 +256,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ uint64_t bar_empty[MAX_STAGES];
   __shared__ uint64_t bar_acc_full[2];
   __shared__ uint64_t bar_acc_empty[2];
-  __shared__ uint64_t bar_res[2][2];  // [panel group][staging buffer]
+  __shared__ uint64_t bar_res[2];     // per epilogue group: operand tile landed / staging free
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
   __shared__ volatile int group_stop[2][2];  // [panel group][tile parity]: leave after this tile
-  __shared__ int32_t bias_s[MAX_BIAS];
+  __shared__ __align__(16) int32_t bias_s[MAX_BIAS];
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -281,9 +281,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bar_acc_full[a], 1);
-      mbar_init(&bar_acc_empty[a], NUM_EPI_WARPS);
-      mbar_init(&bar_res[a][0], 1);
-      mbar_init(&bar_res[a][1], 1);
+      mbar_init(&bar_acc_empty[a], NUM_EPI_WARPS / 2);
+      mbar_init(&bar_res[a], 1);
     }
     abort_flag = 0;
     group_stop[0][0] = group_stop[0][1] = group_stop[1][0] = group_stop[1][1] = 0;
@@ -369,76 +368,54 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
+    // Two groups of four warps; group g drains accumulator g, i.e. every second tile of this
+    // CTA, so the waits of one group (TMEM loads, barriers, TMA) hide behind the other's work.
     const int ew = warp - 2;         // 0..7
     const int quarter = warp & 3;    // TMEM lanes 32*quarter .. +31 belong to this warp
-    const int half = ew >> 2;        // two warps share a quarter and split the columns
+    const int group = ew >> 2;
     const int row_in_tile = quarter * 32 + lane;
     const bool has_res = p.tma_out && p.res_step >= 0;
     const int pw = p.panel_bytes;
-    // column range of this warp inside the tile, and the staging panel it writes
-    int c_begin, c_end, group;
-    if (p.tma_out && p.panels == 2) {
-      group = half;
-      c_begin = half * 128;
-      c_end = c_begin + 128;
-    } else {
-      group = 0;
-      const int width = p.tma_out ? pw : p.block_n;
-      const int hw = max(32, width / 2);
-      c_begin = half * hw;
-      c_end = min(width, c_begin + hw);
-    }
-    const int group_threads = (p.tma_out && p.panels == 2) ? 128 : 256;
-    const bool leader = lane == 0 && ((p.tma_out && p.panels == 2) ? (ew & 3) == 0 : ew == 0);
     const int panel_size = BLOCK_M * pw;
-    uint8_t* io_base = smem + p.ring_bytes + (size_t)group * p.io_bufs * panel_size;
+    const bool leader = lane == 0 && (ew & 3) == 0;
+    uint8_t* io_base = smem + p.ring_bytes + (size_t)group * p.panels * panel_size;
     const bool vec_ok = (p.y_dtype == CVMK_I8) ? (p.oc % 16 == 0) : (p.oc % 4 == 0);
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    const int acc = group;
+    const int stride_tiles = 2 * gridDim.x;
+    const int first_tile = blockIdx.x + group * gridDim.x;
+    if (has_res && leader && first_tile < num_tiles) {
+      mbar_expect_tx(&bar_res[group], (uint32_t)(p.panels * panel_size));
+      for (int q = 0; q < p.panels; ++q)
+        tma_load_2d(io_base + (size_t)q * panel_size, &tmap_r, &bar_res[group],
+                    (first_tile % p.num_n_tiles) * p.block_n + q * 128, (first_tile / p.num_n_tiles) * BLOCK_M);
+    }
+    int k = 0;  // index of this group's tile
+    for (int tile = first_tile; tile < num_tiles; tile += stride_tiles, ++k) {
       const int n0 = (tile % p.num_n_tiles) * p.block_n;
       const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
       const int row = m0 + row_in_tile;
-      const int buf = p.io_bufs == 2 ? (it & 1) : 0;
-      uint8_t* pb = io_base + (size_t)buf * panel_size;
-      bool ok = true;
-      if (p.tma_out) {
-        if (leader) {
-          if (it > 0) tma_store_wait_read();  // every earlier store has left shared memory
-          if (has_res && !abort_flag) {
-            const int pcol = group * 128;
-            if (it == 0 || p.io_bufs == 1) {
-              mbar_expect_tx(&bar_res[group][buf], (uint32_t)panel_size);
-              tma_load_2d(pb, &tmap_r, &bar_res[group][buf], n0 + pcol, m0);
-            }
-            const int nt = tile + gridDim.x;
-            if (p.io_bufs == 2 && nt < num_tiles) {  // fetch the next tile's operand one tile ahead
-              const int nb = buf ^ 1;
-              mbar_expect_tx(&bar_res[group][nb], (uint32_t)panel_size);
-              tma_load_2d(io_base + (size_t)nb * panel_size, &tmap_r, &bar_res[group][nb],
-                          (nt % p.num_n_tiles) * p.block_n + pcol, (nt / p.num_n_tiles) * BLOCK_M);
-            }
-          }
-        }
-        if (!has_res) named_barrier(1 + group, group_threads);  // staging buffer is free again
-      }
-      ok = mbar_wait(&bar_acc_full[acc], acc_phase, &abort_flag, 4);
+      bool ok = mbar_wait(&bar_acc_full[acc], (uint32_t)(k & 1), &abort_flag, 4);
       tc_fence_after();
-      if (ok && has_res) {
-        const uint32_t use = (uint32_t)(p.io_bufs == 2 ? (it >> 1) : it);
-        ok = mbar_wait(&bar_res[group][buf], use & 1, &abort_flag, 5);
+      if (ok && p.tma_out) {
+        // staging is ours again: operand tile landed (join) / previous store has been read
+        if (has_res) ok = mbar_wait(&bar_res[group], (uint32_t)(k & 1), &abort_flag, 5);
+        else if (k > 0) ok = mbar_wait(&bar_res[group], (uint32_t)((k - 1) & 1), &abort_flag, 5);
       }
       if (ok) {
-        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+        const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
+        int32_t v[32];
+        tmem_ld32(tbase, v);
+        for (int c0 = 0; c0 < p.block_n; c0 += 32) {
           const int col0 = n0 + c0;
           if (col0 >= p.oc) break;  // uniform across the warp
-          int32_t v[32];
-          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n + c0), v);
           if (p.bias) {
             if (bias_in_smem) {
+              const int4* bp = reinterpret_cast<const int4*>(bias_s + col0);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] += bias_s[col0 + j];
+              for (int j = 0; j < 8; ++j) {
+                const int4 b4 = bp[j];
+                v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+              }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] += (col0 + j < p.oc) ? __ldg(p.bias + col0 + j) : 0;
@@ -446,6 +423,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           const size_t lin = (size_t)row * p.oc + col0;
           if (p.tma_out) {
+            uint8_t* pb = io_base + (size_t)(c0 >> 7) * panel_size;
             const int j0 = (c0 & 127) >> 4;  // first 16-byte chunk of this thread inside the panel row
             uint4* q0 = reinterpret_cast<uint4*>(pb + panel_offset(row_in_tile, j0, pw));
             uint4* q1 = reinterpret_cast<uint4*>(pb + panel_offset(row_in_tile, j0 + 1, pw));
@@ -453,9 +431,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (has_res) {
                 int32_t rv[32];
                 const uint4 r0 = *q0, r1 = *q1;
-                const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+                const int w[8] = {(int)r0.x, (int)r0.y, (int)r0.z, (int)r0.w, (int)r1.x, (int)r1.y, (int)r1.z, (int)r1.w};
 #pragma unroll
-                for (int k = 0; k < 32; ++k) rv[k] = (int32_t)(int8_t)(w[k >> 2] >> ((k & 3) * 8));
+                for (int e = 0; e < 32; ++e) rv[e] = (int32_t)(int8_t)(w[e >> 2] >> ((e & 3) * 8));
                 apply_chain<32, true>(p.chain, v, lin, col0, 1, rv, p.res_step, p.first_step);
               } else {
                 apply_chain<32>(p.chain, v, lin, col0, 1, nullptr, -1, p.first_step);
@@ -485,6 +463,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               }
             }
           }
+          if (c0 + 32 < p.block_n && n0 + c0 + 32 < p.oc) tmem_ld32(tbase + (uint32_t)(c0 + 32), v);
         }
       }
       tc_fence_before();
@@ -494,16 +473,29 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         fence_async_smem();  // make the staged bytes visible to the TMA engine
         // One thread decides for the whole group whether to go on, so that nobody is left alone
         // at the next barrier.
-        if (leader) group_stop[group][it & 1] = abort_flag;
-        named_barrier(1 + group, group_threads);
-        const int stop = group_stop[group][it & 1];
-        if (leader && !stop) tma_store_2d(&tmap_y, pb, n0 + group * 128, m0);
+        if (leader) group_stop[group][k & 1] = abort_flag;
+        named_barrier(1 + group, 128);
+        const int stop = group_stop[group][k & 1];
+        if (leader && !stop) {
+          for (int q = 0; q < p.panels; ++q)
+            if (n0 + q * 128 < p.oc) tma_store_2d(&tmap_y, io_base + (size_t)q * panel_size, n0 + q * 128, m0);
+          tma_store_wait_read();  // the other group keeps the SM busy meanwhile
+          const int nt = tile + stride_tiles;
+          if (nt < num_tiles) {
+            if (has_res) {
+              mbar_expect_tx(&bar_res[group], (uint32_t)(p.panels * panel_size));
+              for (int q = 0; q < p.panels; ++q)
+                tma_load_2d(io_base + (size_t)q * panel_size, &tmap_r, &bar_res[group],
+                            (nt % p.num_n_tiles) * p.block_n + q * 128, (nt / p.num_n_tiles) * BLOCK_M);
+            } else {
+              mbar_arrive(&bar_res[group]);
+            }
+          }
+        }
         if (stop) break;
       } else if (abort_flag) {
         break;
       }
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
     }
     if (p.tma_out && leader) tma_store_wait_all();
   }
@@ -634,7 +626,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   }
   plan->panels = bn == 256 ? 2 : 1;
   plan->panel_bytes = bn < 128 ? bn : 128;
-  plan->io_bufs = plan->res_step >= 0 ? 2 : 1;
+  plan->io_bufs = 2;  // one staging set per epilogue group
   const int io_bytes = plan->tma_out ? plan->panels * plan->io_bufs * BLOCK_M * plan->panel_bytes : 0;
   const int stage_bytes = (BLOCK_M + bn) * bk;
   int stages = (SMEM_DYNAMIC_MAX - 1024 - io_bytes) / stage_bytes;
@@ -713,6 +705,15 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.io_bufs = plan->io_bufs; p.ring_bytes = plan->ring_bytes;
   int rc = lower_chain(d.ep, &p.chain);
   if (rc != CVMK_OK) return rc;
+  // lower_chain() may merge steps: find the TMA-served operand again by its pointer.
+  if (plan->res_step >= 0) {
+    const void* want = d.ep.s[plan->res_step].ptr;
+    p.res_step = -1;
+    for (int i = 0; i < p.chain.n; ++i)
+      if ((p.chain.s[i].op == K_ADD_T || p.chain.s[i].op == K_SUB_T || p.chain.s[i].op == K_RSUB_T) &&
+          p.chain.s[i].ptr == want) { p.res_step = i; break; }
+    if (p.res_step < 0) { set_error("conv2d_tc_launch: tensor operand lost while lowering the chain"); return CVMK_ERR_ARG; }
+  }
   // A leading per-channel add is the bias: the kernel keeps it in shared memory.
   p.bias = nullptr;
   p.first_step = 0;
