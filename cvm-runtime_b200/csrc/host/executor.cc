@@ -66,6 +66,9 @@ struct Lowering {
   std::vector<DevBuf> buf;
   std::vector<int> uses;
   std::vector<char> is_head, safe8, absorbed;
+  uint32_t data_eid = 0;
+  DevBuf raw_in;          // the input exactly as the C-ABI delivers it (row-major int8 / int32)
+  int32_t data_range = 127;
 
   Lowering(Executor& e, const Graph& gr) : ex(e), g(gr) {}
 
@@ -351,7 +354,7 @@ struct Lowering {
     const bool depthwise = !dense && groups == C && OC == C && C % 16 == 0 && safe8[ex_];
     // Few-channel convolutions (image stems): gather patches into a [M, Kp] matrix, then run the
     // tensor-core kernel on it as a 1x1 convolution.
-    const int kflat = KH * KW * icg, kp = (kflat + 31) / 32 * 32;
+    const int kflat = KH * KW * icg, kp = kflat > 64 ? (kflat + 63) / 64 * 64 : (kflat + 31) / 32 * 32;
     cvmk_conv_desc packed = probe;
     packed.N = N * OH * OW; packed.H = packed.W = 1; packed.C = kp; packed.KH = packed.KW = 1;
     packed.OH = packed.OW = 1; packed.stride_h = packed.stride_w = 1; packed.pad_h = packed.pad_w = 0;
@@ -380,15 +383,28 @@ struct Lowering {
     CUDA_OK(cudaMemcpy(wdev, w8.data(), w8.size(), cudaMemcpyHostToDevice));
 
     if (via_pack) {
-      DevBuf& xin = materialize(ex_);
       int8_t* amat = (int8_t*)ex.dalloc((size_t)packed.N * kp);
+      cvmk_stem_pack_desc sp;
+      memset(&sp, 0, sizeof(sp));
+      sp.x = (const int8_t*)raw_in.ptr; sp.a = amat;
+      sp.N = N; sp.H = H; sp.W = W; sp.C = C; sp.KH = KH; sp.KW = KW; sp.OH = OH; sp.OW = OW;
+      sp.stride_h = sh; sp.stride_w = sw; sp.pad_h = ph; sp.pad_w = pw; sp.dil_h = dh; sp.dil_w = dw;
+      sp.Kp = kp; sp.clamp = data_range;
+      const bool from_raw = ex_ == data_eid && raw_in.dtype == CVMK_I8 && cvmk_stem_pack_supported(&sp) &&
+                            !getenv("CVM_B200_NO_STEM_PACK");
+      if (from_raw) {  // gather straight from the NCHW input: no channels-last copy of it is needed
+        add_step(label + "[stem_pack]", [sp](cudaStream_t s) { return cvmk_stem_pack(&sp, s); });
+      }
+      DevBuf xin_holder;
+      if (!from_raw) xin_holder = materialize(ex_);
+      const DevBuf& xin = xin_holder;
       cvmk_im2col_desc pk;
       memset(&pk, 0, sizeof(pk));
       pk.x = (const int8_t*)xin.ptr; pk.a = amat;
       pk.N = N; pk.H = H; pk.W = W; pk.C = C; pk.KH = KH; pk.KW = KW; pk.OH = OH; pk.OW = OW;
       pk.stride_h = sh; pk.stride_w = sw; pk.pad_h = ph; pk.pad_w = pw; pk.dil_h = dh; pk.dil_w = dw;
       pk.Kp = kp;
-      add_step(label + "[pack]", [pk](cudaStream_t s) { return cvmk_im2col_pack(&pk, s); });
+      if (!from_raw) add_step(label + "[pack]", [pk](cudaStream_t s) { return cvmk_im2col_pack(&pk, s); });
       cvmk_conv_desc d = packed;
       d.x = amat; d.w = wdev; d.y = out.ptr; d.y_dtype = out.dtype;
       d.status = ex.status_dev_;
@@ -727,25 +743,17 @@ struct Lowering {
     {
       const uint32_t eid = g.entry_id(data_nid, 0);
       const int prec = g.precision[eid];
-      DevBuf& dst = materialize(eid);
-      DevBuf raw;
-      raw.shape = g.shape[eid];
-      raw.dtype = prec > 8 ? CVMK_I32 : CVMK_I8;
-      raw.nhwc = false;
-      ex.in_bytes_ = raw.bytes();
+      data_eid = eid;
+      raw_in.shape = g.shape[eid];
+      raw_in.dtype = prec > 8 ? CVMK_I32 : CVMK_I8;
+      raw_in.nhwc = false;
+      ex.in_bytes_ = raw_in.bytes();
       ex.in_dev_ = ex.dalloc(ex.in_bytes_);
       CUDA_OK(cudaMallocHost(&ex.in_host_, ex.in_bytes_));
       memset(ex.in_host_, 0, ex.in_bytes_);
       ex.pinned_.push_back(ex.in_host_);
-      raw.ptr = ex.in_dev_;
-      cvmk_epilogue ep;
-      memset(&ep, 0, sizeof(ep));
-      const int32_t range = (int32_t)((1u << (prec - 1)) - 1);
-      ep.n = 1;
-      ep.s[0].op = CVMK_EP_CLIP;
-      ep.s[0].a = -range;
-      ep.s[0].b = range;
-      emit_convert(raw, dst, "input:data", &ep);  // graph_runtime.cc:379-386
+      raw_in.ptr = ex.in_dev_;
+      data_range = (int32_t)((1u << (prec - 1)) - 1);
     }
     // Fused groups are emitted at the position of their last member, so every operand of the
     // chain already exists when the kernel runs.
@@ -771,6 +779,17 @@ struct Lowering {
       }
       std::stable_sort(order.begin(), order.end());
       ex.steps_ = prologue;
+      if (buf[data_eid].ptr || is_head[data_eid]) {
+        // some consumer reads the input tensor itself: raw API bytes -> clamp to the declared
+        // precision (graph_runtime.cc:379-386) -> the entry's own layout
+        cvmk_epilogue ep;
+        memset(&ep, 0, sizeof(ep));
+        ep.n = 1;
+        ep.s[0].op = CVMK_EP_CLIP;
+        ep.s[0].a = -data_range;
+        ep.s[0].b = data_range;
+        emit_convert(raw_in, materialize(data_eid), "input:data", &ep);
+      }
       for (const auto& pr : order)
         for (auto& s : per_root[pr.second]) ex.steps_.push_back(std::move(s));
     }

@@ -181,6 +181,85 @@ __global__ void __launch_bounds__(256) im2col_pack_kernel(const __grid_constant_
   }
 }
 
+
+// Patch gather straight from the NCHW network input.  One CTA per (image, output row): the KH
+// input rows of every channel are staged (clamped, zero-padded left and right) in shared memory,
+// then warp q builds the q-th 16-byte chunk of the A rows of that output row, 32 pixels at a time.
+struct StemParams {
+  const int8_t* x; int8_t* a;
+  int N, H, W, C, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw, Kp, K, clamp, wp;
+};
+__global__ void __launch_bounds__(512) stem_pack_kernel(const __grid_constant__ StemParams p) {
+  extern __shared__ __align__(16) int8_t srow[];  // [KH][C][wp], wp = W + 2 * pw
+  const int n = blockIdx.x / p.OH, oy = blockIdx.x % p.OH;
+  const int iy0 = oy * p.sh - p.ph;
+  const int total = p.KH * p.C * p.wp;
+  const bool vec = (p.W % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+  if (vec) {
+    // zero everything (padding columns, rows outside the image), then one 16-byte global load per
+    // thread and row piece: all loads of a CTA are in flight together
+    for (int i = threadIdx.x; i < (total + 3) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(srow)[i] = 0;
+    __syncthreads();
+    const int vpr = p.W / 16;  // vectors per input row
+    const int tasks = p.KH * p.C * vpr;
+    for (int i = threadIdx.x; i < tasks; i += blockDim.x) {
+      const int vx = i % vpr;
+      const int c = (i / vpr) % p.C;
+      const int r = i / (vpr * p.C);
+      const int iy = iy0 + r * p.dh;
+      if (iy < 0 || iy >= p.H) continue;
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.x + (((int64_t)n * p.C + c) * p.H + iy) * p.W) + vx);
+      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+      int8_t* dst = srow + (r * p.C + c) * p.wp + p.pw + vx * 16;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        int v = (int)(int8_t)(w4[j >> 2] >> ((j & 3) * 8));
+        dst[j] = (int8_t)max(min(v, p.clamp), -p.clamp);
+      }
+    }
+  } else {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+      const int xx = i % p.wp - p.pw;
+      const int c = (i / p.wp) % p.C;
+      const int iy = iy0 + (i / (p.wp * p.C)) * p.dh;
+      int v = 0;
+      if (xx >= 0 && xx < p.W && iy >= 0 && iy < p.H) {
+        v = __ldg(p.x + (((int64_t)n * p.C + c) * p.H + iy) * p.W + xx);
+        v = max(min(v, p.clamp), -p.clamp);
+      }
+      srow[i] = (int8_t)v;
+    }
+  }
+  __syncthreads();
+  // blockDim.x is a multiple of the chunk count, so a thread always builds the same chunk q and
+  // consecutive threads write consecutive 16-byte pieces of the (contiguous) A rows of this
+  // output row.
+  const int chunks = p.Kp / 16;
+  const int q = threadIdx.x % chunks;
+  const int ox_step = blockDim.x / chunks;
+  int off[16];  // shared-memory offset of byte j of this chunk for output pixel 0, -1: zero
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int k = q * 16 + j;
+    if (k < p.K) {
+      const int fy = k / (p.KW * p.C), r = k - fy * (p.KW * p.C);
+      const int fx = r / p.C, c = r - fx * p.C;
+      off[j] = (fy * p.C + c) * p.wp + fx * p.dw;
+    } else {
+      off[j] = -1;
+    }
+  }
+  int8_t* arow = p.a + (((int64_t)n * p.OH + oy) * p.OW) * p.Kp + q * 16;
+  for (int ox = threadIdx.x / chunks; ox < p.OW; ox += ox_step) {
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (off[j] >= 0) w[j >> 2] |= (uint32_t)(uint8_t)srow[off[j] + ox * p.sw] << ((j & 3) * 8);
+    *reinterpret_cast<uint4*>(arow + (int64_t)ox * p.Kp) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 int grid_sized(int64_t work, int threads) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -244,4 +323,36 @@ extern "C" int cvmk_im2col_pack(const cvmk_im2col_desc* d, cvmk_stream_t stream)
   p.total = (int64_t)d->N * d->OH * d->OW * (d->Kp / 16);
   im2col_pack_kernel<<<grid_sized(p.total, 256), 256, p.K * sizeof(int), (cudaStream_t)stream>>>(p);
   return check_cuda(cudaGetLastError(), "im2col_pack_kernel launch");
+}
+
+extern "C" int cvmk_stem_pack_supported(const cvmk_stem_pack_desc* d) {
+  if (!d) return 0;
+  if (d->C < 1 || d->C > 4 || d->Kp % 16 || d->KH * d->KW * d->C > d->Kp) return 0;
+  if ((int64_t)d->KH * d->C * (d->W + 2 * d->pad_w) > 48 * 1024) return 0;
+  if ((int64_t)d->N * d->OH > INT32_MAX) return 0;
+  return 1;
+}
+
+extern "C" int cvmk_stem_pack(const cvmk_stem_pack_desc* d, cvmk_stream_t stream) {
+  if (!d || !d->x || !d->a || !cvmk_stem_pack_supported(d) || ((uintptr_t)d->a & 15)) {
+    set_error("stem_pack: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  StemParams p;
+  p.x = d->x; p.a = d->a;
+  p.N = d->N; p.H = d->H; p.W = d->W; p.C = d->C; p.KH = d->KH; p.KW = d->KW; p.OH = d->OH; p.OW = d->OW;
+  p.sh = d->stride_h; p.sw = d->stride_w; p.ph = d->pad_h; p.pw = d->pad_w; p.dh = d->dil_h; p.dw = d->dil_w;
+  p.Kp = d->Kp; p.K = d->KH * d->KW * d->C; p.clamp = d->clamp;
+  // right padding also covers the taps of the last output pixel
+  const int reach = (d->OW - 1) * d->stride_w + (d->KW - 1) * d->dil_w + 1;
+  p.wp = d->W + 2 * d->pad_w;
+  if (reach > p.wp) p.wp = reach;
+  const int smem = d->KH * d->C * p.wp;
+  if (smem > 48 * 1024) { set_error("stem_pack: input rows do not fit shared memory"); return CVMK_ERR_UNSUPPORTED; }
+  const int chunks = d->Kp / 16;
+  int threads = chunks * 32;             // a multiple of the chunk count, see the kernel
+  while (threads > 512) threads -= chunks;
+  if (chunks > 512) { set_error("stem_pack: Kp too large"); return CVMK_ERR_UNSUPPORTED; }
+  stem_pack_kernel<<<d->N * d->OH, threads, smem, (cudaStream_t)stream>>>(p);
+  return check_cuda(cudaGetLastError(), "stem_pack_kernel launch");
 }

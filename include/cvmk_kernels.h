@@ -234,6 +234,21 @@ typedef struct {
 } cvmk_im2col_desc;
 CVMK_API int cvmk_im2col_pack(const cvmk_im2col_desc* d, cvmk_stream_t stream);
 
+/* Same gather, reading the network input as the C-ABI delivers it: int8 NCHW [N, C, H, W] with
+ * C <= 4, each value clamped to [-clamp, clamp] on the way (the input clamp of
+ * CvmRuntime::SetInput, src/runtime/graph_runtime.cc:379-386).  One CTA stages the KH input rows
+ * of one output row in shared memory; needs KH * C * (W + 2 * pad_w) <= 48 KB. */
+typedef struct {
+  const int8_t* x;
+  int8_t* a;
+  int32_t N, H, W, C, KH, KW, OH, OW;
+  int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int32_t Kp;
+  int32_t clamp;
+} cvmk_stem_pack_desc;
+CVMK_API int cvmk_stem_pack_supported(const cvmk_stem_pack_desc* d);
+CVMK_API int cvmk_stem_pack(const cvmk_stem_pack_desc* d, cvmk_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * get_valid_counts (cpu/ops/nms.cc:42-63): per batch keep rows with row[1] > score_threshold in
  * their original order, write their number to valid_count[b], fill the remaining rows with -1.
