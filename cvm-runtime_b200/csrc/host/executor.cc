@@ -350,6 +350,21 @@ struct Lowering {
     probe.N = N; probe.H = H; probe.W = W; probe.C = C; probe.OC = OC; probe.KH = KH; probe.KW = KW;
     probe.OH = OH; probe.OW = OW; probe.stride_h = sh; probe.stride_w = sw; probe.pad_h = ph; probe.pad_w = pw;
     probe.dil_h = dh; probe.dil_w = dw;
+    // |sum + bias| can never exceed this: int8 operands (|x| <= 128 even after a narrowing view)
+    // and the bias values themselves when they are parameters.
+    {
+      int64_t bias_max = 0;
+      if (use_bias) {
+        const uint32_t eb = g.entry_id(n.inputs[2]);
+        auto bit = g.params.find(eb);
+        if (bit != g.params.end()) {
+          for (int32_t v : bit->second.data) bias_max = std::max<int64_t>(bias_max, std::llabs((long long)v));
+        } else {
+          bias_max = ((int64_t)1 << (g.precision[eb] - 1)) - 1;
+        }
+      }
+      probe.acc_bound = (int64_t)icg * KH * KW * 128 * 128 + bias_max;
+    }
     const bool tc = groups == 1 && cvmk_conv2d_tc_supported(&probe) && !getenv("CVM_B200_NO_TC");
     const bool depthwise = !dense && groups == C && OC == C && C % 16 == 0 && safe8[ex_];
     // Few-channel convolutions (image stems): gather patches into a [M, Kp] matrix, then run the

@@ -634,6 +634,172 @@ bool gvc_prec(const Attrs& a, const std::vector<Shape>& shapes, std::vector<int>
   return true;
 }
 
+// RepeatShape, src/top/tensor/transform.cc:22-49
+bool repeat_shape(const Attrs& a, std::vector<Shape>* in, std::vector<Shape>* out) {
+  VERIFY_EQ(in->size(), 1U);
+  VERIFY_EQ(out->size(), 1U);
+  const Shape& s = (*in)[0];
+  const int ndim = (int)s.size();
+  VERIFY_GT(a.i("repeats"), 0) << "operator " << a.name << " repeats:" << a.i("repeats") << " must greater than 0";
+  verify_attr_range(a.i("axis"), "repeat.axis", -ndim, ndim - 1);
+  const int pivot = a.i("axis") < 0 ? ndim + (int)a.i("axis") : (int)a.i("axis");
+  Shape o = s;
+  o[pivot] = s[pivot] * a.i("repeats");
+  (*out)[0] = o;
+  return true;
+}
+
+// TileShape, src/top/tensor/transform.cc:72-99
+bool tile_shape(const Attrs& a, std::vector<Shape>* in, std::vector<Shape>* out) {
+  VERIFY_EQ(in->size(), 1U);
+  VERIFY_EQ(out->size(), 1U);
+  const Shape& s = (*in)[0];
+  const Shape& reps = a.t("reps");
+  const size_t sdim = s.size(), rdim = reps.size();
+  VERIFY(rdim > 0) << "repetition array is not defined. data.ndim = " << sdim;
+  for (int64_t r : reps) verify_attr_range(r, "tile.reps", 1);
+  const size_t odim = std::max(sdim, rdim);
+  Shape o(odim);
+  for (size_t i = 0; i < odim; ++i) {
+    const int64_t sv = i < sdim ? s[sdim - 1 - i] : 1;
+    const int64_t rv = i < rdim ? reps[rdim - 1 - i] : 1;
+    o[odim - 1 - i] = sv * rv;
+  }
+  (*out)[0] = o;
+  return true;
+}
+
+// TransposeShape, src/top/tensor/transform.cc:635-666
+bool transpose_shape(const Attrs& a, std::vector<Shape>* in, std::vector<Shape>* out) {
+  VERIFY_EQ(in->size(), 1U);
+  VERIFY_EQ(out->size(), 1U);
+  const Shape& s = (*in)[0];
+  const int ndim = (int)s.size();
+  Shape axes = a.t("axes");
+  Shape o(ndim);
+  if (axes.empty()) {
+    for (int i = 0; i < ndim; ++i) o[i] = s[ndim - 1 - i];
+  } else {
+    VERIFY_EQ(s.size(), axes.size());
+    for (int i = 0; i < ndim; ++i) {
+      int64_t ax = axes[i];
+      verify_attr_range(ax, "transpose.axis", -ndim, ndim - 1);
+      if (ax < 0) { ax += ndim; axes[i] = ax; }
+      for (int j = 0; j < ndim; ++j)
+        if (i != j) VERIFY(ax != axes[j]) << "repeated axis in transpose";
+      o[i] = s[ax];
+    }
+  }
+  (*out)[0] = o;
+  return true;
+}
+
+// StridedSliceInferShape, src/top/tensor/transform.cc:755-799
+bool strided_slice_shape(const Attrs& a, std::vector<Shape>* in, std::vector<Shape>* out) {
+  const Shape& d = (*in)[0];
+  const size_t nd = d.size();
+  Shape b = a.t("begin"), e = a.t("end"), st = a.t("stride");
+  for (size_t i = b.size(); i < nd; ++i) b.push_back(0);
+  for (size_t i = e.size(); i < nd; ++i) e.push_back(d[i]);
+  for (size_t i = st.size(); i < nd; ++i) st.push_back(1);
+  Shape o = d;
+  for (size_t i = 0; i < nd; ++i) {
+    VERIFY(st[i] != 0);
+    const int64_t lo = st[i] < 0 ? -1 : 0, hi = st[i] < 0 ? d[i] - 1 : d[i];
+    int64_t bg = b[i] < 0 ? d[i] + b[i] : b[i];
+    int64_t en = e[i] < 0 ? d[i] + e[i] : e[i];
+    bg = std::min(std::max(bg, lo), hi);
+    en = std::min(std::max(en, lo), hi);
+    const int interval = (int)std::llabs(en - bg);
+    const int size = (int)((interval + std::llabs(st[i]) - 1) / std::llabs(st[i]));
+    VERIFY(st[i] < 0 ? (en < bg) : (bg < en))
+        << ": Input [Begin=" << b[i] << ", End=" << e[i] << "] is invalid for axis=" << i;
+    o[i] = size;
+  }
+  (*out)[0] = o;
+  return true;
+}
+
+// TakeInferShape, src/top/tensor/transform.cc:840-875
+bool take_shape(const Attrs& a, std::vector<Shape>* in, std::vector<Shape>* out) {
+  VERIFY_EQ(in->size(), 2U);
+  VERIFY_EQ(out->size(), 1U);
+  const Shape &d = (*in)[0], &idx = (*in)[1];
+  const int ndim = (int)d.size();
+  Shape o;
+  if (!a.has.at("axis")) {
+    o = idx;
+  } else {
+    int axis = (int)a.i("axis");
+    verify_attr_range(axis, "take.axis", -ndim, ndim - 1);
+    if (axis < 0) axis += ndim;
+    for (int i = 0; i < ndim; ++i) {
+      if (i == axis) o.insert(o.end(), idx.begin(), idx.end());
+      else o.push_back(d[i]);
+    }
+  }
+  (*out)[0] = o;
+  return shape_size(d) != 0;
+}
+
+// LUTInferShape / LUTInferPrecision, src/top/tensor/transform.cc:945-996
+bool lut_shape(const Attrs& a, std::vector<Shape>* in, std::vector<Shape>* out) {
+  VERIFY_EQ(in->size(), 2U);
+  VERIFY_EQ(out->size(), 1U);
+  VERIFY_EQ(shape_size((*in)[1]), a.i("in_dim"));
+  (*out)[0] = (*in)[0];
+  return true;
+}
+bool lut_prec(const Attrs& a, const std::vector<Shape>&, std::vector<int>* ip, std::vector<int>* op) {
+  in_prec_check(a, *ip);
+  (*op)[0] = ip->at(1);
+  return true;
+}
+
+// SliceLikeShape, src/top/tensor/transform.cc:1017-1054
+bool slice_like_shape(const Attrs& a, std::vector<Shape>* in, std::vector<Shape>* out) {
+  VERIFY_EQ(in->size(), 2U);
+  VERIFY_EQ(out->size(), 1U);
+  const Shape &src = (*in)[0], &target = (*in)[1];
+  const Shape& axis = a.t("axis");
+  VERIFY(src.size() == target.size() || !axis.empty())
+      << "input X and shape_like must be of the same shape if no axis is given";
+  Shape end = src;
+  if (axis.empty()) {
+    for (size_t i = 0; i < src.size(); ++i) {
+      if (i < target.size()) {
+        end[i] = target[i];
+        VERIFY_LE(end[i], src[i]) << "End index of axis " << i << " exceeds input shape: " << end[i] << " vs " << src[i];
+      }
+    }
+  } else {
+    for (int64_t i : axis) {
+      if (i < 0) i += (int64_t)src.size();
+      verify_attr_range(i, "slice_like.axis", 0, (int64_t)std::min(target.size(), src.size()) - 1);
+      end[i] = target[i];
+      VERIFY_LE(end[i], src[i]) << "End index of axis " << i << " exceeds input shape: " << end[i] << " vs " << src[i];
+    }
+  }
+  (*out)[0] = end;
+  return true;
+}
+
+// WhereShape, src/top/tensor/transform.cc:1059-1079
+bool where_shape(const Attrs&, std::vector<Shape>* in, std::vector<Shape>* out) {
+  VERIFY_EQ(in->size(), 3U);
+  VERIFY_EQ(out->size(), 1U);
+  const Shape &c = (*in)[0], &x = (*in)[1], &y = (*in)[2];
+  VERIFY(x == y) << "x and y must have the same shape: " << shape_str(x) << " vs " << shape_str(y);
+  if (c != x) {
+    VERIFY_EQ(c.size(), 1U) << "Shape of condition " << shape_str(c)
+                            << " must be either equal to x or has dimension of 1.";
+    VERIFY_EQ(c[0], x[0]) << "If dim of condition is 1, " << shape_str(c)
+                          << " must be the same as the first dimension of input shape.";
+  }
+  (*out)[0] = x;
+  return true;
+}
+
 #define REQ(n, k) {n, k, true, "", false, 0}
 #define REQ_LB(n, k, lb) {n, k, true, "", true, lb}
 #define OPT(n, k, d) {n, k, false, d, false, 0}
@@ -734,6 +900,16 @@ std::vector<OpDef> build_table() {
   bcast("broadcast_max", max_in_precision);        // :218-234
   bcast("broadcast_div", same_precision);          // :236-252
   bcast("broadcast_greater", same_precision);      // :254-269
+  t.push_back({"repeat", 1, 1, true, {REQ("repeats", F_INT), OPT("axis", F_INT, "0")}, repeat_shape, same_precision, false});
+  t.push_back({"tile", 1, 1, true, {OPT("reps", F_TUPLE, "(0,)")}, tile_shape, same_precision, false});
+  t.push_back({"transpose", 1, 1, true, {OPT("axes", F_TUPLE, "()")}, transpose_shape, same_precision, false});
+  t.push_back({"strided_slice", 1, 1, true,
+               {OPT("begin", F_TUPLE, "(0,)"), OPT("end", F_TUPLE, "(1,)"), OPT("stride", F_TUPLE, "()")},
+               strided_slice_shape, same_precision, false});
+  t.push_back({"take", 2, 1, true, {{"axis", F_OPT_INT, false, "None", false, 0}}, take_shape, same_precision, false});
+  t.push_back({"cvm_lut", 2, 1, true, {REQ("in_dim", F_INT)}, lut_shape, lut_prec, false});
+  t.push_back({"slice_like", 2, 1, true, {OPT("axis", F_TUPLE, "()")}, slice_like_shape, same_precision, false});
+  t.push_back({"where", 3, 1, false, {}, where_shape, same_precision, false});  // SamePrecision: follows the condition
   t.push_back({"get_valid_counts", 1, 2, true, {OPT("score_threshold", F_INT, "0")}, gvc_shape, gvc_prec, false});
   t.push_back({"non_max_suppression", 2, 1, true,
                {OPT("max_output_size", F_INT, "-1"), OPT("iou_threshold", F_INT, "50"),

@@ -26,7 +26,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
+#include <algorithm>
 #include "common.cuh"
 
 namespace cvmk {
@@ -60,6 +62,13 @@ struct ConvParams {
   int panel_bytes;      // row length of a panel in bytes: min(block_n, 128)
   int io_bufs;          // staging buffers per panel: 1 or 2
   int ring_bytes;       // bytes of the operand ring (the staging buffers follow it)
+  // Requantisation fast path (see fast_requant below): 0 off, 1 shift+clamp, 2 + tensor add/sub + clamp
+  int fast_mode;
+  int f_shift;          // rounding shift; its addend 2^(shift-1) is folded into the staged bias
+  int f_add;
+  uint32_t f_lo1, f_hi1;  // first clamp, both halves of an s16x2 word
+  uint32_t f_lo2, f_hi2;  // clamp after the tensor step
+  int f_sub;            // tensor step subtracts its operand
   DevChain chain;
 };
 
@@ -247,6 +256,59 @@ __device__ __forceinline__ uint32_t panel_offset(int row, int j, int pw) {
   return lin ^ (((lin >> 7) & mask) << 4);
 }
 
+// Byte permute with the full selector semantics of the instruction: a selector nibble with its top
+// bit set replicates the sign of the chosen byte (the __byte_perm() intrinsic documents only the low
+// three bits of each nibble).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
+// Requantisation of 32 accumulators to int8 when the caller has proven that the biased sums cannot
+// overflow and fit 16 bits after the shift:  t = (acc + bias + 2^(s-1)) >> s  is computed in 32
+// bits, then pairs are packed into s16x2 words and everything else runs two elements per
+// instruction: clamp, the add / subtract of the int8 tensor operand (sign-extended by a byte
+// permute), the final clamp (one fused add-min-relu when its lower bound is 0), and the pack to
+// bytes.  Same values as the step-by-step chain: every clamp commutes with the monotone shift, and
+// all intermediate values are exact in 16 bits.
+__device__ __forceinline__ void fast_requant(const ConvParams& p, const int32_t (&v)[32], const uint4& r0,
+                                             const uint4& r1, uint4* o0, uint4* o1) {
+  uint32_t h[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    h[j] = __byte_perm((uint32_t)(v[2 * j] >> p.f_shift), (uint32_t)(v[2 * j + 1] >> p.f_shift), 0x5410);
+  if (p.f_lo1 == 0) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) h[j] = __vimin_s16x2_relu(h[j], p.f_hi1);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) h[j] = __vmaxs2(__vmins2(h[j], p.f_hi1), p.f_lo1);
+  }
+  if (p.fast_mode == 2) {
+    const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint32_t ra = prmt(rw[q], 0, 0x9180);  // bytes 0,1 sign-extended to 16 bits
+      const uint32_t rb = prmt(rw[q], 0, 0xB3A2);  // bytes 2,3
+      if (!p.f_sub && p.f_lo2 == 0) {
+        h[2 * q] = __viaddmin_s16x2_relu(h[2 * q], ra, p.f_hi2);
+        h[2 * q + 1] = __viaddmin_s16x2_relu(h[2 * q + 1], rb, p.f_hi2);
+      } else {
+        const uint32_t xa = p.f_sub ? __vsub2(h[2 * q], ra) : __vadd2(h[2 * q], ra);
+        const uint32_t xb = p.f_sub ? __vsub2(h[2 * q + 1], rb) : __vadd2(h[2 * q + 1], rb);
+        h[2 * q] = __vmaxs2(__vmins2(xa, p.f_hi2), p.f_lo2);
+        h[2 * q + 1] = __vmaxs2(__vmins2(xb, p.f_hi2), p.f_lo2);
+      }
+    }
+  }
+  uint32_t w[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) w[q] = __byte_perm(h[2 * q], h[2 * q + 1], 0x6420);
+  *o0 = make_uint4(w[0], w[1], w[2], w[3]);
+  *o1 = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
@@ -272,7 +334,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int k_per_tap = p.c / p.block_k;
   const int num_kb = p.kh * p.kw * k_per_tap;
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
-  const bool bias_in_smem = p.bias != nullptr && p.oc <= MAX_BIAS;
+  const bool bias_in_smem = (p.bias != nullptr || p.fast_mode) && p.oc <= MAX_BIAS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -290,7 +352,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
   if (bias_in_smem) {
     const int padded = min(MAX_BIAS, (p.oc + 31) & ~31);
-    for (int i = threadIdx.x; i < padded; i += NUM_THREADS) bias_s[i] = i < p.oc ? __ldg(p.bias + i) : 0;
+    for (int i = threadIdx.x; i < padded; i += NUM_THREADS)
+      bias_s[i] = (i < p.oc && p.bias ? __ldg(p.bias + i) : 0) + (p.fast_mode ? p.f_add : 0);
   }
   if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
   tc_fence_before();
@@ -408,7 +471,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int c0 = 0; c0 < p.block_n; c0 += 32) {
           const int col0 = n0 + c0;
           if (col0 >= p.oc) break;  // uniform across the warp
-          if (p.bias) {
+          if (p.bias || p.fast_mode) {
             if (bias_in_smem) {
               const int4* bp = reinterpret_cast<const int4*>(bias_s + col0);
 #pragma unroll
@@ -427,6 +490,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int j0 = (c0 & 127) >> 4;  // first 16-byte chunk of this thread inside the panel row
             uint4* q0 = reinterpret_cast<uint4*>(pb + panel_offset(row_in_tile, j0, pw));
             uint4* q1 = reinterpret_cast<uint4*>(pb + panel_offset(row_in_tile, j0 + 1, pw));
+            if (p.fast_mode) {
+              uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
+              if (p.fast_mode == 2) { r0 = *q0; r1 = *q1; }
+              uint4 a, b;
+              fast_requant(p, v, r0, r1, &a, &b);
+              *q0 = a;
+              *q1 = b;
+              if (c0 + 32 < p.block_n && n0 + c0 + 32 < p.oc) tmem_ld32(tbase + (uint32_t)(c0 + 32), v);
+              continue;
+            }
             if (row < p.m_total) {
               if (has_res) {
                 int32_t rv[32];
@@ -720,6 +793,42 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   if (p.chain.n > 0 && p.chain.s[0].op == K_ADD_C) {
     p.bias = reinterpret_cast<const int32_t*>(p.chain.s[0].ptr);
     p.first_step = 1;
+  }
+
+  // Packed requantisation: chain = [bias] rs_clamp [add_t|sub_t (the TMA-served operand) clip].
+  p.fast_mode = 0;
+  if (p.tma_out && d.acc_bound > 0 && d.OC <= MAX_BIAS && !getenv("CVM_B200_NO_FAST_REQUANT")) {
+    const int i0 = p.first_step;
+    const int left = p.chain.n - i0;
+    if (left >= 1 && p.chain.s[i0].op == K_RS_CLAMP) {
+      const DevStep& rs = p.chain.s[i0];
+      const int64_t add = rs.c;
+      const int sh = rs.d;
+      const int64_t lo1 = ((int64_t)rs.a + add) >> sh, hi1 = ((int64_t)rs.b + add) >> sh;
+      const bool no_overflow = d.acc_bound + add < (int64_t)INT32_MAX;
+      const bool fits16 = ((d.acc_bound + add) >> sh) < 32767;
+      const bool clamp_ok = lo1 >= -32767 && hi1 <= 32767 && lo1 <= hi1;
+      if (no_overflow && fits16 && clamp_ok) {
+        auto x2 = [](int64_t v) { return (uint32_t)((uint32_t)(uint16_t)(int16_t)v | ((uint32_t)(uint16_t)(int16_t)v << 16)); };
+        if (left == 1) {
+          p.fast_mode = 1;
+        } else if (left == 3 && p.res_step == i0 + 1 && p.chain.s[i0 + 2].op == K_CLIP &&
+                   (p.chain.s[i0 + 1].op == K_ADD_T || p.chain.s[i0 + 1].op == K_SUB_T) &&
+                   p.chain.s[i0 + 2].a >= -32767 && p.chain.s[i0 + 2].b <= 32767 &&
+                   std::max(std::abs(lo1), std::abs(hi1)) + 128 < 32767) {
+          p.fast_mode = 2;
+          p.f_sub = p.chain.s[i0 + 1].op == K_SUB_T;
+          p.f_lo2 = x2(p.chain.s[i0 + 2].a);
+          p.f_hi2 = x2(p.chain.s[i0 + 2].b);
+        }
+        if (p.fast_mode) {
+          p.f_shift = sh;
+          p.f_add = (int)add;
+          p.f_lo1 = x2(lo1);
+          p.f_hi1 = x2(hi1);
+        }
+      }
+    }
   }
 
   static bool attr_set_dev[64] = {false};

@@ -112,6 +112,10 @@ typedef struct {
   int32_t OH, OW;
   int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int32_t* status;
+  /* Upper bound on |sum + bias| over every output element, proven by the caller from the operand
+   * ranges (0 = unknown).  When it shows that the rounding shift cannot overflow and that its
+   * result fits 16 bits, the kernel requantises two elements per instruction. */
+  int64_t acc_bound;
   cvmk_epilogue ep;
 } cvmk_conv_desc;
 

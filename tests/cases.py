@@ -86,6 +86,29 @@ def op_cases():
     add("conv_depthwise_s2", lambda: conv_case(9, 1, 48, 9, 9, 48, 3, 2, 1, groups=48, shift=6))
     add("conv_grouped", lambda: conv_case(10, 1, 12, 7, 7, 8, 3, 1, 0, groups=4, shift=7))
 
+    def join_case(seed, sub, relu, clip_attrs, other_first=False, oc=64):
+        """conv -> cvm_right_shift -> elemwise add/sub with a second int8 tensor -> [relu] -> clip:
+        the residual join that the executor folds into the convolution."""
+        def f():
+            rng = np.random.RandomState(seed)
+            g = wl.GraphBuilder(seed)
+            x = rnd(rng, (2, 32, 9, 7), 8)
+            d = g.var("data", x.shape, 8)
+            y = g.conv(d, oc, 3, 1, 1, relu=False, shift=9)
+            other = g.var("res", g.shape_of(y), 8, rnd(rng, g.shape_of(y), 8))
+            ins = [other, y] if other_first else [y, other]
+            z = g.op("elemwise_sub" if sub else "elemwise_add", ins, g.shape_of(y))
+            if relu:
+                z = g.op("relu", [z], g.shape_of(z))
+            z = g.op(clip_attrs[0], [z], g.shape_of(z), clip_attrs[1])
+            js, pb = g.finish(z)
+            return js, pb, x
+        return f
+    add("conv_join_add_relu_clip", join_case(13, False, True, ("cvm_clip", {"precision": 8})))
+    add("conv_join_sub_clip", join_case(14, True, False, ("clip", {"a_min": -100, "a_max": 90})))
+    add("conv_join_rsub_clip", join_case(15, True, False, ("cvm_clip", {"precision": 7}), other_first=True))
+    add("conv_join_add_oc48", join_case(16, False, True, ("cvm_clip", {"precision": 8}), oc=48))
+
     def dense_case(seed, m, k, units, bias=True):
         def f():
             g = wl.GraphBuilder(seed)
