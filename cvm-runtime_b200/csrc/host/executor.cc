@@ -105,7 +105,11 @@ struct Lowering {
       else if (op == "concatenate" || op == "broadcast_max") {
         s = true;
         for (size_t i = 0; i < n.inputs.size(); ++i) s = s && in_safe(i);
-      } else if (op == "cvm_precision" || op == "broadcast_greater") s = true;
+      } else if (op == "transpose" || op == "strided_slice" || op == "slice_like" || op == "repeat" ||
+                 op == "tile" || op == "take") s = in_safe(0);
+      else if (op == "cvm_lut") s = in_safe(1);
+      else if (op == "where") s = in_safe(1) && in_safe(2);
+      else if (op == "cvm_precision" || op == "broadcast_greater") s = true;
       safe8[e0] = s;
     }
     for (uint32_t e = 0; e < ne; ++e) {
@@ -696,6 +700,185 @@ struct Lowering {
     }
   }
 
+  // ------------------------------------------------------------------ index-map transforms
+  // One dimension of a gather: `extent` points, each moving the source by a_stride and the
+  // destination by y_stride elements.
+  struct GDim { int64_t extent, a_stride, y_stride; };
+
+  // dst[y_off + sum c_k ys_k] = src[a_off + sum c_k as_k] as strided copies.  Unit extents are
+  // dropped, the destination order decides the iteration order (coalesced writes), neighbours
+  // that form one run in both tensors are merged, and spaces of more than six extents are
+  // peeled into several launches.
+  void emit_gather(const DevBuf& src, int64_t a_off, const DevBuf& dst, std::vector<GDim> dims,
+                   const std::string& label) {
+    std::vector<GDim> v;
+    for (const auto& d : dims) if (d.extent != 1) v.push_back(d);
+    std::stable_sort(v.begin(), v.end(), [](const GDim& a, const GDim& b) { return a.y_stride > b.y_stride; });
+    std::vector<GDim> m;
+    for (const auto& d : v) {
+      if (!m.empty() && m.back().a_stride == d.a_stride * d.extent && m.back().y_stride == d.y_stride * d.extent) {
+        m.back().extent *= d.extent;
+        m.back().a_stride = d.a_stride;
+        m.back().y_stride = d.y_stride;
+      } else {
+        m.push_back(d);
+      }
+    }
+    if (m.empty()) m.push_back({1, 0, 0});
+    emit_gather_peeled(src, a_off, dst, 0, m, label);
+  }
+  void emit_gather_peeled(const DevBuf& src, int64_t a_off, const DevBuf& dst, int64_t y_off,
+                          const std::vector<GDim>& m, const std::string& label) {
+    if (m.size() > 6) {
+      std::vector<GDim> rest(m.begin() + 1, m.end());
+      for (int64_t c = 0; c < m[0].extent; ++c)
+        emit_gather_peeled(src, a_off + c * m[0].a_stride, dst, y_off + c * m[0].y_stride, rest, label);
+      return;
+    }
+    cvmk_strided_desc d;
+    memset(&d, 0, sizeof(d));
+    d.op = CVMK_OP_COPY;
+    d.ndim = (int)m.size();
+    for (int k = 0; k < d.ndim; ++k) {
+      d.extent[k] = m[k].extent;
+      d.a_stride[k] = m[k].a_stride;
+      d.y_stride[k] = m[k].y_stride;
+    }
+    d.a = src.ptr; d.a_dtype = src.dtype; d.a_off = a_off;
+    d.y = dst.ptr; d.y_dtype = dst.dtype; d.y_off = y_off;
+    add_step(label, [d](cudaStream_t s) { return cvmk_strided(&d, s); });
+  }
+
+  // transpose / strided_slice / slice_like / repeat / tile (cpu/ops/ops.cc:603-683, :743-866):
+  // every output element is one input element, at an index that is affine in the output index.
+  void lower_index_map(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const std::string& op = n.op->name;
+    const DevBuf x = materialize(g.entry_id(n.inputs[0]));
+    const DevBuf y = materialize(g.entry_id(nid, 0));
+    const Shape &xsh = x.shape, &ysh = y.shape;
+    const auto xs = phys_strides(xsh, x.nhwc), ys = phys_strides(ysh, y.nhwc);
+    const int xnd = (int)xsh.size(), ynd = (int)ysh.size();
+    std::vector<GDim> dims;
+    int64_t a_off = 0;
+    if (op == "transpose") {
+      Shape axes = n.attrs.t("axes");
+      for (int j = 0; j < ynd; ++j) {
+        int64_t ax = axes.empty() ? ynd - 1 - j : axes[j];
+        if (ax < 0) ax += xnd;
+        dims.push_back({ysh[j], xs[ax], ys[j]});
+      }
+    } else if (op == "strided_slice") {
+      Shape b = n.attrs.t("begin"), st = n.attrs.t("stride");
+      for (int i = (int)b.size(); i < xnd; ++i) b.push_back(0);
+      for (int i = (int)st.size(); i < xnd; ++i) st.push_back(1);
+      for (int j = 0; j < xnd; ++j) {
+        const int64_t lo = st[j] < 0 ? -1 : 0, hi = st[j] < 0 ? xsh[j] - 1 : xsh[j];
+        int64_t bg = b[j] < 0 ? b[j] + xsh[j] : b[j];
+        bg = std::min(std::max(bg, lo), hi);
+        a_off += bg * xs[j];
+        dims.push_back({ysh[j], xs[j] * st[j], ys[j]});
+      }
+    } else if (op == "slice_like") {
+      for (int j = 0; j < xnd; ++j) dims.push_back({ysh[j], xs[j], ys[j]});
+    } else if (op == "repeat") {
+      int axis = (int)n.attrs.i("axis");
+      if (axis < 0) axis += xnd;
+      const int64_t rep = n.attrs.i("repeats");
+      for (int j = 0; j < xnd; ++j) {
+        if (j == axis) {
+          dims.push_back({xsh[j], xs[j], ys[j] * rep});
+          dims.push_back({rep, 0, ys[j]});
+        } else {
+          dims.push_back({ysh[j], xs[j], ys[j]});
+        }
+      }
+    } else {  // tile: right-aligned, output column c reads input column c % extent
+      for (int j = 0; j < ynd; ++j) {
+        const int xj = j - (ynd - xnd);
+        if (xj < 0) {
+          dims.push_back({ysh[j], 0, ys[j]});
+        } else {
+          dims.push_back({ysh[j] / xsh[xj], 0, ys[j] * xsh[xj]});
+          dims.push_back({xsh[xj], xs[xj], ys[j]});
+        }
+      }
+    }
+    emit_gather(x, a_off, y, dims, op + ":" + n.name());
+  }
+
+  // A row-major buffer to produce entry `eid` into; finish_rowmajor() moves it into the entry's
+  // own layout when that is channels-last.
+  DevBuf rowmajor_target(uint32_t eid) {
+    DevBuf& b = materialize(eid);
+    if (!b.nhwc) return b;
+    DevBuf t = b;
+    t.nhwc = false;
+    t.ptr = ex.dalloc(t.bytes());
+    return t;
+  }
+  void finish_rowmajor(const DevBuf& t, uint32_t eid, const std::string& label) {
+    if (t.ptr != buf[eid].ptr) emit_convert(t, buf[eid], label + ":to_nhwc");
+  }
+
+  // take (cpu/ops/ops.cc:868-945) and cvm_lut (:947-956)
+  void lower_take(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const bool lut = n.op->name == "cvm_lut";
+    const std::string label = n.op->name + ":" + n.name();
+    const uint32_t e_x = g.entry_id(n.inputs[lut ? 1 : 0]), e_i = g.entry_id(n.inputs[lut ? 0 : 1]);
+    const uint32_t eo = g.entry_id(nid, 0);
+    cvmk_take_desc d;
+    memset(&d, 0, sizeof(d));
+    const DevBuf x = canon_view(e_x, label);
+    d.x = x.ptr; d.x_dtype = x.dtype;
+    if (lut || !n.attrs.has.at("axis")) {
+      d.outer = 1; d.inner = 1;
+      d.extent = shape_size(x.shape);
+    } else {
+      int axis = (int)n.attrs.i("axis");
+      if (axis < 0) axis += (int)x.shape.size();
+      d.outer = d.inner = 1;
+      for (int j = 0; j < axis; ++j) d.outer *= x.shape[j];
+      for (int j = axis + 1; j < (int)x.shape.size(); ++j) d.inner *= x.shape[j];
+      d.extent = x.shape[axis];
+    }
+    d.count = shape_size(g.shape[e_i]);
+    if (lut) {
+      // flat lookup: the output has the shape, and therefore the layout, of the index tensor
+      const DevBuf idx = materialize(e_i);
+      const DevBuf y = materialize(eo);
+      d.indices = idx.ptr; d.idx_dtype = idx.dtype; d.y = y.ptr; d.y_dtype = y.dtype;
+      add_step(label, [d](cudaStream_t s) { return cvmk_take(&d, s); });
+      return;
+    }
+    const DevBuf idx = canon_view(e_i, label + ":indices");
+    const DevBuf y = rowmajor_target(eo);
+    d.indices = idx.ptr; d.idx_dtype = idx.dtype; d.y = y.ptr; d.y_dtype = y.dtype;
+    add_step(label, [d](cudaStream_t s) { return cvmk_take(&d, s); });
+    finish_rowmajor(y, eo, label);
+  }
+
+  // where (cpu/ops/ops.cc:1049-1075).  x, y and the result share a shape, hence a layout; a
+  // condition of that shape does too, and a 1-D condition indexes the outermost dimension, which is
+  // outermost in both layouts.
+  void lower_where(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    const DevBuf c = materialize(g.entry_id(n.inputs[0]));
+    const DevBuf x = materialize(g.entry_id(n.inputs[1]));
+    const DevBuf y = materialize(g.entry_id(n.inputs[2]));
+    const DevBuf o = materialize(g.entry_id(nid, 0));
+    cvmk_where_desc d;
+    memset(&d, 0, sizeof(d));
+    d.cond = c.ptr; d.cond_dtype = c.dtype;
+    d.x = x.ptr; d.x_dtype = x.dtype;
+    d.y = y.ptr; d.y_dtype = y.dtype;
+    d.out = o.ptr; d.out_dtype = o.dtype;
+    d.n = shape_size(x.shape);
+    d.inner = c.shape.size() == x.shape.size() ? 1 : d.n / x.shape[0];
+    add_step("where:" + n.name(), [d](cudaStream_t s) { return cvmk_where(&d, s); });
+  }
+
   void lower_gvc(uint32_t nid) {
     const Node& n = g.nodes[nid];
     const std::string label = "get_valid_counts:" + n.name();
@@ -740,6 +923,10 @@ struct Lowering {
     if (op == "concatenate") return lower_concat(nid);
     if (op == "flatten" || op == "reshape" || op == "squeeze" || op == "expand_dims") return lower_reshape(nid);
     if (op == "sum" || op == "max") return lower_reduce(nid);
+    if (op == "transpose" || op == "strided_slice" || op == "slice_like" || op == "repeat" || op == "tile")
+      return lower_index_map(nid);
+    if (op == "take" || op == "cvm_lut") return lower_take(nid);
+    if (op == "where") return lower_where(nid);
     if (op == "get_valid_counts") return lower_gvc(nid);
     if (op == "non_max_suppression") return lower_nms(nid);
     if (lower_elemwise_root(nid)) return;
@@ -839,6 +1026,7 @@ Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
   Lowering low(*this, g);
   low.run();
   // One eager pass sets per-kernel attributes and surfaces launch errors before capture.
+  Upload(in_host_, stream_);
   Enqueue(stream_);
   CUDA_OK(cudaStreamSynchronize(stream_));
   if (use_graph_) {
@@ -861,8 +1049,29 @@ Executor::~Executor() {
   if (stream_) cudaStreamDestroy(stream_);
 }
 
+// Queues the upload of one input.  Page-locked (or device) memory is read where it lies; pageable
+// memory goes through the pinned staging buffer in chunks, so that the host copy of one chunk
+// overlaps the transfer of the previous one.
+void Executor::Upload(const void* input, cudaStream_t s) {
+  cudaPointerAttributes at;
+  bool direct = false;
+  if (cudaPointerGetAttributes(&at, input) == cudaSuccess)
+    direct = at.type == cudaMemoryTypeHost || at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+  else
+    cudaGetLastError();
+  if (direct) {
+    CUDA_OK(cudaMemcpyAsync(in_dev_, input, in_bytes_, cudaMemcpyDefault, s));
+    return;
+  }
+  const size_t chunk = (size_t)4 << 20;
+  for (size_t off = 0; off < in_bytes_; off += chunk) {
+    const size_t n = std::min(chunk, in_bytes_ - off);
+    memcpy((char*)in_host_ + off, (const char*)input + off, n);
+    CUDA_OK(cudaMemcpyAsync((char*)in_dev_ + off, (char*)in_host_ + off, n, cudaMemcpyHostToDevice, s));
+  }
+}
+
 void Executor::Enqueue(cudaStream_t s) {
-  CUDA_OK(cudaMemcpyAsync(in_dev_, in_host_, in_bytes_, cudaMemcpyHostToDevice, s));
   for (auto& st : steps_) {
     int rc = st.launch(s);
     CHECK(rc == CVMK_OK) << "step " << st.label << " failed (" << rc << "): " << cvmk_last_error();
@@ -874,7 +1083,7 @@ void Executor::Enqueue(cudaStream_t s) {
 void Executor::Run(const void* input, size_t input_bytes) {
   CHECK(input_bytes == in_bytes_) << "input size " << input_bytes << " vs. " << in_bytes_;
   CUDA_OK(cudaSetDevice(device_));
-  memcpy(in_host_, input, in_bytes_);
+  Upload(input, stream_);
   if (graph_exec_) CUDA_OK(cudaGraphLaunch(graph_exec_, stream_));
   else Enqueue(stream_);
   CUDA_OK(cudaStreamSynchronize(stream_));
@@ -918,11 +1127,10 @@ float Executor::ReplayDevice(int iters) {
 std::vector<std::pair<std::string, float>> Executor::ProfileOnce(const void* input, size_t input_bytes) {
   CHECK(input_bytes == in_bytes_);
   CUDA_OK(cudaSetDevice(device_));
-  memcpy(in_host_, input, in_bytes_);
   std::vector<std::pair<std::string, float>> out;
   std::vector<cudaEvent_t> ev(steps_.size() + 1);
   for (auto& e : ev) CUDA_OK(cudaEventCreate(&e));
-  CUDA_OK(cudaMemcpyAsync(in_dev_, in_host_, in_bytes_, cudaMemcpyHostToDevice, stream_));
+  Upload(input, stream_);
   CUDA_OK(cudaEventRecord(ev[0], stream_));
   for (size_t i = 0; i < steps_.size(); ++i) {
     KERNEL_OK(steps_[i].launch(stream_));

@@ -10,7 +10,8 @@
 //     producing kernel (conv2d / dense / reduce / element-wise), so their int32 intermediates are
 //     never written;
 //   - pre-packed int8 weights (OIHW -> OHWI) and TMA tensor maps for the tensor-core convolutions;
-//   - a CUDA graph of the whole step list including the input upload and the output download.
+//   - a CUDA graph of the whole step list and the output download; the input upload is queued
+//     in front of it (straight from page-locked caller memory, staged in chunks otherwise).
 // There is no CPU fallback: every step is a CUDA kernel from this library.
 #pragma once
 #include <cuda_runtime.h>
@@ -82,6 +83,7 @@ class Executor {
   bool use_graph_ = true;
 
   void* dalloc(size_t bytes);
+  void Upload(const void* input, cudaStream_t s);
   void Enqueue(cudaStream_t s);
   friend struct Lowering;
 };

@@ -309,6 +309,23 @@ __device__ __forceinline__ void fast_requant(const ConvParams& p, const int32_t 
   *o1 = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
+// Optional phase timers (development builds only, -DCVMK_CONV_TIMING): per CTA, cycles the elected
+// lanes spend waiting and working.  Slots: 0 producer waits for a free stage, 1 MMA waits for a
+// free accumulator, 2 MMA waits for operands, 3 MMA loop, 4+4g.. epilogue group g: wait for the
+// accumulator, wait for the staging tile, TMEM loads + arithmetic, store phase; 12 whole kernel.
+#ifdef CVMK_CONV_TIMING
+__device__ long long g_conv_timing[148 * 16];
+#define TSTART(var) long long var = clock64()
+#define TADD(slot, var) do { const long long now__ = clock64(); tacc[slot] += now__ - var; var = now__; } while (0)
+#define TDECL long long tacc[16] = {0}
+#define TFLUSH(slot) do { if (blockIdx.x < 148) g_conv_timing[blockIdx.x * 16 + (slot)] = tacc[slot]; } while (0)
+#else
+#define TSTART(var) do {} while (0)
+#define TADD(slot, var) do {} while (0)
+#define TDECL do {} while (0)
+#define TFLUSH(slot) do {} while (0)
+#endif
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
@@ -367,6 +384,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool live = true;
+      TDECL;
+      TSTART(tk);
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
         const int n_tile = tile % p.num_n_tiles;
         const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
@@ -381,7 +400,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int cb = kb - tap * k_per_tap;
           const int fy = tap / p.kw;
           const int fx = tap - fy * p.kw;
+          TSTART(tw);
           if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
+          TADD(0, tw);
           uint8_t* sa = smem + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + a_bytes;
           mbar_expect_tx(&bar_full[stage], (uint32_t)stage_bytes);
@@ -395,6 +416,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
+      TADD(12, tk);
+      TFLUSH(0);
+      TFLUSH(12);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -405,12 +429,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int acc = 0;
       uint32_t acc_phase = 0;
       bool live = true;
+      TDECL;
+      TSTART(tl);
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+        TSTART(tw);
         if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1, &abort_flag, 2)) { live = false; break; }
+        TADD(1, tw);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.block_n);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&bar_full[stage], phase, &abort_flag, 3)) { live = false; break; }
+          TADD(2, tw);
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
           const uint32_t sb = sa + a_bytes;
@@ -428,6 +457,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
+      TADD(3, tl);
+      TFLUSH(1);
+      TFLUSH(2);
+      TFLUSH(3);
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
@@ -453,17 +486,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     (first_tile % p.num_n_tiles) * p.block_n + q * 128, (first_tile / p.num_n_tiles) * BLOCK_M);
     }
     int k = 0;  // index of this group's tile
+    TDECL;
     for (int tile = first_tile; tile < num_tiles; tile += stride_tiles, ++k) {
       const int n0 = (tile % p.num_n_tiles) * p.block_n;
       const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
       const int row = m0 + row_in_tile;
+      TSTART(tw);
       bool ok = mbar_wait(&bar_acc_full[acc], (uint32_t)(k & 1), &abort_flag, 4);
+      TADD(4 + 4 * group, tw);
       tc_fence_after();
       if (ok && p.tma_out) {
         // staging is ours again: operand tile landed (join) / previous store has been read
         if (has_res) ok = mbar_wait(&bar_res[group], (uint32_t)(k & 1), &abort_flag, 5);
         else if (k > 0) ok = mbar_wait(&bar_res[group], (uint32_t)((k - 1) & 1), &abort_flag, 5);
       }
+      TADD(5 + 4 * group, tw);
       if (ok) {
         const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
         int32_t v[32];
@@ -542,6 +579,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
+      TADD(6 + 4 * group, tw);
       if (p.tma_out) {
         fence_async_smem();  // make the staged bytes visible to the TMA engine
         // One thread decides for the whole group whether to go on, so that nobody is left alone
@@ -565,11 +603,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
           }
         }
+        TADD(7 + 4 * group, tw);
         if (stop) break;
       } else if (abort_flag) {
         break;
       }
     }
+#ifdef CVMK_CONV_TIMING
+    if (leader) { TFLUSH(4 + 4 * group); TFLUSH(5 + 4 * group); TFLUSH(6 + 4 * group); TFLUSH(7 + 4 * group); }
+#endif
     if (p.tma_out && leader) tma_store_wait_all();
   }
 
@@ -849,3 +891,9 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   conv_tc_kernel<<<plan->grid, NUM_THREADS, plan->smem_bytes, (cudaStream_t)stream>>>(ta, tb, ty, tr, p);
   return check_cuda(cudaGetLastError(), "conv_tc_kernel launch");
 }
+
+#ifdef CVMK_CONV_TIMING
+extern "C" int cvmk_conv_timing_read(long long* host, int count) {
+  return (int)cudaMemcpyFromSymbol(host, g_conv_timing, sizeof(long long) * (size_t)count);
+}
+#endif

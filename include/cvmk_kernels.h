@@ -254,6 +254,35 @@ CVMK_API int cvmk_stem_pack_supported(const cvmk_stem_pack_desc* d);
 CVMK_API int cvmk_stem_pack(const cvmk_stem_pack_desc* d, cvmk_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * take (cpu/ops/ops.cc:868-945) and cvm_lut (:947-956) on row-major tensors:
+ *     y[o, m, n] = x[o, clamp(indices[m], 0, extent - 1), n]
+ * with o < outer (product of x's dims before the axis), m < count (elements of `indices`),
+ * n < inner (product of x's dims after the axis).  Without an axis, and for cvm_lut, the tensor is
+ * taken flat: outer = inner = 1 and extent = its element count.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;       int32_t x_dtype;   int32_t pad0;
+  const void* indices; int32_t idx_dtype; int32_t pad1;
+  void* y;             int32_t y_dtype;   int32_t pad2;
+  int64_t outer, count, inner, extent;
+} cvmk_take_desc;
+CVMK_API int cvmk_take(const cvmk_take_desc* d, cvmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * where (cpu/ops/ops.cc:1049-1075): out[i] = cond[i / inner] == 0 ? y[i] : x[i] over n elements.
+ * inner = 1 is the element-wise form (condition shaped like x); inner = elements per leading row
+ * is the form with a 1-D condition over the first dimension.  x, y and out share one layout.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* cond; int32_t cond_dtype; int32_t pad0;
+  const void* x;    int32_t x_dtype;    int32_t pad1;
+  const void* y;    int32_t y_dtype;    int32_t pad2;
+  void* out;        int32_t out_dtype;  int32_t pad3;
+  int64_t n, inner;
+} cvmk_where_desc;
+CVMK_API int cvmk_where(const cvmk_where_desc* d, cvmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * get_valid_counts (cpu/ops/nms.cc:42-63): per batch keep rows with row[1] > score_threshold in
  * their original order, write their number to valid_count[b], fill the remaining rows with -1.
  * x, y: int32 [B, N, K]; valid_count: int32 [B].

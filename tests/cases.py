@@ -19,13 +19,15 @@ pkg = ge.load_package()
 wl = pkg.workloads
 
 
-def single_op(func, data, data_prec, attrs, out_shapes, params=(), seed=0, head=None):
+def single_op(func, data, data_prec, attrs, out_shapes, params=(), seed=0, head=None, data_pos=0):
     """Graph `data (+ params) -> func -> heads`.  `params` is a list of (ndarray, precision);
-    `head` selects one output of a multi-output operator."""
+    `head` selects one output of a multi-output operator; `data_pos` is the position of the
+    runtime input among the operator's inputs."""
     g = wl.GraphBuilder(seed)
-    ins = [g.var("data", data.shape, data_prec)]
+    ins = []
     for i, (arr, prec) in enumerate(params):
         ins.append(g.var("p%d" % i, arr.shape, prec, arr))
+    ins.insert(data_pos, g.var("data", data.shape, data_prec))
     out = g.op(func, ins, out_shapes, attrs)
     heads = out if isinstance(out, list) else [out]
     if head is not None:
@@ -245,6 +247,84 @@ def op_cases():
     add("expand_dims", reshape_like("expand_dims", 83, (3, 4), {"axis": 1, "num_newaxis": 2}, [3, 1, 1, 4], prec=12))
     add("squeeze", reshape_like("squeeze", 84, (3, 1, 4, 1), {"axis": (1, 3)}, [3, 4], prec=12))
 
+    # index-map transforms, take / cvm_lut, where
+    def xform(func, seed, shape, attrs, out, prec=8):
+        def f():
+            return single_op(func, rnd(np.random.RandomState(seed), shape, prec), prec, attrs, [out])
+        return f
+    add("transpose_default", xform("transpose", 110, (3, 4, 5), None, [5, 4, 3], prec=12))
+    add("transpose_nchw_to_nhwc", xform("transpose", 111, (2, 16, 3, 5), {"axes": (0, 2, 3, 1)}, [2, 3, 5, 16]))
+    add("transpose_120", xform("transpose", 112, (4, 3, 6), {"axes": (1, 2, 0)}, [3, 6, 4], prec=16))
+    add("transpose_neg_axes", xform("transpose", 113, (2, 3, 4, 5), {"axes": (-1, 0, -2, 1)}, [5, 2, 4, 3]))
+    add("transpose_2d", xform("transpose", 114, (7, 33), {"axes": (1, 0)}, [33, 7], prec=20))
+    add("transpose_6d", xform("transpose", 115, (2, 3, 2, 3, 2, 3), {"axes": (5, 3, 1, 4, 2, 0)}, [3, 3, 3, 2, 2, 2]))
+    add("strided_slice_basic", xform("strided_slice", 120, (3, 8, 6), {"begin": (0, 1), "end": (2, 7), "stride": (1, 2)}, [2, 3, 6], prec=12))
+    add("strided_slice_neg_stride", xform("strided_slice", 121, (5, 9), {"begin": (4, -1), "end": (0, 2), "stride": (-2, -3)}, [2, 2], prec=16))
+    add("strided_slice_neg_begin_4d", xform("strided_slice", 122, (2, 8, 6, 6), {"begin": (0, -6, 1, 0), "end": (2, 8, 5, 6)}, [2, 6, 4, 6]))
+    add("strided_slice_clamped", xform("strided_slice", 123, (6, 5), {"begin": (-100, 2), "end": (100, 100)}, [6, 3], prec=10))
+    add("strided_slice_anchor_cols", xform("strided_slice", 124, (2, 50, 6), {"begin": (0, 0, 2), "end": (2, 50, 6)}, [2, 50, 4], prec=16))
+
+    def slice_like(seed, shape, like, axis, out, prec=8):
+        def f():
+            rng = np.random.RandomState(seed)
+            attrs = {"axis": axis} if axis is not None else None
+            return single_op("slice_like", rnd(rng, shape, prec), prec, attrs, [out],
+                             params=[(rnd(rng, like, 8), 8)])
+        return f
+    add("slice_like_all", slice_like(130, (4, 6, 5), (2, 6, 3), None, [2, 6, 3], prec=12))
+    add("slice_like_axes", slice_like(131, (2, 16, 7, 9), (2, 3, 5, 6), (2, 3), [2, 16, 5, 6]))
+    add("slice_like_neg_axis", slice_like(132, (3, 10), (7, 4), (-1,), [3, 4], prec=16))
+    add("repeat_axis0", xform("repeat", 140, (3, 4), {"repeats": 2, "axis": 0}, [6, 4], prec=12))
+    add("repeat_channels", xform("repeat", 141, (2, 8, 3, 3), {"repeats": 3, "axis": 1}, [2, 24, 3, 3]))
+    add("repeat_last_neg", xform("repeat", 142, (2, 3, 5), {"repeats": 4, "axis": -1}, [2, 3, 20], prec=16))
+    add("tile_same_rank", xform("tile", 150, (2, 3), {"reps": (2, 3)}, [4, 9], prec=12))
+    add("tile_more_reps", xform("tile", 151, (3, 2), {"reps": (2, 1, 2)}, [2, 3, 4], prec=16))
+    add("tile_fewer_reps", xform("tile", 152, (2, 4, 3, 5), {"reps": (2, 2)}, [2, 4, 6, 10]))
+    add("tile_6d", xform("tile", 153, (2, 1, 3, 2, 1, 2), {"reps": (2, 2, 1, 2, 3, 2)}, [4, 2, 3, 4, 3, 4]))
+
+    def take(seed, shape, idx_shape, axis, out, prec=8, idx_range=None, data_is_index=False):
+        def f():
+            rng = np.random.RandomState(seed)
+            x = rnd(rng, shape, prec)
+            n = int(np.prod(shape)) if axis is None else shape[axis]
+            lo, hi = idx_range if idx_range else (-3, n + 3)   # out-of-range indices are clamped
+            idx = rng.randint(lo, hi, size=idx_shape).astype(np.int32)
+            attrs = {"axis": axis} if axis is not None else None
+            if data_is_index:
+                return single_op("take", idx, 16, attrs, [out], params=[(x, prec)], data_pos=1)
+            return single_op("take", x, prec, attrs, [out], params=[(idx, 16)])
+        return f
+    add("take_flat", take(160, (4, 5, 3), (7, 2), None, [7, 2], prec=12))
+    add("take_axis0_embedding", take(161, (50, 16), (3, 9), 0, [3, 9, 16], data_is_index=True))
+    add("take_axis1", take(162, (3, 6, 4), (5,), 1, [3, 5, 4], prec=16))
+    add("take_axis_neg_4d", take(163, (2, 8, 3, 5), (2, 2), -1, [2, 8, 3, 2, 2]))
+    add("take_axis2_4d_out", take(164, (2, 8, 7), (3, 5), 2, [2, 8, 3, 5]))
+
+    def lut(seed, shape, in_dim, table_prec, idx_prec):
+        def f():
+            rng = np.random.RandomState(seed)
+            table = rnd(rng, (in_dim,), table_prec)
+            a = (1 << (idx_prec - 1)) - 1
+            idx = rng.randint(-2 if idx_prec > 8 else -a, a + 1, size=shape).astype(np.int8 if idx_prec <= 8 else np.int32)
+            return single_op("cvm_lut", idx, idx_prec, {"in_dim": in_dim}, [list(shape)], params=[(table, table_prec)])
+        return f
+    add("cvm_lut_int8_index", lut(170, (2, 16, 5, 5), 100, 16, 8))
+    add("cvm_lut_wide_index", lut(171, (3, 40), 300, 8, 10))
+
+    def where(seed, shape, rows, cond_is_data=True, prec=8):
+        def f():
+            rng = np.random.RandomState(seed)
+            cshape = (shape[0],) if rows else shape
+            cond = (rng.randint(0, 3, size=cshape) - 1).astype(np.int8)   # -1, 0, 1
+            x, y = rnd(rng, shape, prec), rnd(rng, shape, prec)
+            if cond_is_data:
+                return single_op("where", cond, 8, None, [list(shape)], params=[(x, prec), (y, prec)])
+            return single_op("where", x, prec, None, [list(shape)], params=[(cond, 8), (y, prec)], data_pos=1)
+        return f
+    add("where_elementwise", where(180, (2, 16, 3, 5), False))
+    add("where_elementwise_int32", where(181, (6, 7), False, cond_is_data=False, prec=20))
+    add("where_1d", where(182, (9,), False, prec=16))
+
     def gvc(seed, b, n, k, thr, head=1):
         def f():
             rng = np.random.RandomState(seed)
@@ -339,4 +419,30 @@ def malformed_cases():
     # crashes, so this case has no golden status (recorded as -11).
     mut("version_1_1_0_no_tables", lambda g: (g.update({"version": "cvm_1.1.0"}), g.pop("node_row_ptr"), g.pop("arg_nodes")))
     mut("postprocess_argmax_ok", lambda g: g.update({"postprocess": "argmax"}))
+
+    # transform operators with attributes or shapes their shape inference refuses
+    def bad_op(name, func, shape, attrs, out_shape, params=(), prec=8):
+        j, p, _ = single_op(func, np.zeros(shape, np.int8), prec, attrs, [out_shape], params=params)
+        out[name] = (j, p)
+    bad_op("transpose_repeated_axis", "transpose", (2, 3, 4), {"axes": (0, 1, 1)}, [2, 3, 3])
+    bad_op("transpose_axis_count", "transpose", (2, 3, 4), {"axes": (1, 0)}, [3, 2, 4])
+    bad_op("transpose_wrong_out_shape", "transpose", (2, 3, 4), {"axes": (2, 0, 1)}, [4, 3, 2])
+    bad_op("tile_zero_rep", "tile", (2, 3), {"reps": (2, 0)}, [4, 3])
+    bad_op("tile_default_reps", "tile", (2, 3), None, [2, 3])
+    bad_op("repeat_zero", "repeat", (2, 3), {"repeats": 0, "axis": 0}, [2, 3])
+    bad_op("repeat_bad_axis", "repeat", (2, 3), {"repeats": 2, "axis": 2}, [2, 3])
+    bad_op("repeat_missing_repeats", "repeat", (2, 3), {"axis": 0}, [2, 3])
+    bad_op("strided_slice_empty", "strided_slice", (4, 5), {"begin": (2, 0), "end": (2, 5)}, [1, 5])
+    bad_op("strided_slice_zero_stride", "strided_slice", (4, 5), {"begin": (0, 0), "end": (2, 5), "stride": (1, 0)}, [2, 5])
+    bad_op("strided_slice_wrong_direction", "strided_slice", (4, 5), {"begin": (0,), "end": (3,), "stride": (-1,)}, [3, 5])
+    bad_op("slice_like_exceeds", "slice_like", (2, 3), None, [4, 3], params=[(np.zeros((4, 3), np.int8), 8)])
+    bad_op("slice_like_rank_mismatch", "slice_like", (2, 3, 4), None, [2, 3, 4], params=[(np.zeros((2, 3), np.int8), 8)])
+    bad_op("slice_like_bad_axis", "slice_like", (2, 3, 4), {"axis": (2,)}, [2, 3, 4], params=[(np.zeros((2, 3), np.int8), 8)])
+    bad_op("take_bad_axis", "take", (3, 4), {"axis": 2}, [3, 2], params=[(np.zeros((2,), np.int32), 16)])
+    bad_op("take_axis_not_int", "take", (3, 4), {"axis": "x"}, [3, 2], params=[(np.zeros((2,), np.int32), 16)])
+    bad_op("cvm_lut_in_dim_mismatch", "cvm_lut", (3, 4), {"in_dim": 9}, [3, 4], params=[(np.zeros((10,), np.int8), 8)])
+    bad_op("where_xy_mismatch", "where", (3, 4), None, [3, 4],
+           params=[(np.zeros((3, 4), np.int8), 8), (np.zeros((3, 5), np.int8), 8)])
+    bad_op("where_cond_rows_mismatch", "where", (2,), None, [3, 4],
+           params=[(np.zeros((3, 4), np.int8), 8), (np.zeros((3, 4), np.int8), 8)])
     return out
