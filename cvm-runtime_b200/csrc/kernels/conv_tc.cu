@@ -69,6 +69,7 @@ struct ConvParams {
   uint32_t f_lo1, f_hi1;  // first clamp, both halves of an s16x2 word
   uint32_t f_lo2, f_hi2;  // clamp after the tensor step
   int f_sub;            // tensor step subtracts its operand
+  int fast_variant;     // (first clamp starts at 0) + 2 * kind; kind: 0 none, 1 add + clamp from 0, 2 add, 3 subtract
   DevChain chain;
 };
 
@@ -272,33 +273,35 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 // permute), the final clamp (one fused add-min-relu when its lower bound is 0), and the pack to
 // bytes.  Same values as the step-by-step chain: every clamp commutes with the monotone shift, and
 // all intermediate values are exact in 16 bits.
+// RELU1: the first clamp has lower bound 0.  KIND: 0 no tensor step, 1 add with a final clamp whose
+// lower bound is 0, 2 add with a general clamp, 3 subtract with a general clamp.  All of it is
+// resolved at compile time so that the 32 columns form one straight-line block.
+template <int RELU1, int KIND>
 __device__ __forceinline__ void fast_requant(const ConvParams& p, const int32_t (&v)[32], const uint4& r0,
                                              const uint4& r1, uint4* o0, uint4* o1) {
   uint32_t h[16];
+  const int sh = p.f_shift;
+  const uint32_t hi1 = p.f_hi1, lo1 = p.f_lo1, hi2 = p.f_hi2, lo2 = p.f_lo2;
 #pragma unroll
-  for (int j = 0; j < 16; ++j)
-    h[j] = __byte_perm((uint32_t)(v[2 * j] >> p.f_shift), (uint32_t)(v[2 * j + 1] >> p.f_shift), 0x5410);
-  if (p.f_lo1 == 0) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) h[j] = __vimin_s16x2_relu(h[j], p.f_hi1);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) h[j] = __vmaxs2(__vmins2(h[j], p.f_hi1), p.f_lo1);
+  for (int j = 0; j < 16; ++j) {
+    h[j] = __byte_perm((uint32_t)(v[2 * j] >> sh), (uint32_t)(v[2 * j + 1] >> sh), 0x5410);
+    if (RELU1) h[j] = __vimin_s16x2_relu(h[j], hi1);
+    else h[j] = __vmaxs2(__vmins2(h[j], hi1), lo1);
   }
-  if (p.fast_mode == 2) {
+  if (KIND != 0) {
     const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       const uint32_t ra = prmt(rw[q], 0, 0x9180);  // bytes 0,1 sign-extended to 16 bits
       const uint32_t rb = prmt(rw[q], 0, 0xB3A2);  // bytes 2,3
-      if (!p.f_sub && p.f_lo2 == 0) {
-        h[2 * q] = __viaddmin_s16x2_relu(h[2 * q], ra, p.f_hi2);
-        h[2 * q + 1] = __viaddmin_s16x2_relu(h[2 * q + 1], rb, p.f_hi2);
+      if (KIND == 1) {
+        h[2 * q] = __viaddmin_s16x2_relu(h[2 * q], ra, hi2);
+        h[2 * q + 1] = __viaddmin_s16x2_relu(h[2 * q + 1], rb, hi2);
       } else {
-        const uint32_t xa = p.f_sub ? __vsub2(h[2 * q], ra) : __vadd2(h[2 * q], ra);
-        const uint32_t xb = p.f_sub ? __vsub2(h[2 * q + 1], rb) : __vadd2(h[2 * q + 1], rb);
-        h[2 * q] = __vmaxs2(__vmins2(xa, p.f_hi2), p.f_lo2);
-        h[2 * q + 1] = __vmaxs2(__vmins2(xb, p.f_hi2), p.f_lo2);
+        const uint32_t xa = KIND == 3 ? __vsub2(h[2 * q], ra) : __vadd2(h[2 * q], ra);
+        const uint32_t xb = KIND == 3 ? __vsub2(h[2 * q + 1], rb) : __vadd2(h[2 * q + 1], rb);
+        h[2 * q] = __vmaxs2(__vmins2(xa, hi2), lo2);
+        h[2 * q + 1] = __vmaxs2(__vmins2(xb, hi2), lo2);
       }
     }
   }
@@ -307,6 +310,37 @@ __device__ __forceinline__ void fast_requant(const ConvParams& p, const int32_t 
   for (int q = 0; q < 8; ++q) w[q] = __byte_perm(h[2 * q], h[2 * q + 1], 0x6420);
   *o0 = make_uint4(w[0], w[1], w[2], w[3]);
   *o1 = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// One thread's row of a tile on the fast path: `chunks` groups of 32 columns are read from TMEM,
+// biased (the rounding addend is part of the staged bias), requantised and written to the
+// swizzled staging panels, in place of the tensor operand when there is one.
+template <int RELU1, int KIND>
+__device__ __forceinline__ void fast_row(const ConvParams& p, uint32_t tbase, int chunks, const int32_t* bias_row,
+                                         uint8_t* io_base, int panel_size, int row_in_tile, int pw) {
+  const uint32_t row_off = (uint32_t)row_in_tile * (uint32_t)pw;
+  const uint32_t sw = (row_off >> 7) & (((uint32_t)pw - 1u) >> 4);  // swizzle key of this row, as in panel_offset()
+  for (int ci = 0; ci < chunks; ++ci) {
+    int32_t v[32];
+    tmem_ld32(tbase + (uint32_t)(ci * 32), v);
+    const int4* bp = reinterpret_cast<const int4*>(bias_row + ci * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int4 b4 = bp[j];
+      v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+    }
+    const int c0 = ci * 32;
+    uint8_t* pb = io_base + (size_t)(c0 >> 7) * panel_size + row_off;
+    const uint32_t j0 = (uint32_t)(c0 & 127) >> 4;
+    uint4* q0 = reinterpret_cast<uint4*>(pb + ((j0 ^ sw) << 4));
+    uint4* q1 = reinterpret_cast<uint4*>(pb + (((j0 + 1) ^ sw) << 4));
+    uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
+    if (KIND != 0) { r0 = *q0; r1 = *q1; }
+    uint4 a, b;
+    fast_requant<RELU1, KIND>(p, v, r0, r1, &a, &b);
+    *q0 = a;
+    *q1 = b;
+  }
 }
 
 // Optional phase timers (development builds only, -DCVMK_CONV_TIMING): per CTA, cycles the elected
@@ -503,6 +537,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       TADD(5 + 4 * group, tw);
       if (ok) {
         const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
+        if (p.fast_mode) {
+          const int chunks = min(p.block_n, p.oc - n0) >> 5;  // OC is a multiple of 32 on this path
+          const int32_t* brow = bias_s + n0;
+          switch (p.fast_variant) {
+            case 0: fast_row<0, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 1: fast_row<1, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 2: fast_row<0, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 3: fast_row<1, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 4: fast_row<0, 2>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 5: fast_row<1, 2>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 6: fast_row<0, 3>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            default: fast_row<1, 3>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+          }
+        } else {
         int32_t v[32];
         tmem_ld32(tbase, v);
         for (int c0 = 0; c0 < p.block_n; c0 += 32) {
@@ -527,16 +575,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int j0 = (c0 & 127) >> 4;  // first 16-byte chunk of this thread inside the panel row
             uint4* q0 = reinterpret_cast<uint4*>(pb + panel_offset(row_in_tile, j0, pw));
             uint4* q1 = reinterpret_cast<uint4*>(pb + panel_offset(row_in_tile, j0 + 1, pw));
-            if (p.fast_mode) {
-              uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
-              if (p.fast_mode == 2) { r0 = *q0; r1 = *q1; }
-              uint4 a, b;
-              fast_requant(p, v, r0, r1, &a, &b);
-              *q0 = a;
-              *q1 = b;
-              if (c0 + 32 < p.block_n && n0 + c0 + 32 < p.oc) tmem_ld32(tbase + (uint32_t)(c0 + 32), v);
-              continue;
-            }
             if (row < p.m_total) {
               if (has_res) {
                 int32_t rv[32];
@@ -574,6 +612,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
           }
           if (c0 + 32 < p.block_n && n0 + c0 + 32 < p.oc) tmem_ld32(tbase + (uint32_t)(c0 + 32), v);
+        }
         }
       }
       tc_fence_before();
@@ -864,6 +903,8 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
           p.f_hi2 = x2(p.chain.s[i0 + 2].b);
         }
         if (p.fast_mode) {
+          const int kind = p.fast_mode == 1 ? 0 : (p.f_sub ? 3 : (p.chain.s[i0 + 2].a == 0 ? 1 : 2));
+          p.fast_variant = (lo1 == 0 ? 1 : 0) + 2 * kind;
           p.f_shift = sh;
           p.f_add = (int)add;
           p.f_lo1 = x2(lo1);
