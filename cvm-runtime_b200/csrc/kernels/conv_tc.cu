@@ -37,7 +37,10 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int MAX_STAGES = 8;
 constexpr int NUM_EPI_WARPS = 8;
-constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: epilogue
+// warp 0: TMA loads of the operands, warp 1: MMA + TMEM owner, warps 2..9: epilogue,
+// warp 10: TMA traffic of the staged output tiles (stores, residual-operand loads)
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS + 32;
+constexpr int IO_WARP = 2 + NUM_EPI_WARPS;
 constexpr uint32_t SPIN_LIMIT = 1u << 19;  // x 2 us per hardware wait
 constexpr int SMEM_DYNAMIC_MAX = 227 * 1024 - 8704;  // 227 KB per CTA minus the static part (bias, barriers)
 constexpr int MAX_BIAS = 2048;          // bias vectors up to this length are staged in shared memory
@@ -50,7 +53,10 @@ struct ConvParams {
   int oh, ow;
   int c, kh, kw;
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
-  int block_k, block_n, stages, a_im2col;
+  int block_k, block_n, stages;
+  int a_mode;           // activations: 0 plain 2-D tiles (1x1, dense), 1 im2col-mode TMA, 2 spatial patches
+  int patch_w, patch_h, patch_n;  // a_mode 2: an M tile is patch_w x patch_h output pixels of patch_n images
+  int tiles_w, tiles_h;           // a_mode 2: patches per image row / column
   int num_m_tiles, num_n_tiles;
   int tmem_cols;
   int* status;
@@ -60,11 +66,12 @@ struct ConvParams {
   int res_step;         // chain step whose int8 tensor operand is fetched with TMA (-1: none)
   int panels;           // 128-column panels per tile (1 or 2) on the TMA output path
   int panel_bytes;      // row length of a panel in bytes: min(block_n, 128)
-  int io_bufs;          // staging buffers per panel: 1 or 2
+  int io_bufs;          // staging buffers per epilogue group: 1 or 2
   int ring_bytes;       // bytes of the operand ring (the staging buffers follow it)
   // Requantisation fast path (see fast_requant below): 0 off, 1 shift+clamp, 2 + tensor add/sub + clamp
   int fast_mode;
-  int f_shift;          // rounding shift; its addend 2^(shift-1) is folded into the staged bias
+  int f_shift;          // rounding shift (<= 16); its addend 2^(shift-1) is folded into the staged bias
+  int f_mul;            // 2^(16 - shift)
   int f_add;
   uint32_t f_lo1, f_hi1;  // first clamp, both halves of an s16x2 word
   uint32_t f_lo2, f_hi2;  // clamp after the tensor step
@@ -133,6 +140,15 @@ __device__ __forceinline__ void tma_load_im2col_4d(void* dst, const CUtensorMap*
       " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(smem_u32(dst)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
       "h"(off_w), "h"(off_h)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 
@@ -234,6 +250,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                    reinterpret_cast<uint64_t>(map)),
                "r"(smem_u32(src)), "r"(c0), "r"(c1)
                : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 __device__ __forceinline__ void tma_store_wait_read() {
@@ -244,9 +269,6 @@ __device__ __forceinline__ void tma_store_wait_all() {
 }
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void named_barrier(int id, int count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 // Byte offset of 16-byte chunk `j` of row `row` inside a staging panel whose rows are `pw` bytes
 // long and stored with the TMA swizzle of that width (address bits [4,7) ^= bits [7,10), cut to
@@ -280,11 +302,10 @@ template <int RELU1, int KIND>
 __device__ __forceinline__ void fast_requant(const ConvParams& p, const int32_t (&v)[32], const uint4& r0,
                                              const uint4& r1, uint4* o0, uint4* o1) {
   uint32_t h[16];
-  const int sh = p.f_shift;
   const uint32_t hi1 = p.f_hi1, lo1 = p.f_lo1, hi2 = p.f_hi2, lo2 = p.f_lo2;
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    h[j] = __byte_perm((uint32_t)(v[2 * j] >> sh), (uint32_t)(v[2 * j + 1] >> sh), 0x5410);
+    h[j] = __byte_perm((uint32_t)v[2 * j], (uint32_t)v[2 * j + 1], 0x7632);  // the two upper halves
     if (RELU1) h[j] = __vimin_s16x2_relu(h[j], hi1);
     else h[j] = __vmaxs2(__vmins2(h[j], hi1), lo1);
   }
@@ -323,11 +344,18 @@ __device__ __forceinline__ void fast_row(const ConvParams& p, uint32_t tbase, in
   for (int ci = 0; ci < chunks; ++ci) {
     int32_t v[32];
     tmem_ld32(tbase + (uint32_t)(ci * 32), v);
+    // (acc + bias + rounding addend) << (16 - shift) as one multiply-add per element: bits
+    // [16, 32) of the result are bits [shift, shift + 16) of the biased sum, i.e. the low half of
+    // its arithmetic right shift, which is all the packed arithmetic below needs.
     const int4* bp = reinterpret_cast<const int4*>(bias_row + ci * 32);
+    const int mul = p.f_mul;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int4 b4 = bp[j];
-      v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+      v[4 * j] = v[4 * j] * mul + b4.x;
+      v[4 * j + 1] = v[4 * j + 1] * mul + b4.y;
+      v[4 * j + 2] = v[4 * j + 2] * mul + b4.z;
+      v[4 * j + 3] = v[4 * j + 3] * mul + b4.w;
     }
     const int c0 = ci * 32;
     uint8_t* pb = io_base + (size_t)(c0 >> 7) * panel_size + row_off;
@@ -360,6 +388,25 @@ __device__ long long g_conv_timing[148 * 16];
 #define TFLUSH(slot) do {} while (0)
 #endif
 
+// Origin of a tile: first output channel, and either the first linear output row (modes 0, 1) or
+// the corner (w, h, n) of the spatial patch (mode 2).
+struct TileOrigin { int n0, m0, cw, ch, cn; };
+__device__ __forceinline__ TileOrigin tile_origin(const ConvParams& p, int tile) {
+  TileOrigin t;
+  const int mt = tile / p.num_n_tiles;
+  t.n0 = (tile - mt * p.num_n_tiles) * p.block_n;
+  t.m0 = mt * BLOCK_M;
+  t.cw = t.ch = t.cn = 0;
+  if (p.a_mode == 2) {
+    const int r = mt / p.tiles_w;
+    t.cw = (mt - r * p.tiles_w) * p.patch_w;
+    const int tn = r / p.tiles_h;
+    t.ch = (r - tn * p.tiles_h) * p.patch_h;
+    t.cn = tn * p.patch_n;
+  }
+  return t;
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
@@ -369,10 +416,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ uint64_t bar_empty[MAX_STAGES];
   __shared__ uint64_t bar_acc_full[2];
   __shared__ uint64_t bar_acc_empty[2];
-  __shared__ uint64_t bar_res[2];     // per epilogue group: operand tile landed / staging free
+  __shared__ uint64_t bar_res[2][2];     // [group][buffer]: staging buffer free / operand tile landed in it
+  __shared__ uint64_t bar_staged[2][2];  // [group][buffer]: the group has written its tile into the buffer
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
-  __shared__ volatile int group_stop[2][2];  // [panel group][tile parity]: leave after this tile
   __shared__ __align__(16) int32_t bias_s[MAX_BIAS];
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -395,16 +442,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bar_acc_full[a], 1);
       mbar_init(&bar_acc_empty[a], NUM_EPI_WARPS / 2);
-      mbar_init(&bar_res[a], 1);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&bar_res[a][b], 1);
+        mbar_init(&bar_staged[a][b], NUM_EPI_WARPS / 2);
+      }
     }
     abort_flag = 0;
-    group_stop[0][0] = group_stop[0][1] = group_stop[1][0] = group_stop[1][1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (bias_in_smem) {
     const int padded = min(MAX_BIAS, (p.oc + 31) & ~31);
     for (int i = threadIdx.x; i < padded; i += NUM_THREADS)
-      bias_s[i] = (i < p.oc && p.bias ? __ldg(p.bias + i) : 0) + (p.fast_mode ? p.f_add : 0);
+    {
+      const int32_t b = i < p.oc && p.bias ? __ldg(p.bias + i) : 0;
+      // fast path: (bias + rounding addend) pre-multiplied by 2^(16 - shift), see fast_row()
+      bias_s[i] = p.fast_mode ? (int32_t)((uint32_t)(b + p.f_add) * (uint32_t)p.f_mul) : b;
+    }
   }
   if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
   tc_fence_before();
@@ -421,8 +474,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       TDECL;
       TSTART(tk);
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
-        const int n_tile = tile % p.num_n_tiles;
-        const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
+        const TileOrigin to = tile_origin(p, tile);
+        const int m0 = to.m0;
         const int img = m0 / (p.oh * p.ow);
         const int rem = m0 - img * (p.oh * p.ow);
         const int oy = rem / p.ow;
@@ -440,13 +493,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           uint8_t* sa = smem + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + a_bytes;
           mbar_expect_tx(&bar_full[stage], (uint32_t)stage_bytes);
-          if (p.a_im2col)
+          if (p.a_mode == 2)  // the patch of this tile, shifted by the filter tap; zero fill outside the image
+            tma_load_4d(sa, &tmap_a, &bar_full[stage], cb * p.block_k, to.cw + fx * p.dil_w - p.pad_w,
+                        to.ch + fy * p.dil_h - p.pad_h, to.cn);
+          else if (p.a_mode == 1)
             tma_load_im2col_4d(sa, &tmap_a, &bar_full[stage], cb * p.block_k, base_w, base_h, img,
                                (uint16_t)(fx * p.dil_w), (uint16_t)(fy * p.dil_h));
           else
             tma_load_2d(sa, &tmap_a, &bar_full[stage], cb * p.block_k, m0);
-          tma_load_2d(sb, &tmap_b, &bar_full[stage], tap * p.c + cb * p.block_k,
-                      n_tile * p.block_n);
+          tma_load_2d(sb, &tmap_b, &bar_full[stage], tap * p.c + cb * p.block_k, to.n0);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
@@ -496,10 +551,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       TFLUSH(2);
       TFLUSH(3);
     }
-  } else {
+  } else if (warp < IO_WARP) {
     // ------------------------------------------------------------------ epilogue warps
     // Two groups of four warps; group g drains accumulator g, i.e. every second tile of this
-    // CTA, so the waits of one group (TMEM loads, barriers, TMA) hide behind the other's work.
+    // CTA, so the waits of one group (TMEM loads, barriers) hide behind the other's work.  On the
+    // TMA output path a group writes its tile into one of its staging buffers and hands it to the
+    // IO warp; it never waits for a store itself.
     const int ew = warp - 2;         // 0..7
     const int quarter = warp & 3;    // TMEM lanes 32*quarter .. +31 belong to this warp
     const int group = ew >> 2;
@@ -507,34 +564,43 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const bool has_res = p.tma_out && p.res_step >= 0;
     const int pw = p.panel_bytes;
     const int panel_size = BLOCK_M * pw;
+    const int buf_bytes = p.panels * panel_size;
     const bool leader = lane == 0 && (ew & 3) == 0;
-    uint8_t* io_base = smem + p.ring_bytes + (size_t)group * p.panels * panel_size;
+    uint8_t* group_base = smem + p.ring_bytes + (size_t)group * p.io_bufs * buf_bytes;
     const bool vec_ok = (p.y_dtype == CVMK_I8) ? (p.oc % 16 == 0) : (p.oc % 4 == 0);
     const int acc = group;
     const int stride_tiles = 2 * gridDim.x;
     const int first_tile = blockIdx.x + group * gridDim.x;
-    if (has_res && leader && first_tile < num_tiles) {
-      mbar_expect_tx(&bar_res[group], (uint32_t)(p.panels * panel_size));
-      for (int q = 0; q < p.panels; ++q)
-        tma_load_2d(io_base + (size_t)q * panel_size, &tmap_r, &bar_res[group],
-                    (first_tile % p.num_n_tiles) * p.block_n + q * 128, (first_tile / p.num_n_tiles) * BLOCK_M);
+    // patch mode: this thread's pixel inside the patch
+    int pr_w = 0, pr_h = 0, pr_n = 0;
+    if (p.a_mode == 2) {
+      pr_w = row_in_tile % p.patch_w;
+      const int r = row_in_tile / p.patch_w;
+      pr_h = r % p.patch_h;
+      pr_n = r / p.patch_h;
     }
     int k = 0;  // index of this group's tile
     TDECL;
+    (void)leader;
     for (int tile = first_tile; tile < num_tiles; tile += stride_tiles, ++k) {
-      const int n0 = (tile % p.num_n_tiles) * p.block_n;
-      const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
-      const int row = m0 + row_in_tile;
+      const TileOrigin to = tile_origin(p, tile);
+      const int n0 = to.n0;
+      int row = to.m0 + row_in_tile;  // linear output row; m_total marks a row outside the tensor
+      if (p.a_mode == 2) {
+        const int ow = to.cw + pr_w, oh = to.ch + pr_h, on = to.cn + pr_n;
+        row = (ow < p.ow && oh < p.oh && on * p.oh * p.ow < p.m_total) ? (on * p.oh + oh) * p.ow + ow : p.m_total;
+      }
+      const int buf = p.io_bufs == 2 ? (k & 1) : 0;
+      const uint32_t use = (uint32_t)(p.io_bufs == 2 ? (k >> 1) : k);  // how often this buffer was used before
+      uint8_t* io_base = group_base + (size_t)buf * buf_bytes;
       TSTART(tw);
       bool ok = mbar_wait(&bar_acc_full[acc], (uint32_t)(k & 1), &abort_flag, 4);
       TADD(4 + 4 * group, tw);
       tc_fence_after();
-      if (ok && p.tma_out) {
-        // staging is ours again: operand tile landed (join) / previous store has been read
-        if (has_res) ok = mbar_wait(&bar_res[group], (uint32_t)(k & 1), &abort_flag, 5);
-        else if (k > 0) ok = mbar_wait(&bar_res[group], (uint32_t)((k - 1) & 1), &abort_flag, 5);
-      }
+      // the staging buffer is ours: its previous store has been read, or the operand tile landed
+      if (ok && p.tma_out) ok = mbar_wait(&bar_res[group][buf], use & 1u, &abort_flag, 5);
       TADD(5 + 4 * group, tw);
+      if (!ok) break;
       if (ok) {
         const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
         if (p.fast_mode) {
@@ -616,42 +682,62 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
       tc_fence_before();
+      if (p.tma_out) fence_async_smem();  // make the staged bytes visible to the TMA engine
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
-      TADD(6 + 4 * group, tw);
-      if (p.tma_out) {
-        fence_async_smem();  // make the staged bytes visible to the TMA engine
-        // One thread decides for the whole group whether to go on, so that nobody is left alone
-        // at the next barrier.
-        if (leader) group_stop[group][k & 1] = abort_flag;
-        named_barrier(1 + group, 128);
-        const int stop = group_stop[group][k & 1];
-        if (leader && !stop) {
-          for (int q = 0; q < p.panels; ++q)
-            if (n0 + q * 128 < p.oc) tma_store_2d(&tmap_y, io_base + (size_t)q * panel_size, n0 + q * 128, m0);
-          tma_store_wait_read();  // the other group keeps the SM busy meanwhile
-          const int nt = tile + stride_tiles;
-          if (nt < num_tiles) {
-            if (has_res) {
-              mbar_expect_tx(&bar_res[group], (uint32_t)(p.panels * panel_size));
-              for (int q = 0; q < p.panels; ++q)
-                tma_load_2d(io_base + (size_t)q * panel_size, &tmap_r, &bar_res[group],
-                            (nt % p.num_n_tiles) * p.block_n + q * 128, (nt / p.num_n_tiles) * BLOCK_M);
-            } else {
-              mbar_arrive(&bar_res[group]);
-            }
-          }
-        }
-        TADD(7 + 4 * group, tw);
-        if (stop) break;
-      } else if (abort_flag) {
-        break;
+      if (lane == 0) {
+        mbar_arrive(&bar_acc_empty[acc]);
+        if (p.tma_out) mbar_arrive(&bar_staged[group][buf]);
       }
+      TADD(6 + 4 * group, tw);
+      if (abort_flag) break;
     }
 #ifdef CVMK_CONV_TIMING
     if (leader) { TFLUSH(4 + 4 * group); TFLUSH(5 + 4 * group); TFLUSH(6 + 4 * group); TFLUSH(7 + 4 * group); }
 #endif
-    if (p.tma_out && leader) tma_store_wait_all();
+  } else if (p.tma_out && lane == 0) {
+    // ------------------------------------------------------------------ IO warp
+    // Moves the staged tiles: waits until a group has written a buffer, stores it with TMA, waits
+    // until the TMA engine has read it, then hands the buffer back -- directly, or by loading the
+    // int8 operand tile of the tile that will use it next (residual joins).
+    const bool has_res = p.res_step >= 0;
+    const int panel_size = BLOCK_M * p.panel_bytes;
+    const int buf_bytes = p.panels * panel_size;
+    uint8_t* io_all = smem + p.ring_bytes;
+    auto buffer_of = [&](int g, int b) { return io_all + (size_t)(g * p.io_bufs + b) * buf_bytes; };
+    auto hand_back = [&](int g, int b, int next_tile) {
+      if (next_tile >= num_tiles) return;
+      if (!has_res) { mbar_arrive(&bar_res[g][b]); return; }
+      const TileOrigin to = tile_origin(p, next_tile);
+      uint8_t* dst = buffer_of(g, b);
+      mbar_expect_tx(&bar_res[g][b], (uint32_t)buf_bytes);
+      for (int q = 0; q < p.panels; ++q) {
+        if (p.a_mode == 2)
+          tma_load_4d(dst + (size_t)q * panel_size, &tmap_r, &bar_res[g][b], to.n0 + q * 128, to.cw, to.ch, to.cn);
+        else
+          tma_load_2d(dst + (size_t)q * panel_size, &tmap_r, &bar_res[g][b], to.n0 + q * 128, to.m0);
+      }
+    };
+    // every buffer starts free (or with the operand of its first tile on the way)
+    for (int g = 0; g < 2; ++g)
+      for (int b = 0; b < p.io_bufs; ++b) hand_back(g, b, (int)blockIdx.x + (2 * b + g) * (int)gridDim.x);
+    int i = 0;  // position in this CTA's tile sequence
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
+      const int g = i & 1, k = i >> 1;
+      const int b = p.io_bufs == 2 ? (k & 1) : 0;
+      const uint32_t use = (uint32_t)(p.io_bufs == 2 ? (k >> 1) : k);
+      if (!mbar_wait(&bar_staged[g][b], use & 1u, &abort_flag, 6)) break;
+      const TileOrigin to = tile_origin(p, tile);
+      const uint8_t* src = buffer_of(g, b);
+      for (int q = 0; q < p.panels; ++q) {
+        if (to.n0 + q * 128 >= p.oc) break;
+        if (p.a_mode == 2) tma_store_4d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.cw, to.ch, to.cn);
+        else tma_store_2d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.m0);
+      }
+      tma_store_commit();
+      tma_store_wait_read();
+      hand_back(g, b, tile + 2 * p.io_bufs * (int)gridDim.x);
+    }
+    tma_store_wait_all();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -726,6 +812,34 @@ CUresult encode_rows(EncodeTiledFn enc, CUtensorMap* map, const void* base, int6
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
+// 4-D int8 tensor map over an NHWC tensor [n, h, w, c] with a {box_c, box_w, box_h, box_n} box.
+CUresult encode_nhwc(EncodeTiledFn enc, CUtensorMap* map, const void* base, int64_t n, int64_t h, int64_t w,
+                     int64_t c, int box_c, int box_w, int box_h, int box_n, CUtensorMapL2promotion promo) {
+  cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)c, (cuuint64_t)(w * c), (cuuint64_t)(h * w * c)};
+  cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)box_w, (cuuint32_t)box_h, (cuuint32_t)box_n};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(box_c), promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
+// Spatial patches for stride-1 filters: an M tile of 128 output pixels is pw x ph pixels of pn
+// images (powers of two, pw * ph * pn = 128), so that the activations of one filter tap are one
+// plain tiled TMA box shifted by the tap.  Picks the split that wastes the fewest rows; false if
+// even that needs over a quarter more tiles than the linear order.
+bool pick_patch(const cvmk_conv_desc& d, int* pw, int* ph, int* pn) {
+  const int64_t linear = ((int64_t)d.N * d.OH * d.OW + BLOCK_M - 1) / BLOCK_M;
+  int64_t best = -1;
+  for (int w = BLOCK_M; w >= 1; w >>= 1) {
+    for (int h = 1; w * h <= BLOCK_M; h <<= 1) {
+      const int n = BLOCK_M / (w * h);
+      const int64_t tiles = (int64_t)((d.OW + w - 1) / w) * ((d.OH + h - 1) / h) * ((d.N + n - 1) / n);
+      if (best < 0 || tiles < best) { best = tiles; *pw = w; *ph = h; *pn = n; }
+    }
+  }
+  return best > 0 && best * 4 <= linear * 5;
+}
+
 }  // namespace
 }  // namespace cvmk
 
@@ -758,11 +872,15 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
 
   memset(plan, 0, sizeof(*plan));
   plan->d = *d;
-  const int bk = pick_block_k(d->C);
+  int bk = pick_block_k(d->C);
   const int bn = pick_block_n(d->OC);
-  plan->block_k = bk;
   plan->block_n = bn;
+  int patch_w = 0, patch_h = 0, patch_n = 0;
   plan->a_im2col = is_pointwise(*d) ? 0 : 1;
+  if (plan->a_im2col && d->stride_h == 1 && d->stride_w == 1 && !getenv("CVM_B200_NO_PATCH") &&
+      pick_patch(*d, &patch_w, &patch_h, &patch_n))
+    plan->a_im2col = 2;
+  plan->reserved[0] = patch_w; plan->reserved[1] = patch_h; plan->reserved[2] = patch_n;
 
   // Output path: int8 tiles leave through shared memory and a TMA store; the first int8 tensor
   // operand of the chain (a residual join) comes in by TMA as well.
@@ -780,10 +898,22 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   }
   plan->panels = bn == 256 ? 2 : 1;
   plan->panel_bytes = bn < 128 ? bn : 128;
-  plan->io_bufs = 2;  // one staging set per epilogue group
-  const int io_bytes = plan->tma_out ? plan->panels * plan->io_bufs * BLOCK_M * plan->panel_bytes : 0;
+  // Staging: each epilogue group owns one buffer, or two when they fit beside an operand ring that
+  // is still deep enough; short reductions (little work per output tile) may give up half of their
+  // K block for it.
+  const int group_bytes = plan->panels * BLOCK_M * plan->panel_bytes;
+  const int64_t k_all = (int64_t)d->KH * d->KW * d->C;
+  const int budget = SMEM_DYNAMIC_MAX - 1024;
+  plan->io_bufs = 1;
+  if (plan->tma_out && !getenv("CVM_B200_SINGLE_STAGING")) {
+    auto ring_depth = [&](int k) { return (budget - 4 * group_bytes) / ((BLOCK_M + bn) * k); };
+    if (ring_depth(bk) >= 3) plan->io_bufs = 2;
+    else if (bk == 128 && k_all <= 512 && ring_depth(64) >= 3) { plan->io_bufs = 2; bk = 64; }
+  }
+  plan->block_k = bk;
+  const int io_bytes = plan->tma_out ? 2 * plan->io_bufs * group_bytes : 0;
   const int stage_bytes = (BLOCK_M + bn) * bk;
-  int stages = (SMEM_DYNAMIC_MAX - 1024 - io_bytes) / stage_bytes;
+  int stages = (budget - io_bytes) / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) { set_error("conv2d_tc_prepare: tile does not fit shared memory"); return CVMK_ERR_UNSUPPORTED; }
   plan->stages = stages;
@@ -795,7 +925,10 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   CUtensorMap* ta = reinterpret_cast<CUtensorMap*>(plan->tmap_a);
   CUtensorMap* tb = reinterpret_cast<CUtensorMap*>(plan->tmap_b);
   CUresult r;
-  if (plan->a_im2col) {
+  if (plan->a_im2col == 2) {
+    r = encode_nhwc(enc_tiled, ta, d->x, d->N, d->H, d->W, d->C, bk, patch_w, patch_h, patch_n,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+  } else if (plan->a_im2col) {
     cuuint64_t dims[4] = {(cuuint64_t)d->C, (cuuint64_t)d->W, (cuuint64_t)d->H, (cuuint64_t)d->N};
     cuuint64_t strides[3] = {(cuuint64_t)d->C, (cuuint64_t)d->W * d->C,
                              (cuuint64_t)d->H * d->W * d->C};
@@ -812,16 +945,24 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   r = encode_rows(enc_tiled, tb, d->w, d->OC, k_total, bk, bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: weight tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
   if (plan->tma_out) {
-    r = encode_rows(enc_tiled, reinterpret_cast<CUtensorMap*>(plan->tmap_y), d->y, m_total, d->OC,
-                    plan->panel_bytes, BLOCK_M, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    auto encode_out = [&](unsigned char* map, const void* base, CUtensorMapL2promotion promo) {
+      CUtensorMap* m = reinterpret_cast<CUtensorMap*>(map);
+      if (plan->a_im2col == 2)
+        return encode_nhwc(enc_tiled, m, base, d->N, d->OH, d->OW, d->OC, plan->panel_bytes, patch_w, patch_h,
+                           patch_n, promo);
+      return encode_rows(enc_tiled, m, base, m_total, d->OC, plan->panel_bytes, BLOCK_M, promo);
+    };
+    r = encode_out(plan->tmap_y, d->y, CU_TENSOR_MAP_L2_PROMOTION_NONE);
     if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: output tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
     if (plan->res_step >= 0) {
-      r = encode_rows(enc_tiled, reinterpret_cast<CUtensorMap*>(plan->tmap_r), d->ep.s[plan->res_step].ptr,
-                      m_total, d->OC, plan->panel_bytes, BLOCK_M, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+      r = encode_out(plan->tmap_r, d->ep.s[plan->res_step].ptr, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
       if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: operand tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
     }
   }
-  const int64_t num_m_tiles = (m_total + BLOCK_M - 1) / BLOCK_M;
+  int64_t num_m_tiles = (m_total + BLOCK_M - 1) / BLOCK_M;
+  if (plan->a_im2col == 2)
+    num_m_tiles = (int64_t)((d->OW + patch_w - 1) / patch_w) * ((d->OH + patch_h - 1) / patch_h) *
+                  ((d->N + patch_n - 1) / patch_n);
   const int64_t num_n_tiles = (d->OC + bn - 1) / bn;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -846,8 +987,14 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.pad_h = d.pad_h; p.pad_w = d.pad_w;
   p.dil_h = d.dil_h; p.dil_w = d.dil_w;
   p.block_k = plan->block_k; p.block_n = plan->block_n;
-  p.stages = plan->stages; p.a_im2col = plan->a_im2col;
+  p.stages = plan->stages; p.a_mode = plan->a_im2col;
   p.num_m_tiles = (p.m_total + BLOCK_M - 1) / BLOCK_M;
+  if (p.a_mode == 2) {
+    p.patch_w = plan->reserved[0]; p.patch_h = plan->reserved[1]; p.patch_n = plan->reserved[2];
+    p.tiles_w = (d.OW + p.patch_w - 1) / p.patch_w;
+    p.tiles_h = (d.OH + p.patch_h - 1) / p.patch_h;
+    p.num_m_tiles = p.tiles_w * p.tiles_h * ((d.N + p.patch_n - 1) / p.patch_n);
+  }
   p.num_n_tiles = (d.OC + plan->block_n - 1) / plan->block_n;
   int cols = 2 * plan->block_n;
   int pow2 = 32;
@@ -888,7 +1035,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
       const int64_t lo1 = ((int64_t)rs.a + add) >> sh, hi1 = ((int64_t)rs.b + add) >> sh;
       const bool no_overflow = d.acc_bound + add < (int64_t)INT32_MAX;
       const bool fits16 = ((d.acc_bound + add) >> sh) < 32767;
-      const bool clamp_ok = lo1 >= -32767 && hi1 <= 32767 && lo1 <= hi1;
+      const bool clamp_ok = lo1 >= -32767 && hi1 <= 32767 && lo1 <= hi1 && sh <= 16;
       if (no_overflow && fits16 && clamp_ok) {
         auto x2 = [](int64_t v) { return (uint32_t)((uint32_t)(uint16_t)(int16_t)v | ((uint32_t)(uint16_t)(int16_t)v << 16)); };
         if (left == 1) {
@@ -906,6 +1053,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
           const int kind = p.fast_mode == 1 ? 0 : (p.f_sub ? 3 : (p.chain.s[i0 + 2].a == 0 ? 1 : 2));
           p.fast_variant = (lo1 == 0 ? 1 : 0) + 2 * kind;
           p.f_shift = sh;
+          p.f_mul = 1 << (16 - sh);
           p.f_add = (int)add;
           p.f_lo1 = x2(lo1);
           p.f_hi1 = x2(hi1);
