@@ -473,46 +473,82 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool live = true;
       TDECL;
       TSTART(tk);
+      // The loop below runs on one thread, so its own instruction latency bounds the rate of
+      // loads: the filter taps are walked with nested counters (no divisions), and everything
+      // that is constant for a tile is computed once per tile.
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t full0 = smem_u32(&bar_full[0]);
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
         const TileOrigin to = tile_origin(p, tile);
         const int m0 = to.m0;
-        const int img = m0 / (p.oh * p.ow);
-        const int rem = m0 - img * (p.oh * p.ow);
-        const int oy = rem / p.ow;
-        const int ox = rem - oy * p.ow;
-        const int base_w = ox * p.stride_w - p.pad_w;
-        const int base_h = oy * p.stride_h - p.pad_h;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          const int tap = kb / k_per_tap;
-          const int cb = kb - tap * k_per_tap;
-          const int fy = tap / p.kw;
-          const int fx = tap - fy * p.kw;
-          TSTART(tw);
-          if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
-          TADD(0, tw);
-          uint8_t* sa = smem + (size_t)stage * stage_bytes;
-          uint8_t* sb = sa + a_bytes;
-          mbar_expect_tx(&bar_full[stage], (uint32_t)stage_bytes);
-          if (p.a_mode == 2)  // the patch of this tile, shifted by the filter tap; zero fill outside the image
-            tma_load_4d(sa, &tmap_a, &bar_full[stage], cb * p.block_k, to.cw + fx * p.dil_w - p.pad_w,
-                        to.ch + fy * p.dil_h - p.pad_h, to.cn);
-          else if (p.a_mode == 1)
-            tma_load_im2col_4d(sa, &tmap_a, &bar_full[stage], cb * p.block_k, base_w, base_h, img,
-                               (uint16_t)(fx * p.dil_w), (uint16_t)(fy * p.dil_h));
-          else
-            tma_load_2d(sa, &tmap_a, &bar_full[stage], cb * p.block_k, m0);
-          tma_load_2d(sb, &tmap_b, &bar_full[stage], tap * p.c + cb * p.block_k, to.n0);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        int img = 0, base_w = 0, base_h = 0;
+        if (p.a_mode == 1) {
+          img = m0 / (p.oh * p.ow);
+          const int rem = m0 - img * (p.oh * p.ow);
+          const int oy = rem / p.ow;
+          const int ox = rem - oy * p.ow;
+          base_w = ox * p.stride_w - p.pad_w;
+          base_h = oy * p.stride_h - p.pad_h;
+        }
+        int kcol = 0;  // column of the weight matrix: tap * C + channel block
+        for (int fy = 0; live && fy < p.kh; ++fy) {
+          const int off_h = fy * p.dil_h;
+          for (int fx = 0; live && fx < p.kw; ++fx) {
+            const int off_w = fx * p.dil_w;
+            for (int cc = 0; cc < p.c; cc += p.block_k, kcol += p.block_k) {
+              TSTART(tw);
+              if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
+              TADD(0, tw);
+              const uint32_t sa = smem_base + (uint32_t)(stage * stage_bytes);
+              const uint32_t sb = sa + (uint32_t)a_bytes;
+              const uint32_t bar = full0 + 8u * (uint32_t)stage;
+              asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                           "r"((uint32_t)stage_bytes) : "memory");
+              TADD(13, tw);
+              if (p.a_mode == 2)  // the patch of this tile, shifted by the filter tap; zero fill outside the image
+                asm volatile(
+                    "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                    " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)),
+                    "r"(bar), "r"(cc), "r"(to.cw + off_w - p.pad_w), "r"(to.ch + off_h - p.pad_h), "r"(to.cn)
+                    : "memory");
+              else if (p.a_mode == 1)
+                asm volatile(
+                    "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+                    " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(sa),
+                    "l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(bar), "r"(cc), "r"(base_w), "r"(base_h), "r"(img),
+                    "h"((uint16_t)off_w), "h"((uint16_t)off_h)
+                    : "memory");
+              else
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                    " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(bar),
+                    "r"(cc), "r"(m0)
+                    : "memory");
+              TADD(14, tw);
+              asm volatile(
+                  "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                  " [%0], [%1, {%3, %4}], [%2];" ::"r"(sb), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(bar),
+                  "r"(kcol), "r"(to.n0)
+                  : "memory");
+              TADD(15, tw);
+              if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            }
+          }
         }
       }
       TADD(12, tk);
       TFLUSH(0);
       TFLUSH(12);
+      TFLUSH(13);
+      TFLUSH(14);
+      TFLUSH(15);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_i8(p.block_n);
+      const uint64_t desc_a0 = umma_desc(smem_u32(smem), p.block_k);
+      const int nk = p.block_k / 32;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -530,14 +566,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (!mbar_wait(&bar_full[stage], phase, &abort_flag, 3)) { live = false; break; }
           TADD(2, tw);
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
-          const uint32_t sb = sa + a_bytes;
-          const uint64_t da = umma_desc(sa, p.block_k);
-          const uint64_t db = umma_desc(sb, p.block_k);
-          const int nk = p.block_k / 32;
-          for (int j = 0; j < nk; ++j)
-            mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc,
-                   (kb > 0 || j > 0) ? 1u : 0u);
+          // descriptors of this stage: the start-address field counts 16-byte units
+          const uint64_t da = desc_a0 + (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
+          const uint64_t db = da + (uint64_t)((uint32_t)a_bytes >> 4);
+          mma_i8(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
+          for (int j = 1; j < nk; ++j) mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
           mma_commit(&bar_empty[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
