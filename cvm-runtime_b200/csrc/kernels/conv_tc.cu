@@ -39,8 +39,11 @@ constexpr int MAX_STAGES = 8;
 constexpr int NUM_EPI_WARPS = 8;
 // warp 0: TMA loads of the operands, warp 1: MMA + TMEM owner, warps 2..9: epilogue,
 // warp 10: TMA traffic of the staged output tiles (stores, residual-operand loads)
-constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS + 32;
+// warp 11: second TMA producer (issuing a load costs its thread about a hundred cycles, so two
+// threads take alternate K blocks)
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS + 64;
 constexpr int IO_WARP = 2 + NUM_EPI_WARPS;
+constexpr int PRODUCER2_WARP = IO_WARP + 1;
 constexpr uint32_t SPIN_LIMIT = 1u << 19;  // x 2 us per hardware wait
 constexpr int SMEM_DYNAMIC_MAX = 227 * 1024 - 8704;  // 227 KB per CTA minus the static part (bias, barriers)
 constexpr int MAX_BIAS = 2048;          // bias vectors up to this length are staged in shared memory
@@ -465,11 +468,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == PRODUCER2_WARP) {
+    // ------------------------------------------------------------------ TMA producers
+    // Producer `which` issues the K blocks whose running number (over all tiles of this CTA) is
+    // congruent to it modulo 2; both walk the same sequence of ring slots.
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
+      const int which = warp == 0 ? 0 : 1;
+      int stage = which % p.stages;
+      uint32_t phase = which >= p.stages ? 1u : 0u;
+      int turn = which;  // K blocks to skip before the next one of this producer
       bool live = true;
       TDECL;
       TSTART(tk);
@@ -496,6 +503,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int fx = 0; live && fx < p.kw; ++fx) {
             const int off_w = fx * p.dil_w;
             for (int cc = 0; cc < p.c; cc += p.block_k, kcol += p.block_k) {
+              if (turn != 0) { turn = 0; continue; }
+              turn = 1;
               TSTART(tw);
               if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
               TADD(0, tw);
@@ -531,17 +540,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   "r"(kcol), "r"(to.n0)
                   : "memory");
               TADD(15, tw);
-              if (++stage == p.stages) { stage = 0; phase ^= 1; }
+              stage += 2;
+              if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
             }
           }
         }
       }
       TADD(12, tk);
-      TFLUSH(0);
-      TFLUSH(12);
-      TFLUSH(13);
-      TFLUSH(14);
-      TFLUSH(15);
+#ifdef CVMK_CONV_TIMING
+      if (which == 0) { TFLUSH(0); TFLUSH(12); TFLUSH(13); TFLUSH(14); TFLUSH(15); }
+#endif
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
