@@ -401,6 +401,39 @@ struct Lowering {
     int8_t* wdev = (int8_t*)ex.dalloc(w8.size());
     CUDA_OK(cudaMemcpy(wdev, w8.data(), w8.size(), cudaMemcpyHostToDevice));
 
+    // Stem on the tensor cores without a patch matrix: the network input itself, few channels.
+    if (via_pack && ex_ == data_eid && raw_in.dtype == CVMK_I8 && dh == 1 && dw == 1 && out.dtype == CVMK_I8 &&
+        !getenv("CVM_B200_NO_STEM_FUSED")) {
+      cvmk_stem_conv_desc sd;
+      memset(&sd, 0, sizeof(sd));
+      sd.x = (const int8_t*)raw_in.ptr; sd.y = out.ptr;
+      sd.N = N; sd.H = H; sd.W = W; sd.C = C; sd.OC = OC; sd.KH = KH; sd.KW = KW; sd.OH = OH; sd.OW = OW;
+      sd.stride_h = sh; sd.stride_w = sw; sd.pad_h = ph; sd.pad_w = pw;
+      sd.clamp = data_range;
+      sd.status = ex.status_dev_;
+      sd.acc_bound = probe.acc_bound;
+      sd.ep = ch.ep;
+      if (cvmk_conv2d_stem_supported(&sd)) {
+        // [KH][OC][32]: byte kx * C + c of row (ky, oc) = w[oc][c][ky][kx], the rest zero
+        std::vector<int8_t> ws((size_t)KH * OC * 32, 0);
+        for (int o = 0; o < OC; ++o)
+          for (int c = 0; c < C; ++c)
+            for (int ky = 0; ky < KH; ++ky)
+              for (int kx = 0; kx < KW; ++kx)
+                ws[((size_t)ky * OC + o) * 32 + kx * C + c] = (int8_t)wt.data[(((size_t)o * C + c) * KH + ky) * KW + kx];
+        int8_t* wsdev = (int8_t*)ex.dalloc(ws.size());
+        CUDA_OK(cudaMemcpy(wsdev, ws.data(), ws.size(), cudaMemcpyHostToDevice));
+        sd.w = wsdev;
+        void* mem = nullptr;
+        CHECK(posix_memalign(&mem, 64, sizeof(cvmk_stem_conv_plan)) == 0);
+        ex.stem_plans_.emplace_back((cvmk_stem_conv_plan*)mem, plan_deleter);
+        cvmk_stem_conv_plan* plan = ex.stem_plans_.back().get();
+        KERNEL_OK(cvmk_conv2d_stem_prepare(&sd, plan));
+        add_step(label + "[stem]", [plan](cudaStream_t s) { return cvmk_conv2d_stem_launch(plan, s); });
+        return;
+      }
+    }
+
     if (via_pack) {
       int8_t* amat = (int8_t*)ex.dalloc((size_t)packed.N * kp);
       cvmk_stem_pack_desc sp;

@@ -71,6 +71,7 @@ class Executor {
   std::vector<void*> allocs_;
   std::vector<void*> pinned_;
   std::vector<std::unique_ptr<cvmk_conv_plan, void (*)(void*)>> plans_;
+  std::vector<std::unique_ptr<cvmk_stem_conv_plan, void (*)(void*)>> stem_plans_;
   size_t device_bytes_ = 0;
   // input staging
   void* in_host_ = nullptr;

@@ -202,6 +202,54 @@ __global__ void __launch_bounds__(256) reduce_kernel(const __grid_constant__ Red
 // max_pool2d, NHWC.  int8: one thread owns 16 channels of one output pixel (vmax4 on packed
 // bytes); int32: 4 channels.  Taps outside the image are skipped, which equals a max with INT_MIN
 // because the reference guarantees at least one tap inside (pad < pool size).
+// One thread per 16 neighbouring outputs (innermost kept extent, counted in groups of 16 here).
+__global__ void __launch_bounds__(128) reduce_vec16_kernel(const __grid_constant__ ReduceParams p) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+    int64_t rem = i, base = 0;
+#pragma unroll
+    for (int k = 5; k >= 0; --k) {
+      if (k < p.n_keep) {
+        const int64_t c = rem % p.ke[k];
+        rem /= p.ke[k];
+        base += c * (k == p.n_keep - 1 ? 16 : p.ks[k]);
+      }
+    }
+    const int8_t* src = reinterpret_cast<const int8_t*>(p.x) + base;
+    int32_t acc[16];
+    int64_t r0 = 0;
+    if (p.init_zero) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = 0;
+    } else {
+      const int4 raw = __ldg(reinterpret_cast<const int4*>(src));
+      const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = (int32_t)(int8_t)(w[j >> 2] >> ((j & 3) * 8));
+      r0 = 1;
+    }
+#pragma unroll 4
+    for (int64_t r = r0; r < p.red_total; ++r) {
+      const int4 raw = __ldg(reinterpret_cast<const int4*>(src + r * p.rs[0]));
+      const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int32_t val = (int32_t)(int8_t)(w[j >> 2] >> ((j & 3) * 8));
+        if (p.is_max) acc[j] = acc[j] < val ? val : acc[j];
+        else acc[j] = (int32_t)((uint32_t)acc[j] + (uint32_t)val);
+      }
+    }
+    apply_chain<16>(p.chain, acc, (size_t)i * 16, 0, 0);
+    if (p.yd == CVMK_I8) {
+      reinterpret_cast<int4*>(p.y)[i] = pack16(acc);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        reinterpret_cast<int4*>(p.y)[i * 4 + q] = make_int4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+    }
+  }
+}
+
 struct PoolParams {
   const void* x; void* y;
   int N, H, W, C, OH, OW, KH, KW, sh, sw, ph, pw;
@@ -354,6 +402,36 @@ extern "C" int cvmk_strided(const cvmk_strided_desc* d, cvmk_stream_t stream) {
 }
 
 extern "C" int cvmk_reduce(const cvmk_reduce_desc* d, cvmk_stream_t stream) {
+  // Channels-last reductions over the spatial extents (global pooling as sum + shift): int8 input,
+  // one run of reduced elements at a constant stride, kept innermost extent contiguous -> each
+  // thread owns 16 neighbouring outputs and reads 16-byte vectors.
+  if (d && d->x && d->y && d->x_dtype == CVMK_I8 && d->n_keep >= 1 && d->n_keep <= 6 && d->n_red >= 1) {
+    int64_t re = d->red_extent[d->n_red - 1], rs = d->red_stride[d->n_red - 1];
+    bool one_run = true;
+    for (int k = d->n_red - 2; k >= 0 && one_run; --k) {
+      one_run = d->red_stride[k] == rs * re;
+      re *= d->red_extent[k];
+    }
+    const int in = d->n_keep - 1;
+    bool ok = one_run && d->keep_stride[in] == 1 && d->keep_extent[in] % 16 == 0 && rs % 16 == 0 && aligned16(d->x) &&
+              (d->y_dtype == CVMK_I32 ? aligned16(d->y) : aligned16(d->y));
+    for (int k = 0; ok && k < in; ++k) ok = d->keep_stride[k] % 16 == 0;
+    if (ok) {
+      ReduceParams p;
+      memset(&p, 0, sizeof(p));
+      p.is_max = d->is_max; p.init_zero = d->init_zero; p.n_keep = d->n_keep; p.n_red = 1;
+      p.total = 1;
+      for (int k = 0; k < d->n_keep; ++k) { p.ke[k] = d->keep_extent[k]; p.ks[k] = d->keep_stride[k]; p.total *= p.ke[k]; }
+      p.ke[in] /= 16;
+      p.total /= 16;
+      p.re[0] = re; p.rs[0] = rs; p.red_total = re;
+      p.x = d->x; p.y = d->y; p.xd = d->x_dtype; p.yd = d->y_dtype;
+      int rc = lower_chain(d->ep, &p.chain);
+      if (rc != CVMK_OK) return rc;
+      reduce_vec16_kernel<<<grid_for(p.total, 128), 128, 0, (cudaStream_t)stream>>>(p);
+      return check_cuda(cudaGetLastError(), "reduce_vec16_kernel launch");
+    }
+  }
   if (!d || !d->x || !d->y || d->n_keep < 0 || d->n_keep > 6 || d->n_red < 0 || d->n_red > 6) {
     set_error("reduce: bad argument");
     return CVMK_ERR_ARG;

@@ -283,6 +283,42 @@ typedef struct {
 CVMK_API int cvmk_where(const cvmk_where_desc* d, cvmk_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * conv2d of the network input itself when it has 1..4 channels (image stems), groups = 1
+ * (cpu/ops/ops.cc:368-456 after the input clamp of graph_runtime.cc:379-386), on the tensor cores
+ * without an intermediate patch matrix.
+ *   x : the input as the C-ABI delivers it, NCHW int8 [N, C, H, W]; values are clamped to +-clamp
+ *   w : int8 [KH][OC][32]: row ky of output channel oc holds w[oc][c][ky][kx] at byte kx * C + c,
+ *       zero in the remaining bytes (KW * C <= 32)
+ *   y : NHWC int8 [N, OH, OW, OC], OC in {32, 64, 128}; chain as for cvmk_conv2d_tc_*
+ * No dilation.  prepare() encodes the output tensor map; the plan must be 64-byte aligned.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const int8_t* x;
+  const int8_t* w;
+  void* y;
+  int32_t N, H, W, C;
+  int32_t OC, KH, KW;
+  int32_t OH, OW;
+  int32_t stride_h, stride_w, pad_h, pad_w;
+  int32_t clamp;
+  int32_t* status;
+  int64_t acc_bound;   /* as in cvmk_conv_desc */
+  cvmk_epilogue ep;
+} cvmk_stem_conv_desc;
+
+typedef struct __attribute__((aligned(64))) {
+  unsigned char tmap_y[128];
+  cvmk_stem_conv_desc d;
+  int32_t grid;
+  int32_t smem_bytes;
+  int32_t reserved[6];
+} cvmk_stem_conv_plan;
+
+CVMK_API int cvmk_conv2d_stem_supported(const cvmk_stem_conv_desc* d);
+CVMK_API int cvmk_conv2d_stem_prepare(const cvmk_stem_conv_desc* d, cvmk_stem_conv_plan* plan);
+CVMK_API int cvmk_conv2d_stem_launch(const cvmk_stem_conv_plan* plan, cvmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * get_valid_counts (cpu/ops/nms.cc:42-63): per batch keep rows with row[1] > score_threshold in
  * their original order, write their number to valid_count[b], fill the remaining rows with -1.
  * x, y: int32 [B, N, K]; valid_count: int32 [B].

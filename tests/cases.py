@@ -83,6 +83,25 @@ def op_cases():
     add("conv_tc_5x5_s2_nobias", lambda: conv_case(4, 2, 32, 13, 13, 40, 5, 2, 2, bias=False, shift=10))
     add("conv_tc_int32_out", lambda: conv_case(5, 1, 64, 6, 6, 24, 3, 1, 1, shift=0))
     add("conv_stem_7x7", lambda: conv_case(6, 2, 3, 30, 30, 16, 7, 2, 3, shift=8, relu=True))
+    # image stems on the tensor cores (1..4 input channels, 32/64/128 output channels)
+    add("conv_stem_fused_7x7_s2", lambda: conv_case(30, 2, 3, 32, 32, 64, 7, 2, 3, shift=8, relu=True))
+    add("conv_stem_fused_3x3_s2_oc32", lambda: conv_case(31, 3, 3, 33, 30, 32, 3, 2, 1, shift=7, relu=True))
+    add("conv_stem_fused_3x3_s1_oc128", lambda: conv_case(32, 1, 3, 17, 48, 128, 3, 1, 1, shift=7))
+    add("conv_stem_fused_wide_row", lambda: conv_case(33, 1, 1, 6, 300, 32, 5, 1, 2, shift=6, relu=True))
+    add("conv_stem_fused_4ch_nobias", lambda: conv_case(34, 2, 4, 20, 16, 64, 5, 2, 0, bias=False, shift=8))
+    add("conv_stem_fused_1x1", lambda: conv_case(35, 2, 2, 9, 16, 32, 1, 1, 0, shift=3))
+    add("conv_stem_fused_s3_rows", lambda: conv_case(36, 1, 3, 37, 32, 64, 7, 3, 2, shift=8, relu=True))
+    def stem_generic():
+        rng = np.random.RandomState(37)
+        g = wl.GraphBuilder(37)
+        x = rnd(rng, (2, 3, 18, 32), 8)
+        d = g.var("data", x.shape, 8)
+        y = g.conv(d, 64, 3, 1, 1, relu=True, shift=7)
+        y = g.op("cvm_clip", [y], g.shape_of(y), {"precision": 6})
+        y = g.op("negative", [y], g.shape_of(y))
+        js, pb = g.finish(y)
+        return js, pb, x
+    add("conv_stem_fused_generic_chain", stem_generic)
     add("conv_odd_channels", lambda: conv_case(7, 1, 5, 8, 8, 7, 3, 1, 1, shift=7))
     add("conv_depthwise", lambda: conv_case(8, 2, 32, 10, 10, 32, 3, 1, 1, groups=32, shift=6, relu=True))
     add("conv_depthwise_s2", lambda: conv_case(9, 1, 48, 9, 9, 48, 3, 2, 1, groups=48, shift=6))
