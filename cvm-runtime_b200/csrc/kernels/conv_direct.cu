@@ -138,6 +138,85 @@ __global__ void __launch_bounds__(128) depthwise_kernel(const __grid_constant__ 
 }
 
 
+// Depthwise 3x3, int8 NHWC, channels a multiple of 4, no dilation, stride S in {1, 2}: one thread
+// owns 4 channels (one 32-bit word per pixel) of a whole output row and walks it in strips of 4
+// pixels.  Its 36 weights (and the bias, when the chain starts with one) are unpacked into
+// registers once per row; every input word is unpacked once per strip and feeds all the outputs
+// it belongs to, so the inner loop is one multiply-add per product.
+template <int S>
+__global__ void __launch_bounds__(256) depthwise3x3_kernel(const __grid_constant__ DirectParams p) {
+  constexpr int PX = 4;
+  constexpr int IN = (PX - 1) * S + 3;  // input pixels of a row that a strip touches
+  const int cw = p.C / 4;
+  const int64_t total = (int64_t)p.N * p.OH * cw;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const bool has_bias = p.chain.n > 0 && p.chain.s[0].op == K_ADD_C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int cv = (int)(i % cw);
+    const int row = (int)(i / cw);
+    const int oy = row % p.OH;
+    const int n = row / p.OH;
+    int32_t wgt[9][4];
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      const int w = __ldg(reinterpret_cast<const int*>(p.w + (int64_t)t * p.C) + cv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) wgt[t][k] = (int32_t)(int8_t)(w >> (k * 8));
+    }
+    int32_t bias[4] = {0, 0, 0, 0};
+    if (has_bias) {
+      const int4 b4 = __ldg(reinterpret_cast<const int4*>(p.chain.s[0].ptr) + cv);
+      bias[0] = b4.x; bias[1] = b4.y; bias[2] = b4.z; bias[3] = b4.w;
+    }
+    const int* rows[3];
+#pragma unroll
+    for (int fy = 0; fy < 3; ++fy) {
+      const int iy = oy * S + fy - p.ph;
+      rows[fy] = (iy < 0 || iy >= p.H) ? nullptr
+               : reinterpret_cast<const int*>(reinterpret_cast<const int8_t*>(p.x) + ((int64_t)n * p.H + iy) * p.W * p.C) + cv;
+    }
+    const int64_t out_row = ((int64_t)n * p.OH + oy) * p.OW;
+    for (int ox0 = 0; ox0 < p.OW; ox0 += PX) {
+      int32_t acc[PX][4];
+#pragma unroll
+      for (int q = 0; q < PX; ++q)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[q][k] = bias[k];
+      const int ix0 = ox0 * S - p.pw;
+#pragma unroll
+      for (int fy = 0; fy < 3; ++fy) {
+        if (!rows[fy]) continue;
+#pragma unroll
+        for (int j = 0; j < IN; ++j) {
+          const int ix = ix0 + j;
+          if (ix < 0 || ix >= p.W) continue;
+          const int xw = __ldg(rows[fy] + ix * cw);
+          int32_t xv[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) xv[k] = (int32_t)(int8_t)(xw >> (k * 8));
+#pragma unroll
+          for (int fx = 0; fx < 3; ++fx) {
+            if ((j - fx) % S != 0 || j - fx < 0 || (j - fx) / S >= PX) continue;  // resolved at compile time
+            const int q = (j - fx) / S;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[q][k] += xv[k] * wgt[fy * 3 + fx][k];
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < PX; ++q) {
+        if (ox0 + q >= p.OW) continue;
+        const int64_t lin = (out_row + ox0 + q) * p.C + cv * 4;
+        apply_chain<4>(p.chain, acc[q], (size_t)lin, cv * 4, 1, nullptr, -1, has_bias ? 1 : 0);
+        if (p.yd == CVMK_I8)
+          *reinterpret_cast<uint32_t*>(reinterpret_cast<int8_t*>(p.y) + lin) = pack4(acc[q][0], acc[q][1], acc[q][2], acc[q][3]);
+        else
+          *reinterpret_cast<int4*>(reinterpret_cast<int32_t*>(p.y) + lin) = make_int4(acc[q][0], acc[q][1], acc[q][2], acc[q][3]);
+      }
+    }
+  }
+}
+
 // Patch gather: one thread builds 16 consecutive bytes of one row of A.  The (fy, fx, c) split
 // of every k is looked up in a shared-memory table built once per block.
 struct PackParams {
@@ -298,6 +377,13 @@ extern "C" int cvmk_conv2d_direct(const cvmk_conv_direct_desc* d, cvmk_stream_t 
         ((uintptr_t)d->x & 15) || ((uintptr_t)d->w & 15) || ((uintptr_t)d->y & 15)) {
       set_error("conv2d_direct: depthwise path needs int8 NHWC, C %% 16 == 0, 16-byte aligned operands");
       return CVMK_ERR_UNSUPPORTED;
+    }
+    if (d->KH == 3 && d->KW == 3 && d->dil_h == 1 && d->dil_w == 1 && d->stride_h == d->stride_w &&
+        (d->stride_h == 1 || d->stride_h == 2)) {
+      const int64_t work3 = (int64_t)d->N * d->OH * (d->C / 4);
+      if (d->stride_h == 1) depthwise3x3_kernel<1><<<grid_sized(work3, 256), 256, 0, s>>>(p);
+      else depthwise3x3_kernel<2><<<grid_sized(work3, 256), 256, 0, s>>>(p);
+      return check_cuda(cudaGetLastError(), "depthwise3x3_kernel launch");
     }
     const int64_t work = (int64_t)d->N * d->OH * ((d->OW + 3) / 4) * (d->C / 16);
     depthwise_kernel<4><<<grid_sized(work, 128), 128, 0, s>>>(p);
