@@ -80,6 +80,7 @@ struct ConvParams {
   uint32_t f_lo1, f_hi1;  // first clamp, both halves of an s16x2 word
   uint32_t f_lo2, f_hi2;  // clamp after the tensor step
   int f_sub;            // tensor step subtracts its operand
+  int dbg;              // development builds: bit 0 skips the weight loads (timing experiments only)
   int fast_variant;     // (first clamp starts at 0) + 2 * kind; kind: 0 none, 1 add + clamp from 0, 2 add, 3 subtract
   DevChain chain;
 };
@@ -286,8 +287,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               const uint32_t sa = smem_base + (uint32_t)(stage * stage_bytes);
               const uint32_t sb = sa + (uint32_t)a_bytes;
               const uint32_t bar = full0 + 8u * (uint32_t)stage;
+#ifdef CVMK_CONV_TIMING
+              const uint32_t tx_bytes = (p.dbg & 1) ? (uint32_t)a_bytes : (uint32_t)stage_bytes;
+#else
+              const uint32_t tx_bytes = (uint32_t)stage_bytes;
+#endif
               asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                           "r"((uint32_t)stage_bytes) : "memory");
+                           "r"(tx_bytes) : "memory");
               TADD(13, tw);
               if (p.a_mode == 2)  // the patch of this tile, shifted by the filter tap; zero fill outside the image
                 asm volatile(
@@ -309,6 +315,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     "r"(cc), "r"(m0)
                     : "memory");
               TADD(14, tw);
+#ifdef CVMK_CONV_TIMING
+              if (!(p.dbg & 1))
+#endif
               asm volatile(
                   "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                   " [%0], [%1, {%3, %4}], [%2];" ::"r"(sb), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(bar),
@@ -352,8 +361,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // descriptors of this stage: the start-address field counts 16-byte units
           const uint64_t da = desc_a0 + (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
           const uint64_t db = da + (uint64_t)((uint32_t)a_bytes >> 4);
+#ifdef CVMK_CONV_TIMING
+          if (p.dbg & 2) {  // timing experiment (wrong results): break the accumulator dependence
+            for (int j = 0; j < nk; ++j)
+              mma_i8(d_tmem + (uint32_t)(((kb * nk + j) & 3) * 64), da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
+          } else
+#endif
+          {
           mma_i8(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
           for (int j = 1; j < nk; ++j) mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
+          }
           mma_commit(&bar_empty[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -653,6 +670,11 @@ bool pick_patch(const cvmk_conv_desc& d, int* pw, int* ph, int* pn) {
       if (best < 0 || tiles < best) { best = tiles; *pw = w; *ph = h; *pn = n; }
     }
   }
+#ifdef CVMK_CONV_TIMING
+  if (const char* e = getenv("CVM_PATCH")) {  // development builds: force a patch shape "w,h,n"
+    if (sscanf(e, "%d,%d,%d", pw, ph, pn) == 3 && *pw * *ph * *pn == BLOCK_M) return true;
+  }
+#endif
   return best > 0 && best * 4 <= linear * 5;
 }
 
@@ -818,6 +840,13 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.tmem_cols = pow2;
   p.status = d.status;
   p.tma_out = plan->tma_out; p.res_step = plan->res_step;
+#ifdef CVMK_CONV_TIMING
+  p.dbg = getenv("CVM_DBG") ? atoi(getenv("CVM_DBG")) : 0;
+  if (getenv("CVM_HINT")) {
+    const uint32_t h = (uint32_t)atoi(getenv("CVM_HINT"));
+    cudaMemcpyToSymbol(tc::g_wait_hint, &h, sizeof(h));
+  }
+#endif
   p.panels = plan->panels; p.panel_bytes = plan->panel_bytes;
   p.io_bufs = plan->io_bufs; p.ring_bytes = plan->ring_bytes;
   int rc = lower_chain(d.ep, &p.chain);

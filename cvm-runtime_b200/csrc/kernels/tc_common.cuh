@@ -11,6 +11,9 @@ namespace tc {
 
 constexpr int BLOCK_M = 128;
 constexpr uint32_t SPIN_LIMIT = 1u << 19;  // x 2 us per hardware wait
+#ifdef CVMK_CONV_TIMING
+__device__ uint32_t g_wait_hint = 2000u;  // development builds: suspend-time hint of the waits, settable
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -49,7 +52,11 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int code) {
   for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+#ifdef CVMK_CONV_TIMING
+    if (mbar_try(bar, parity, g_wait_hint)) return true;
+#else
     if (mbar_try(bar, parity, 2000u)) return true;
+#endif
     if (*abort_flag) return false;
   }
   *abort_flag = code;
