@@ -168,12 +168,16 @@ __global__ void __launch_bounds__(256) depthwise3x3_kernel(const __grid_constant
       const int4 b4 = __ldg(reinterpret_cast<const int4*>(p.chain.s[0].ptr) + cv);
       bias[0] = b4.x; bias[1] = b4.y; bias[2] = b4.z; bias[3] = b4.w;
     }
+    // Rows and columns outside the image are read from a clamped (valid) address and masked to
+    // zero, so that all loads of a strip are independent and in flight together.
     const int* rows[3];
+    bool row_ok[3];
 #pragma unroll
     for (int fy = 0; fy < 3; ++fy) {
       const int iy = oy * S + fy - p.ph;
-      rows[fy] = (iy < 0 || iy >= p.H) ? nullptr
-               : reinterpret_cast<const int*>(reinterpret_cast<const int8_t*>(p.x) + ((int64_t)n * p.H + iy) * p.W * p.C) + cv;
+      row_ok[fy] = iy >= 0 && iy < p.H;
+      const int iyc = min(max(iy, 0), p.H - 1);
+      rows[fy] = reinterpret_cast<const int*>(reinterpret_cast<const int8_t*>(p.x) + ((int64_t)n * p.H + iyc) * p.W * p.C) + cv;
     }
     const int64_t out_row = ((int64_t)n * p.OH + oy) * p.OW;
     for (int ox0 = 0; ox0 < p.OW; ox0 += PX) {
@@ -183,14 +187,21 @@ __global__ void __launch_bounds__(256) depthwise3x3_kernel(const __grid_constant
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[q][k] = bias[k];
       const int ix0 = ox0 * S - p.pw;
+      int xin[3][IN];
 #pragma unroll
       for (int fy = 0; fy < 3; ++fy) {
-        if (!rows[fy]) continue;
 #pragma unroll
         for (int j = 0; j < IN; ++j) {
           const int ix = ix0 + j;
-          if (ix < 0 || ix >= p.W) continue;
-          const int xw = __ldg(rows[fy] + ix * cw);
+          const int v = __ldg(rows[fy] + min(max(ix, 0), p.W - 1) * cw);
+          xin[fy][j] = (row_ok[fy] && ix >= 0 && ix < p.W) ? v : 0;
+        }
+      }
+#pragma unroll
+      for (int fy = 0; fy < 3; ++fy) {
+#pragma unroll
+        for (int j = 0; j < IN; ++j) {
+          const int xw = xin[fy][j];
           int32_t xv[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) xv[k] = (int32_t)(int8_t)(xw >> (k * 8));
