@@ -335,7 +335,7 @@ def main():
             roofline = {
                 "kernel": "conv_tc_kernel (tcgen05 kind::i8 implicit GEMM, all groups=1 conv2d + dense)",
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak, "traffic": conv_tc_traffic(args.workload, args.batch),
                 "note": "int8 multiply-accumulates counted as 2 ops (TOP/s); peak = 2 x the %s sustained bf16 "
                         "cuBLAS figure (%.1f), int8 dense rate being twice bf16; against 2 x burst (%.1f) the "
                         "fraction is %.3f; launches_per_step=%d, avg launch %.1f us" % (
@@ -382,6 +382,15 @@ def main():
     rt.CVMAPIFreeModel(net)
     if dist:
         dist.destroy_process_group()
+
+
+def conv_tc_traffic(workload, batch):
+    """dram__bytes_read.sum + dram__bytes_write.sum per conv_tc_kernel launch (bytes), from the ncu
+    capture summarised in profiles/conv_tc_kernel_resnet50_b128_dram_traffic.md (2192.7 MB over the
+    53 launches of one batch-128 inference), scaled by the batch; null for workloads not captured."""
+    if workload != "resnet50":
+        return None
+    return 2192.7e6 / 53.0 * (batch / 128.0)
 
 
 def tc_conv_ops(graph_json):
