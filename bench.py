@@ -170,7 +170,9 @@ def cpu_baseline(oracle, wl, workload, sample_batch, repeats=1):
     js, pb, x = make_workload(wl, workload, sample_batch)
     cores = os.cpu_count() or 1
     if oracle.ref_lib.available():
-        os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+        # all host threads, also under torchrun (which exports OMP_NUM_THREADS=1 to its workers);
+        # set before the reference library, and with it the OpenMP runtime, is loaded
+        os.environ["OMP_NUM_THREADS"] = str(cores)
         m = oracle.ref_lib.RefModel(js, pb, 0)
         if not m.loaded:
             raise RuntimeError("reference refused the sample model")

@@ -265,20 +265,50 @@ __global__ void __launch_bounds__(256) pool_vec_kernel(const __grid_constant__ P
     const int ox = (int)(pix % p.OW); pix /= p.OW;
     const int oy = (int)(pix % p.OH);
     const int n = (int)(pix / p.OH);
+    // Taps outside the image are read from a clamped (valid) address and replaced by the
+    // identity of max, so the loads of a window are independent of each other.  Signed bytes are
+    // compared as s16x2: even and odd bytes are moved into the high byte of each half.
     int4 m;
-    if (DT == CVMK_I8) m = make_int4(0x80808080, 0x80808080, 0x80808080, 0x80808080);
-    else m = make_int4(INT32_MIN, INT32_MIN, INT32_MIN, INT32_MIN);
-    for (int fy = 0; fy < p.KH; ++fy) {
-      const int iy = oy * p.sh + fy - p.ph;
-      if (iy < 0 || iy >= p.H) continue;
-      for (int fx = 0; fx < p.KW; ++fx) {
-        const int ix = ox * p.sw + fx - p.pw;
-        if (ix < 0 || ix >= p.W) continue;
-        const int4 v = __ldg(reinterpret_cast<const int4*>(p.x) + (((int64_t)n * p.H + iy) * p.W + ix) * p.cvec + cv);
-        if (DT == CVMK_I8) {
-          m.x = (int)__vmaxs4((unsigned)m.x, (unsigned)v.x); m.y = (int)__vmaxs4((unsigned)m.y, (unsigned)v.y);
-          m.z = (int)__vmaxs4((unsigned)m.z, (unsigned)v.z); m.w = (int)__vmaxs4((unsigned)m.w, (unsigned)v.w);
-        } else {
+    if (DT == CVMK_I8) {
+      uint32_t me[4], mo[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { me[q] = 0x80008000u; mo[q] = 0x80008000u; }
+      for (int fy = 0; fy < p.KH; ++fy) {
+        const int iy = oy * p.sh + fy - p.ph;
+        const bool row_ok = iy >= 0 && iy < p.H;
+        const int iyc = min(max(iy, 0), p.H - 1);
+        const int4* row = reinterpret_cast<const int4*>(p.x) + ((int64_t)n * p.H + iyc) * p.W * p.cvec + cv;
+#pragma unroll 3
+        for (int fx = 0; fx < p.KW; ++fx) {
+          const int ix = ox * p.sw + fx - p.pw;
+          const bool ok = row_ok && ix >= 0 && ix < p.W;
+          int4 v = __ldg(row + (int64_t)min(max(ix, 0), p.W - 1) * p.cvec);
+          if (!ok) v = make_int4(0x80808080, 0x80808080, 0x80808080, 0x80808080);
+          const uint32_t w[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            me[q] = __vmaxs2(me[q], (w[q] << 8) & 0xFF00FF00u);
+            mo[q] = __vmaxs2(mo[q], w[q] & 0xFF00FF00u);
+          }
+        }
+      }
+      uint32_t r[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) r[q] = ((me[q] >> 8) & 0x00FF00FFu) | (mo[q] & 0xFF00FF00u);
+      m = make_int4((int)r[0], (int)r[1], (int)r[2], (int)r[3]);
+    } else {
+      m = make_int4(INT32_MIN, INT32_MIN, INT32_MIN, INT32_MIN);
+      for (int fy = 0; fy < p.KH; ++fy) {
+        const int iy = oy * p.sh + fy - p.ph;
+        const bool row_ok = iy >= 0 && iy < p.H;
+        const int iyc = min(max(iy, 0), p.H - 1);
+        const int4* row = reinterpret_cast<const int4*>(p.x) + ((int64_t)n * p.H + iyc) * p.W * p.cvec + cv;
+#pragma unroll 3
+        for (int fx = 0; fx < p.KW; ++fx) {
+          const int ix = ox * p.sw + fx - p.pw;
+          const bool ok = row_ok && ix >= 0 && ix < p.W;
+          int4 v = __ldg(row + (int64_t)min(max(ix, 0), p.W - 1) * p.cvec);
+          if (!ok) v = make_int4(INT32_MIN, INT32_MIN, INT32_MIN, INT32_MIN);
           m.x = max(m.x, v.x); m.y = max(m.y, v.y); m.z = max(m.z, v.z); m.w = max(m.w, v.w);
         }
       }
