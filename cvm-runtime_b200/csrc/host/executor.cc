@@ -153,6 +153,18 @@ struct Lowering {
   // Same logical tensor copied between two buffers that may differ in layout and dtype.
   void emit_convert(const DevBuf& src, const DevBuf& dst, const std::string& label,
                     const cvmk_epilogue* ep = nullptr) {
+    if (src.nhwc == dst.nhwc && src.shape == dst.shape) {
+      // same element order on both sides: the vectorised contiguous kernel does it
+      cvmk_epilogue e;
+      memset(&e, 0, sizeof(e));
+      if (ep) e = *ep;
+      const DevBuf a = src, b = dst;
+      const int64_t cnt = shape_size(dst.shape);
+      add_step(label, [a, b, e, cnt](cudaStream_t s_) {
+        return cvmk_elemwise(a.ptr, a.dtype, b.ptr, b.dtype, cnt, &e, s_);
+      });
+      return;
+    }
     cvmk_strided_desc d;
     memset(&d, 0, sizeof(d));
     d.op = CVMK_OP_COPY;

@@ -58,6 +58,7 @@ struct ConvParams {
   int c, kh, kw;
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int block_k, block_n, stages;
+  int units;            // (filter tap, channel block) pairs loaded and multiplied per ring stage
   int a_mode;           // activations: 0 plain 2-D tiles (1x1, dense), 1 im2col-mode TMA, 2 spatial patches
   int patch_w, patch_h, patch_n;  // a_mode 2: an M tile is patch_w x patch_h output pixels of patch_n images
   int tiles_w, tiles_h;           // a_mode 2: patches per image row / column
@@ -207,9 +208,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int lane = threadIdx.x & 31;
   const int a_bytes = BLOCK_M * p.block_k;
   const int b_bytes = p.block_n * p.block_k;
-  const int stage_bytes = a_bytes + b_bytes;
-  const int k_per_tap = p.c / p.block_k;
-  const int num_kb = p.kh * p.kw * k_per_tap;
+  const int unit_bytes = a_bytes + b_bytes;          // one A tile and the B tile that goes with it
+  const int stage_bytes = p.units * unit_bytes;
+  const int num_units = p.kh * p.kw * (p.c / p.block_k);
+  const int num_kb = (num_units + p.units - 1) / p.units;  // ring stages consumed per tile
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const bool bias_in_smem = (p.bias != nullptr || p.fast_mode) && p.oc <= MAX_BIAS;
 
@@ -252,7 +254,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int which = warp == 0 ? 0 : 1;
       int stage = which % p.stages;
       uint32_t phase = which >= p.stages ? 1u : 0u;
-      int turn = which;  // K blocks to skip before the next one of this producer
+      int turn = which;  // 0: the next stage is this producer's
       bool live = true;
       TDECL;
       TSTART(tk);
@@ -273,57 +275,60 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           base_w = ox * p.stride_w - p.pad_w;
           base_h = oy * p.stride_h - p.pad_h;
         }
-        int kcol = 0;  // column of the weight matrix: tap * C + channel block
-        for (int fy = 0; live && fy < p.kh; ++fy) {
-          const int off_h = fy * p.dil_h;
-          for (int fx = 0; live && fx < p.kw; ++fx) {
-            const int off_w = fx * p.dil_w;
-            for (int cc = 0; cc < p.c; cc += p.block_k, kcol += p.block_k) {
-              if (turn != 0) { turn = 0; continue; }
-              turn = 1;
+        // Units (filter tap x channel block) in weight-matrix order; p.units of them share a stage.
+        int kcol = 0, fy = 0, fx = 0, cc = 0, slot = 0;
+        bool mine = false;
+        uint32_t sa = 0, bar = 0;
+        for (int unit = 0; unit < num_units; ++unit) {
+          if (slot == 0) {
+            mine = turn == 0;
+            turn ^= 1;
+            if (mine) {
               TSTART(tw);
               if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
               TADD(0, tw);
-              const uint32_t sa = smem_base + (uint32_t)(stage * stage_bytes);
-              const uint32_t sb = sa + (uint32_t)a_bytes;
-              const uint32_t bar = full0 + 8u * (uint32_t)stage;
-#ifdef CVMK_CONV_TIMING
-              const uint32_t tx_bytes = (p.dbg & 1) ? (uint32_t)a_bytes : (uint32_t)stage_bytes;
-#else
-              const uint32_t tx_bytes = (uint32_t)stage_bytes;
-#endif
+              sa = smem_base + (uint32_t)(stage * stage_bytes);
+              bar = full0 + 8u * (uint32_t)stage;
+              const int in_stage = min(p.units, num_units - unit);
               asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                           "r"(tx_bytes) : "memory");
-              TADD(13, tw);
-              if (p.a_mode == 2)  // the patch of this tile, shifted by the filter tap; zero fill outside the image
-                asm volatile(
-                    "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-                    " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)),
-                    "r"(bar), "r"(cc), "r"(to.cw + off_w - p.pad_w), "r"(to.ch + off_h - p.pad_h), "r"(to.cn)
-                    : "memory");
-              else if (p.a_mode == 1)
-                asm volatile(
-                    "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
-                    " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(sa),
-                    "l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(bar), "r"(cc), "r"(base_w), "r"(base_h), "r"(img),
-                    "h"((uint16_t)off_w), "h"((uint16_t)off_h)
-                    : "memory");
-              else
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-                    " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(bar),
-                    "r"(cc), "r"(m0)
-                    : "memory");
-              TADD(14, tw);
-#ifdef CVMK_CONV_TIMING
-              if (!(p.dbg & 1))
-#endif
+                           "r"((uint32_t)(in_stage * unit_bytes)) : "memory");
+            }
+          }
+          if (mine) {
+            const int off_w = fx * p.dil_w, off_h = fy * p.dil_h;
+            if (p.a_mode == 2)  // the patch of this tile, shifted by the filter tap; zero fill outside the image
+              asm volatile(
+                  "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                  " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)),
+                  "r"(bar), "r"(cc), "r"(to.cw + off_w - p.pad_w), "r"(to.ch + off_h - p.pad_h), "r"(to.cn)
+                  : "memory");
+            else if (p.a_mode == 1)
+              asm volatile(
+                  "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+                  " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(sa),
+                  "l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(bar), "r"(cc), "r"(base_w), "r"(base_h), "r"(img),
+                  "h"((uint16_t)off_w), "h"((uint16_t)off_h)
+                  : "memory");
+            else
               asm volatile(
                   "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-                  " [%0], [%1, {%3, %4}], [%2];" ::"r"(sb), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(bar),
-                  "r"(kcol), "r"(to.n0)
+                  " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(bar),
+                  "r"(cc), "r"(m0)
                   : "memory");
-              TADD(15, tw);
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa + (uint32_t)a_bytes), "l"(reinterpret_cast<uint64_t>(&tmap_b)),
+                "r"(bar), "r"(kcol), "r"(to.n0)
+                : "memory");
+            sa += (uint32_t)unit_bytes;
+          }
+          // next unit
+          kcol += p.block_k;
+          cc += p.block_k;
+          if (cc >= p.c) { cc = 0; if (++fx == p.kw) { fx = 0; ++fy; } }
+          if (++slot == p.units || unit + 1 == num_units) {
+            slot = 0;
+            if (mine) {
               stage += 2;
               if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
             }
@@ -354,22 +359,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         TADD(1, tw);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.block_n);
+        int unit = 0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&bar_full[stage], phase, &abort_flag, 3)) { live = false; break; }
           TADD(2, tw);
           tc_fence_after();
           // descriptors of this stage: the start-address field counts 16-byte units
-          const uint64_t da = desc_a0 + (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
-          const uint64_t db = da + (uint64_t)((uint32_t)a_bytes >> 4);
-#ifdef CVMK_CONV_TIMING
-          if (p.dbg & 2) {  // timing experiment (wrong results): break the accumulator dependence
-            for (int j = 0; j < nk; ++j)
-              mma_i8(d_tmem + (uint32_t)(((kb * nk + j) & 3) * 64), da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
-          } else
-#endif
-          {
-          mma_i8(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
-          for (int j = 1; j < nk; ++j) mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
+          uint64_t da = desc_a0 + (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
+          const int in_stage = min(p.units, num_units - unit);
+          for (int u = 0; u < in_stage; ++u, ++unit) {
+            const uint64_t db = da + (uint64_t)((uint32_t)a_bytes >> 4);
+            mma_i8(d_tmem, da, db, idesc, unit > 0 ? 1u : 0u);
+            for (int j = 1; j < nk; ++j) mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
+            da += (uint64_t)((uint32_t)unit_bytes >> 4);
           }
           mma_commit(&bar_empty[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
@@ -750,7 +752,19 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   }
   plan->block_k = bk;
   const int io_bytes = plan->tma_out ? 2 * plan->io_bufs * group_bytes : 0;
-  const int stage_bytes = (BLOCK_M + bn) * bk;
+  // Every hand-over of a ring stage (TMA completion -> MMA thread -> commit -> producer) costs a
+  // fixed latency of several hundred cycles whatever the stage holds, so small (tap, channel block)
+  // units are grouped: up to four per stage, about 48 KB, while the ring stays three deep.
+  const int unit_bytes = (BLOCK_M + bn) * bk;
+  const int num_units = (int)(k_all / bk);
+  int units = 48 * 1024 / unit_bytes;
+  if (units > 4) units = 4;
+  if (units > num_units) units = num_units;
+  if (const char* e = getenv("CVM_B200_UNITS")) units = atoi(e);
+  while (units > 1 && (budget - io_bytes) / (units * unit_bytes) < 3) --units;
+  if (units < 1) units = 1;
+  plan->reserved[3] = units;
+  const int stage_bytes = units * unit_bytes;
   int stages = (budget - io_bytes) / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) { set_error("conv2d_tc_prepare: tile does not fit shared memory"); return CVMK_ERR_UNSUPPORTED; }
@@ -826,6 +840,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.dil_h = d.dil_h; p.dil_w = d.dil_w;
   p.block_k = plan->block_k; p.block_n = plan->block_n;
   p.stages = plan->stages; p.a_mode = plan->a_im2col;
+  p.units = plan->reserved[3] > 0 ? plan->reserved[3] : 1;
   p.num_m_tiles = (p.m_total + BLOCK_M - 1) / BLOCK_M;
   if (p.a_mode == 2) {
     p.patch_w = plan->reserved[0]; p.patch_h = plan->reserved[1]; p.patch_n = plan->reserved[2];
