@@ -713,6 +713,10 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   memset(plan, 0, sizeof(*plan));
   plan->d = *d;
   int bk = pick_block_k(d->C);
+  if (const char* e = getenv("CVM_B200_BK")) {  // experiments: a smaller K block (must divide C)
+    const int v = atoi(e);
+    if ((v == 32 || v == 64 || v == 128) && d->C % v == 0 && v <= bk) bk = v;
+  }
   const int bn = pick_block_n(d->OC);
   plan->block_n = bn;
   int patch_w = 0, patch_h = 0, patch_n = 0;
