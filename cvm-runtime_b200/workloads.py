@@ -394,6 +394,65 @@ def ssd_backbone(batch=1, seed=0, size=512, input_seed=7, classes=21):
     return js, pb, image_input(batch, size, input_seed)
 
 
+def ssd_full(batch=1, seed=0, size=128, input_seed=7, classes=8, score_threshold=20, iou_threshold=45,
+             top_k=100):
+    """Image to boxes in one graph (the C5 backbone and heads joined to the C5 tail): per feature map
+    the class and box heads are transposed to channels-last, reshaped to (batch, anchors, .) and
+    concatenated over the maps; score = max over the classes, a small class id from comparisons of
+    class logits (there is no argmax operator), boxes = clip(anchor + (delta >> 2)); the rows
+    [id, score, x1, y1, x2, y2] go through get_valid_counts and non_max_suppression."""
+    g = GraphBuilder(seed)
+    x = g.var("data", (batch, 3, size, size), 8)
+    y = g.conv(x, 32, 3, 2, 1)
+    feats = []
+    cfg = [(64, 1), (128, 2), (128, 1), (256, 2), (256, 1), (512, 2)] + [(512, 1)] * 5 + [(1024, 2), (1024, 1)]
+    for idx, (oc, s) in enumerate(cfg):
+        c = g.shape_of(y)[1]
+        y = g.conv(y, c, 3, s, 1, groups=c)
+        y = g.conv(y, oc, 1, 1, 0)
+        if idx in (4, 10, 12):
+            feats.append(y)
+    for oc in (512, 512, 256, 256):
+        y = g.conv(y, oc // 2, 1, 1, 0)
+        y = g.conv(y, oc, 3, 2, 1)
+        feats.append(y)
+    cls_parts, box_parts = [], []
+    for f, a in zip(feats, (4, 6, 6, 6, 6, 4, 4)):
+        for ch, last, parts in ((a * classes, classes, cls_parts), (a * 4, 4, box_parts)):
+            hd = g.conv(f, ch, 3, 1, 1, relu=False)
+            n_, c_, h_, w_ = g.shape_of(hd)
+            t = g.op("transpose", [hd], (n_, h_, w_, c_), {"axes": (0, 2, 3, 1)})
+            parts.append(g.op("reshape", [t], (n_, h_ * w_ * a, last), {"shape": (0, -1, last)}))
+    total = sum(g.shape_of(o)[1] for o in cls_parts)
+    cls = g.op("concatenate", cls_parts, (batch, total, classes), {"axis": 1})
+    box = g.op("concatenate", box_parts, (batch, total, 4), {"axis": 1})
+    score = g.op("max", [cls], (batch, total, 1), {"axis": (2,), "keepdims": True, "exclude": False})
+
+    def column(k):
+        return g.op("strided_slice", [cls], (batch, total, 1), {"begin": (0, 0, k), "end": (batch, total, k + 1)})
+    c0, c1, c2 = column(0), column(1), column(2)
+    gt1 = g.op("broadcast_greater", [c1, c0], (batch, total, 1))
+    gt2 = g.op("broadcast_greater", [c2, c0], (batch, total, 1))
+    cid = g.op("elemwise_add", [gt1, gt2], (batch, total, 1))
+    rng = np.random.RandomState(seed + 1)
+    ax = rng.randint(0, size - 40, size=(1, total, 1))
+    ay = rng.randint(0, size - 40, size=(1, total, 1))
+    aw = rng.randint(8, 40, size=(1, total, 1))
+    ah = rng.randint(8, 40, size=(1, total, 1))
+    anchors = np.concatenate([ax, ay, ax + aw, ay + ah], axis=2).astype(np.int32)
+    anc = g.var("anchors", anchors.shape, 10, anchors)
+    delta = g.op("cvm_right_shift", [box], (batch, total, 4), {"precision": 6, "shift_bit": 2})
+    moved = g.op("broadcast_add", [delta, anc], (batch, total, 4))
+    boxes = g.op("clip", [moved], (batch, total, 4), {"a_min": 0, "a_max": size})
+    rows = g.op("concatenate", [cid, score, boxes], (batch, total, 6), {"axis": 2})
+    vc, kept = g.op("get_valid_counts", [rows], [(batch,), (batch, total, 6)], {"score_threshold": score_threshold})
+    out = g.op("non_max_suppression", [kept, vc], (batch, total, 6), {
+        "iou_threshold": iou_threshold, "top_k": top_k, "max_output_size": -1, "force_suppress": False,
+        "id_index": 0, "score_index": 1, "coord_start": 2, "return_indices": False, "invalid_to_bottom": True})
+    js, pb = g.finish(out)
+    return js, pb, image_input(batch, size, input_seed)
+
+
 def conv_ops_per_image(graph_json):
     """2 * MACs of every conv2d (groups = 1 and grouped) and dense node, for one image."""
     gj = json.loads(graph_json)

@@ -61,6 +61,7 @@ def model_cases():
         "mobilenet_s64": lambda: wl.mobilenet_v1(batch=2, size=64),
         "vgg19_s32": lambda: wl.vgg19(batch=2, size=32, fc=64),
         "ssd_backbone_s128": lambda: wl.ssd_backbone(batch=1, size=128),
+        "ssd_full_s128": lambda: wl.ssd_full(batch=2, size=128),
         "ssd_tail_b2": lambda: wl.ssd_tail(batch=2, anchors=600, top_k=50),
         "ssd_tail_mos": lambda: wl.ssd_tail(batch=2, anchors=500, top_k=-1, max_output_size=20),
         "ssd_tail_force": lambda: wl.ssd_tail(batch=1, anchors=700, top_k=200, force_suppress=True, score_threshold=100),
