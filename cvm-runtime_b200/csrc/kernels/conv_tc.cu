@@ -231,6 +231,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
+  // Programmatic dependent launch: the next kernel of the stream may start its own prologue on SMs
+  // this grid has left; everything up to here touched no global memory, and nothing below runs
+  // before the previous kernel of the stream has completed and flushed its writes.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (bias_in_smem) {
     const int padded = min(MAX_BIAS, (p.oc + 31) & ~31);
     for (int i = threadIdx.x; i < padded; i += NUM_THREADS)
@@ -240,7 +246,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bias_s[i] = p.fast_mode ? (int32_t)((uint32_t)(b + p.f_add) * (uint32_t)p.f_mul) : b;
     }
   }
-  if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -941,8 +946,19 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   memcpy(&tb, plan->tmap_b, sizeof(tb));
   memcpy(&ty, plan->tmap_y, sizeof(ty));
   memcpy(&tr, plan->tmap_r, sizeof(tr));
-  conv_tc_kernel<<<plan->grid, NUM_THREADS, plan->smem_bytes, (cudaStream_t)stream>>>(ta, tb, ty, tr, p);
-  return check_cuda(cudaGetLastError(), "conv_tc_kernel launch");
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)plan->grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = (size_t)plan->smem_bytes;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  static const bool pdl = getenv("CVM_B200_NO_PDL") == nullptr;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return check_cuda(cudaLaunchKernelEx(&cfg, conv_tc_kernel, ta, tb, ty, tr, p), "conv_tc_kernel launch");
 }
 
 #ifdef CVMK_CONV_TIMING
