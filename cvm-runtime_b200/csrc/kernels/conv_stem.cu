@@ -146,18 +146,34 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
         const int tasks = p.srows * p.C * vpr;
         const uint32_t lo = (uint32_t)(uint8_t)(int8_t)(-p.clamp) * 0x01010101u;
         const uint32_t hi = (uint32_t)(uint8_t)(int8_t)p.clamp * 0x01010101u;
-        for (int i = t; i < tasks; i += BUILDERS) {
-          const int vx = i % vpr;
-          const int c = (i / vpr) % p.C;
-          const int r = i / (vpr * p.C);
-          const int iy = iy0 + r;
-          if (iy < 0 || iy >= p.H) continue;
-          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.x + (((int64_t)n * p.C + c) * p.H + iy) * p.W) + vx);
-          const uint32_t w4[4] = {__vmins4(__vmaxs4(raw.x, lo), hi), __vmins4(__vmaxs4(raw.y, lo), hi),
-                                  __vmins4(__vmaxs4(raw.z, lo), hi), __vmins4(__vmaxs4(raw.w, lo), hi)};
-          uint8_t* dst = srow + (size_t)r * wp_cols + (p.pw + vx * 16) * p.C + c;
+        // Loads first (clamped addresses, so that they are independent and in flight together),
+        // conversion and the byte scatter afterwards; rows outside the image keep their zeros.
+        constexpr int MAXT = 6;
+        for (int i0 = t; i0 < tasks; i0 += BUILDERS * MAXT) {
+          uint4 raw[MAXT];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) dst[j * p.C] = (uint8_t)(w4[j >> 2] >> ((j & 3) * 8));
+          for (int k = 0; k < MAXT; ++k) {
+            const int i = min(i0 + k * BUILDERS, tasks - 1);
+            const int vx = i % vpr;
+            const int c = (i / vpr) % p.C;
+            const int iy = min(max(iy0 + i / (vpr * p.C), 0), p.H - 1);
+            raw[k] = __ldg(reinterpret_cast<const uint4*>(p.x + (((int64_t)n * p.C + c) * p.H + iy) * p.W) + vx);
+          }
+#pragma unroll
+          for (int k = 0; k < MAXT; ++k) {
+            const int i = i0 + k * BUILDERS;
+            if (i >= tasks) break;
+            const int vx = i % vpr;
+            const int c = (i / vpr) % p.C;
+            const int r = i / (vpr * p.C);
+            const int iy = iy0 + r;
+            if (iy < 0 || iy >= p.H) continue;
+            const uint32_t w4[4] = {__vmins4(__vmaxs4(raw[k].x, lo), hi), __vmins4(__vmaxs4(raw[k].y, lo), hi),
+                                    __vmins4(__vmaxs4(raw[k].z, lo), hi), __vmins4(__vmaxs4(raw[k].w, lo), hi)};
+            uint8_t* dst = srow + (size_t)r * wp_cols + (p.pw + vx * 16) * p.C + c;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) dst[j * p.C] = (uint8_t)(w4[j >> 2] >> ((j & 3) * 8));
+          }
         }
       } else {
         const int total = p.srows * p.C * p.W;
