@@ -436,12 +436,34 @@ struct Lowering {
         int8_t* wsdev = (int8_t*)ex.dalloc(ws.size());
         CUDA_OK(cudaMemcpy(wsdev, ws.data(), ws.size(), cudaMemcpyHostToDevice));
         sd.w = wsdev;
-        void* mem = nullptr;
-        CHECK(posix_memalign(&mem, 64, sizeof(cvmk_stem_conv_plan)) == 0);
-        ex.stem_plans_.emplace_back((cvmk_stem_conv_plan*)mem, plan_deleter);
-        cvmk_stem_conv_plan* plan = ex.stem_plans_.back().get();
-        KERNEL_OK(cvmk_conv2d_stem_prepare(&sd, plan));
-        add_step(label + "[stem]", [plan](cudaStream_t s) { return cvmk_conv2d_stem_launch(plan, s); });
+        // The batch is cut into chunks with a plan each, so that an inference can run the stem on
+        // the first images while the later ones are still being uploaded.
+        const int chunks = (N % 4 == 0 && N >= 8 && uses[ex_] == 1 && !is_head[ex_] &&
+                            !getenv("CVM_B200_NO_UPLOAD_OVERLAP")) ? 4 : 1;
+        const int per = N / chunks;
+        std::vector<cvmk_stem_conv_plan*> plans;
+        for (int c = 0; c < chunks; ++c) {
+          cvmk_stem_conv_desc cd = sd;
+          cd.N = per;
+          cd.x = sd.x + (size_t)c * per * C * H * W;
+          cd.y = (int8_t*)sd.y + (size_t)c * per * OH * OW * OC;
+          void* mem = nullptr;
+          CHECK(posix_memalign(&mem, 64, sizeof(cvmk_stem_conv_plan)) == 0);
+          ex.stem_plans_.emplace_back((cvmk_stem_conv_plan*)mem, plan_deleter);
+          KERNEL_OK(cvmk_conv2d_stem_prepare(&cd, ex.stem_plans_.back().get()));
+          plans.push_back(ex.stem_plans_.back().get());
+        }
+        if (chunks > 1) {
+          ex.stem_chunks_ = plans;
+          ex.stem_chunk_bytes_ = (size_t)per * C * H * W;
+        }
+        add_step(label + "[stem]", [plans](cudaStream_t s) {
+          for (auto* pl : plans) {
+            const int rc = cvmk_conv2d_stem_launch(pl, s);
+            if (rc != CVMK_OK) return rc;
+          }
+          return (int)CVMK_OK;
+        });
         return;
       }
     }
@@ -1040,6 +1062,13 @@ struct Lowering {
       for (const auto& pr : order)
         for (auto& s : per_root[pr.second]) ex.steps_.push_back(std::move(s));
     }
+    // upload / stem overlap only when the stem is the very first step of the inference
+    {
+      const std::string tag = "[stem]";
+      const bool first = !ex.steps_.empty() && ex.steps_[0].label.size() >= tag.size() &&
+                         ex.steps_[0].label.compare(ex.steps_[0].label.size() - tag.size(), tag.size(), tag) == 0;
+      if (!first) ex.stem_chunks_.clear();
+    }
     // heads: row-major staging + pinned host mirrors
     for (const auto& e : g.outputs) {
       const uint32_t eid = g.entry_id(e);
@@ -1075,9 +1104,14 @@ Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
   Enqueue(stream_);
   CUDA_OK(cudaStreamSynchronize(stream_));
   if (use_graph_) {
+    if (!stem_chunks_.empty()) {
+      CUDA_OK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+      chunk_events_.resize(stem_chunks_.size());
+      for (auto& e : chunk_events_) CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
     cudaGraph_t graph = nullptr;
     CUDA_OK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
-    Enqueue(stream_);
+    Enqueue(stream_, stem_chunks_.empty() ? 0 : 1);  // the chunked stem is launched outside the graph
     CUDA_OK(cudaStreamEndCapture(stream_, &graph));
     CUDA_OK(cudaGraphInstantiate(&graph_exec_, graph, 0));
     CUDA_OK(cudaGraphDestroy(graph));
@@ -1089,6 +1123,8 @@ Executor::~Executor() {
   if (stream_) cudaStreamSynchronize(stream_);
   if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
   if (kernels_exec_) cudaGraphExecDestroy(kernels_exec_);
+  for (auto e : chunk_events_) cudaEventDestroy(e);
+  if (copy_stream_) cudaStreamDestroy(copy_stream_);
   for (void* p : allocs_) cudaFree(p);
   for (void* p : pinned_) cudaFreeHost(p);
   if (stream_) cudaStreamDestroy(stream_);
@@ -1097,7 +1133,9 @@ Executor::~Executor() {
 // Queues the upload of one input.  Page-locked (or device) memory is read where it lies; pageable
 // memory goes through the pinned staging buffer in chunks, so that the host copy of one chunk
 // overlaps the transfer of the previous one.
-void Executor::Upload(const void* input, cudaStream_t s) {
+void Executor::Upload(const void* input, cudaStream_t s) { UploadRange(input, 0, in_bytes_, s); }
+
+void Executor::UploadRange(const void* input, size_t begin, size_t bytes, cudaStream_t s) {
   cudaPointerAttributes at;
   bool direct = false;
   if (cudaPointerGetAttributes(&at, input) == cudaSuccess)
@@ -1105,19 +1143,20 @@ void Executor::Upload(const void* input, cudaStream_t s) {
   else
     cudaGetLastError();
   if (direct) {
-    CUDA_OK(cudaMemcpyAsync(in_dev_, input, in_bytes_, cudaMemcpyDefault, s));
+    CUDA_OK(cudaMemcpyAsync((char*)in_dev_ + begin, (const char*)input + begin, bytes, cudaMemcpyDefault, s));
     return;
   }
   const size_t chunk = (size_t)4 << 20;
-  for (size_t off = 0; off < in_bytes_; off += chunk) {
-    const size_t n = std::min(chunk, in_bytes_ - off);
+  for (size_t off = begin; off < begin + bytes; off += chunk) {
+    const size_t n = std::min(chunk, begin + bytes - off);
     memcpy((char*)in_host_ + off, (const char*)input + off, n);
     CUDA_OK(cudaMemcpyAsync((char*)in_dev_ + off, (char*)in_host_ + off, n, cudaMemcpyHostToDevice, s));
   }
 }
 
-void Executor::Enqueue(cudaStream_t s) {
-  for (auto& st : steps_) {
+void Executor::Enqueue(cudaStream_t s, size_t first) {
+  for (size_t k = first; k < steps_.size(); ++k) {
+    auto& st = steps_[k];
     int rc = st.launch(s);
     CHECK(rc == CVMK_OK) << "step " << st.label << " failed (" << rc << "): " << cvmk_last_error();
   }
@@ -1128,9 +1167,20 @@ void Executor::Enqueue(cudaStream_t s) {
 void Executor::Run(const void* input, size_t input_bytes) {
   CHECK(input_bytes == in_bytes_) << "input size " << input_bytes << " vs. " << in_bytes_;
   CUDA_OK(cudaSetDevice(device_));
-  Upload(input, stream_);
-  if (graph_exec_) CUDA_OK(cudaGraphLaunch(graph_exec_, stream_));
-  else Enqueue(stream_);
+  if (graph_exec_ && !stem_chunks_.empty()) {
+    // chunk c of the batch is uploaded on the copy stream while the stem runs on chunk c - 1
+    for (size_t c = 0; c < stem_chunks_.size(); ++c) {
+      UploadRange(input, c * stem_chunk_bytes_, stem_chunk_bytes_, copy_stream_);
+      CUDA_OK(cudaEventRecord(chunk_events_[c], copy_stream_));
+      CUDA_OK(cudaStreamWaitEvent(stream_, chunk_events_[c], 0));
+      KERNEL_OK(cvmk_conv2d_stem_launch(stem_chunks_[c], stream_));
+    }
+    CUDA_OK(cudaGraphLaunch(graph_exec_, stream_));
+  } else {
+    Upload(input, stream_);
+    if (graph_exec_) CUDA_OK(cudaGraphLaunch(graph_exec_, stream_));
+    else Enqueue(stream_);
+  }
   CUDA_OK(cudaStreamSynchronize(stream_));
   if (*status_host_ != 0) {
     const int code = *status_host_;

@@ -82,10 +82,16 @@ class Executor {
   cudaGraphExec_t graph_exec_ = nullptr;
   cudaGraphExec_t kernels_exec_ = nullptr;
   bool use_graph_ = true;
+  // upload / stem overlap: per-chunk stem plans, the copy stream and one event per chunk
+  std::vector<cvmk_stem_conv_plan*> stem_chunks_;
+  size_t stem_chunk_bytes_ = 0;
+  cudaStream_t copy_stream_ = nullptr;
+  std::vector<cudaEvent_t> chunk_events_;
 
   void* dalloc(size_t bytes);
   void Upload(const void* input, cudaStream_t s);
-  void Enqueue(cudaStream_t s);
+  void UploadRange(const void* input, size_t begin, size_t bytes, cudaStream_t s);
+  void Enqueue(cudaStream_t s, size_t first = 0);
   friend struct Lowering;
 };
 
