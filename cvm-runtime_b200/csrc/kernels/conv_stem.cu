@@ -168,8 +168,19 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
             const int r = i / (vpr * p.C);
             const int iy = iy0 + r;
             if (iy < 0 || iy >= p.H) continue;
-            const uint32_t w4[4] = {__vmins4(__vmaxs4(raw[k].x, lo), hi), __vmins4(__vmaxs4(raw[k].y, lo), hi),
-                                    __vmins4(__vmaxs4(raw[k].z, lo), hi), __vmins4(__vmaxs4(raw[k].w, lo), hi)};
+            uint32_t w4[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+            if (p.clamp == 127) {
+              // only -128 moves: add 1 to every byte equal to 0x80 (exact per-byte zero test of x ^ 0x80)
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t z = w4[q] ^ 0x80808080u;
+                const uint32_t m = ~(((z & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | z) & 0x80808080u;
+                w4[q] += m >> 7;
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) w4[q] = __vmins4(__vmaxs4(w4[q], lo), hi);
+            }
             uint8_t* dst = srow + (size_t)r * wp_cols + (p.pw + vx * 16) * p.C + c;
 #pragma unroll
             for (int j = 0; j < 16; ++j) dst[j * p.C] = (uint8_t)(w4[j >> 2] >> ((j & 3) * 8));
