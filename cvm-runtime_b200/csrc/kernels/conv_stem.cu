@@ -42,6 +42,7 @@ struct StemConvParams {
   int rows_per_block, blocks_per_image, num_blocks;
   int segs, seg_w;
   int srows, srow_bytes;
+  int left;             // byte offset of image column 0 in a staged row (a multiple of 16)
   int tmem_cols;
   int off_a, off_in, off_out, off_bias;  // byte offsets of the shared-memory regions after the weights
   int* status;
@@ -78,6 +79,74 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
 }
 __device__ __forceinline__ void tma_store_wait_read1() {
   asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
+
+// Input rows of a block -> shared memory, channel-interleaved.  One task = 16 pixels of one row:
+// C 16-byte loads (one per channel plane), the clamp, a byte interleave in registers and C 16-byte
+// stores.  The loads of all tasks of a thread are issued before anything depends on them (clamped
+// row index; rows outside the image are written as zeros).
+template <int C>
+__device__ __forceinline__ void stage_rows(const StemConvParams& p, uint8_t* srow, int n, int iy0, int t) {
+  constexpr int MAXT = 2;
+  const int vpr = p.W / 16;
+  const int tasks = p.srows * vpr;
+  const uint32_t lo = (uint32_t)(uint8_t)(int8_t)(-p.clamp) * 0x01010101u;
+  const uint32_t hi = (uint32_t)(uint8_t)(int8_t)p.clamp * 0x01010101u;
+  for (int i0 = t; i0 < tasks; i0 += BUILDERS * MAXT) {
+    uint4 raw[MAXT][C];
+#pragma unroll
+    for (int k = 0; k < MAXT; ++k) {
+      const int i = min(i0 + k * BUILDERS, tasks - 1);
+      const int vx = i % vpr;
+      const int iy = min(max(iy0 + i / vpr, 0), p.H - 1);
+#pragma unroll
+      for (int c = 0; c < C; ++c)
+        raw[k][c] = __ldg(reinterpret_cast<const uint4*>(p.x + (((int64_t)n * C + c) * p.H + iy) * p.W) + vx);
+    }
+#pragma unroll
+    for (int k = 0; k < MAXT; ++k) {
+      const int i = i0 + k * BUILDERS;
+      if (i >= tasks) break;
+      const int vx = i % vpr;
+      const int r = i / vpr;
+      const bool inside = iy0 + r >= 0 && iy0 + r < p.H;
+      uint32_t w[C][4];
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        w[c][0] = raw[k][c].x; w[c][1] = raw[k][c].y; w[c][2] = raw[k][c].z; w[c][3] = raw[k][c].w;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t x = inside ? w[c][q] : 0u;
+          if (p.clamp == 127) {  // only -128 moves: add 1 to every byte equal to 0x80 (exact per-byte test)
+            const uint32_t z = x ^ 0x80808080u;
+            const uint32_t m = ~(((z & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | z) & 0x80808080u;
+            x += m >> 7;
+          } else {
+            x = __vmins4(__vmaxs4(x, lo), hi);
+          }
+          w[c][q] = x;
+        }
+      }
+      // output byte b of the 16 * C is channel b % C of pixel b / C
+      uint32_t out[4 * C];
+#pragma unroll
+      for (int ow = 0; ow < 4 * C; ++ow) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int b = 4 * ow + j;
+          const int pix = b / C, c = b % C;
+          // byte (pix & 3) of the source word goes to byte j of acc
+          const uint32_t sel = (0x3210u & ~(0xFu << (4 * j))) | ((uint32_t)(4 + (pix & 3)) << (4 * j));
+          acc = __byte_perm(acc, w[c][pix >> 2], sel);
+        }
+        out[ow] = acc;
+      }
+      uint4* dst = reinterpret_cast<uint4*>(srow + (size_t)r * p.srow_bytes + p.left + vx * 16 * C);
+#pragma unroll
+      for (int q = 0; q < C; ++q) dst[q] = make_uint4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(STEM_THREADS, 2)
@@ -142,49 +211,11 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
       for (int i = t; i < p.srows * wp_cols / 4; i += BUILDERS) reinterpret_cast<uint32_t*>(srow)[i] = 0;
       bar_sync(1, BUILDERS);
       if (p.W % 16 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
-        const int vpr = p.W / 16;
-        const int tasks = p.srows * p.C * vpr;
-        const uint32_t lo = (uint32_t)(uint8_t)(int8_t)(-p.clamp) * 0x01010101u;
-        const uint32_t hi = (uint32_t)(uint8_t)(int8_t)p.clamp * 0x01010101u;
-        // Loads first (clamped addresses, so that they are independent and in flight together),
-        // conversion and the byte scatter afterwards; rows outside the image keep their zeros.
-        constexpr int MAXT = 6;
-        for (int i0 = t; i0 < tasks; i0 += BUILDERS * MAXT) {
-          uint4 raw[MAXT];
-#pragma unroll
-          for (int k = 0; k < MAXT; ++k) {
-            const int i = min(i0 + k * BUILDERS, tasks - 1);
-            const int vx = i % vpr;
-            const int c = (i / vpr) % p.C;
-            const int iy = min(max(iy0 + i / (vpr * p.C), 0), p.H - 1);
-            raw[k] = __ldg(reinterpret_cast<const uint4*>(p.x + (((int64_t)n * p.C + c) * p.H + iy) * p.W) + vx);
-          }
-#pragma unroll
-          for (int k = 0; k < MAXT; ++k) {
-            const int i = i0 + k * BUILDERS;
-            if (i >= tasks) break;
-            const int vx = i % vpr;
-            const int c = (i / vpr) % p.C;
-            const int r = i / (vpr * p.C);
-            const int iy = iy0 + r;
-            if (iy < 0 || iy >= p.H) continue;
-            uint32_t w4[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
-            if (p.clamp == 127) {
-              // only -128 moves: add 1 to every byte equal to 0x80 (exact per-byte zero test of x ^ 0x80)
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t z = w4[q] ^ 0x80808080u;
-                const uint32_t m = ~(((z & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | z) & 0x80808080u;
-                w4[q] += m >> 7;
-              }
-            } else {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) w4[q] = __vmins4(__vmaxs4(w4[q], lo), hi);
-            }
-            uint8_t* dst = srow + (size_t)r * wp_cols + (p.pw + vx * 16) * p.C + c;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) dst[j * p.C] = (uint8_t)(w4[j >> 2] >> ((j & 3) * 8));
-          }
+        switch (p.C) {
+          case 1: stage_rows<1>(p, srow, n, iy0, t); break;
+          case 2: stage_rows<2>(p, srow, n, iy0, t); break;
+          case 3: stage_rows<3>(p, srow, n, iy0, t); break;
+          default: stage_rows<4>(p, srow, n, iy0, t); break;
         }
       } else {
         const int total = p.srows * p.C * p.W;
@@ -196,7 +227,7 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
           if (iy < 0 || iy >= p.H) continue;
           int v = __ldg(p.x + (((int64_t)n * p.C + c) * p.H + iy) * p.W + ix);
           v = max(min(v, p.clamp), -p.clamp);
-          srow[(size_t)r * wp_cols + (p.pw + ix) * p.C + c] = (uint8_t)(int8_t)v;
+          srow[(size_t)r * wp_cols + p.left + ix * p.C + c] = (uint8_t)(int8_t)v;
         }
       }
       bar_sync(1, BUILDERS);
@@ -208,7 +239,7 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
           if (t < p.seg_w && ox < p.OW) {
             uint8_t* arow = a_tiles + (size_t)buf * p.KH * A_BLOCK + t * SLOT;
             const uint32_t sw_key = (uint32_t)((t >> 2) & 1);
-            const uint32_t off = (uint32_t)(ox * p.sw * p.C);
+            const uint32_t off = (uint32_t)(p.left - p.pw * p.C + ox * p.sw * p.C);
             const uint32_t shift = (off & 3u) * 8u;
             const uint8_t* src0 = srow + (size_t)(rr * p.sh) * wp_cols + (off & ~3u);
             for (int ky = 0; ky < p.KH; ++ky) {
@@ -366,7 +397,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 struct StemLayout {
-  int rows_per_block, segs, seg_w, srows, srow_bytes, off_a, off_in, off_out, off_bias, smem_bytes;
+  int rows_per_block, segs, seg_w, srows, srow_bytes, left, off_a, off_in, off_out, off_bias, smem_bytes;
 };
 
 bool stem_layout(const cvmk_stem_conv_desc& d, StemLayout* L) {
@@ -376,8 +407,9 @@ bool stem_layout(const cvmk_stem_conv_desc& d, StemLayout* L) {
   if (L->rows_per_block > d.OH) L->rows_per_block = d.OH;
   L->srows = (L->rows_per_block - 1) * d.stride_h + d.KH;
   // a window may start at the last output pixel and is read as nine 32-bit words
-  const int reach = ((d.OW - 1) * d.stride_w) * d.C + 40;
-  int row = (d.W + 2 * d.pad_w) * d.C;
+  L->left = (d.pad_w * d.C + 15) / 16 * 16;  // image column 0 starts 16-byte aligned in a staged row
+  const int reach = L->left - d.pad_w * d.C + ((d.OW - 1) * d.stride_w) * d.C + 40;
+  int row = L->left + (d.W + d.pad_w) * d.C;
   if (row < reach) row = reach;
   L->srow_bytes = (row + 15) / 16 * 16;
   const int w_bytes = d.KH * d.OC * SLOT;
@@ -453,7 +485,7 @@ extern "C" int cvmk_conv2d_stem_launch(const cvmk_stem_conv_plan* plan, cvmk_str
   p.rows_per_block = L.rows_per_block;
   p.blocks_per_image = (d.OH + L.rows_per_block - 1) / L.rows_per_block;
   p.num_blocks = d.N * p.blocks_per_image;
-  p.segs = L.segs; p.seg_w = L.seg_w; p.srows = L.srows; p.srow_bytes = L.srow_bytes;
+  p.segs = L.segs; p.seg_w = L.seg_w; p.srows = L.srows; p.srow_bytes = L.srow_bytes; p.left = L.left;
   p.off_a = L.off_a; p.off_in = L.off_in; p.off_out = L.off_out; p.off_bias = L.off_bias;
   int cols = 2 * d.OC, pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
