@@ -27,7 +27,8 @@ namespace {
 
 using namespace tc;
 
-constexpr int STEM_THREADS = 288;
+constexpr int STEM_THREADS = 320;   // warps 0-3 build, 4 MMA, 5-8 epilogue, 9 output stores
+constexpr int STORE_WARP = 9;
 constexpr int BUILDERS = 128;
 constexpr int MMA_WARP = 4;
 constexpr int SLOT = 32;           // bytes of K per filter row
@@ -149,6 +150,48 @@ __device__ __forceinline__ void stage_rows(const StemConvParams& p, uint8_t* sro
   }
 }
 
+// Packed requantisation of one thread's row (see fast_requant): straight-line per 32 columns.
+template <int RELU1>
+__device__ __forceinline__ void stem_fast_row(const FastQ& fq, int mul, uint32_t tbase, int chunks, const int32_t* bias_s,
+                                              uint8_t* panel, uint32_t sw_key) {
+  for (int ci = 0; ci < chunks; ++ci) {
+    int32_t v[32];
+    tmem_ld32(tbase + (uint32_t)(ci * 32), v);
+    const int4* bp = reinterpret_cast<const int4*>(bias_s + ci * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int4 b4 = bp[j];
+      v[4 * j] = v[4 * j] * mul + b4.x;
+      v[4 * j + 1] = v[4 * j + 1] * mul + b4.y;
+      v[4 * j + 2] = v[4 * j + 2] * mul + b4.z;
+      v[4 * j + 3] = v[4 * j + 3] * mul + b4.w;
+    }
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    uint4 a, b;
+    fast_requant<RELU1, 0>(fq, v, z, z, &a, &b);
+    const uint32_t j0 = (uint32_t)(ci * 2);
+    *reinterpret_cast<uint4*>(panel + ((j0 ^ sw_key) << 4)) = a;
+    *reinterpret_cast<uint4*>(panel + (((j0 + 1) ^ sw_key) << 4)) = b;
+  }
+}
+
+#ifdef CVMK_STEM_TIMING
+// Development builds: cycles per role and phase, per CTA.  Slots: 0 builders stage, 1 builders wait
+// for a free A tile, 2 builders build, 3 MMA waits for the accumulator, 4 MMA waits for A, 5 MMA
+// issue, 6 epilogue waits for the accumulator, 7 epilogue waits for a panel, 8 epilogue compute,
+// 9 epilogue store hand-over, 10 whole builder loop, 11 tiles.
+__device__ long long g_stem_timing[296 * 16];
+#define STSTART(var) long long var = clock64()
+#define STADD(slot, var) do { const long long now__ = clock64(); stacc[slot] += now__ - var; var = now__; } while (0)
+#define STDECL long long stacc[16] = {0}
+#define STFLUSH(slot) do { if (blockIdx.x < 296) g_stem_timing[blockIdx.x * 16 + (slot)] = stacc[slot]; } while (0)
+#else
+#define STSTART(var) do {} while (0)
+#define STADD(slot, var) do {} while (0)
+#define STDECL do {} while (0)
+#define STFLUSH(slot) do {} while (0)
+#endif
+
 __global__ void __launch_bounds__(STEM_THREADS, 2)
 conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ StemConvParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -201,10 +244,13 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
     const int wp_cols = p.srow_bytes;
     uint32_t tile = 0;
     bool live = true;
+    STDECL;
+    STSTART(tall);
     for (int blk = blockIdx.x; blk < p.num_blocks; blk += gridDim.x) {
       const int n = blk / p.blocks_per_image;
       const int oy0 = (blk - n * p.blocks_per_image) * p.rows_per_block;
       const int iy0 = oy0 * p.sh - p.ph;
+      STSTART(tw);
       // everybody is done reading the previous block's rows; if a wait ran out for anyone, all
       // builders leave together (nobody may be left alone at a barrier)
       if (bar_any(1, BUILDERS, !live)) break;
@@ -231,10 +277,12 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
         }
       }
       bar_sync(1, BUILDERS);
+      STADD(0, tw);
       for (int rr = 0; live && rr < p.rows_per_block && oy0 + rr < p.OH; ++rr) {
         for (int sg = 0; sg < p.segs; ++sg, ++tile) {
           const int buf = (int)(tile & 1u);
           if (!mbar_wait(&a_empty[buf], ((tile >> 1) & 1u) ^ 1u, &abort_flag, 1)) { live = false; break; }
+          STADD(1, tw);
           const int ox = sg * p.seg_w + t;
           if (t < p.seg_w && ox < p.OW) {
             uint8_t* arow = a_tiles + (size_t)buf * p.KH * A_BLOCK + t * SLOT;
@@ -258,9 +306,14 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&a_full[buf]);
+          STADD(2, tw);
         }
       }
     }
+#ifdef CVMK_STEM_TIMING
+    STADD(10, tall);
+    if (t == 0) { stacc[11] = tile; STFLUSH(0); STFLUSH(1); STFLUSH(2); STFLUSH(10); STFLUSH(11); }
+#endif
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
@@ -271,6 +324,7 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
       const uint64_t a_step = (uint64_t)((uint32_t)A_BLOCK >> 4);
       uint32_t tile = 0;
       bool live = true;
+      STDECL;
       for (int blk = blockIdx.x; live && blk < p.num_blocks; blk += gridDim.x) {
         const int n = blk / p.blocks_per_image;
         const int oy0 = (blk - n * p.blocks_per_image) * p.rows_per_block;
@@ -278,8 +332,11 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
           for (int sg = 0; sg < p.segs; ++sg, ++tile) {
             const int buf = (int)(tile & 1u);
             const uint32_t par = (tile >> 1) & 1u;
+            STSTART(tw);
             if (!mbar_wait(&acc_empty[buf], par ^ 1u, &abort_flag, 2)) { live = false; break; }
+            STADD(3, tw);
             if (!mbar_wait(&a_full[buf], par, &abort_flag, 3)) { live = false; break; }
+            STADD(4, tw);
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.OC);
             const uint64_t da = desc_a0 + (uint64_t)buf * (uint64_t)p.KH * a_step;
@@ -287,15 +344,18 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
               mma_i8(d_tmem, da + (uint64_t)ky * a_step, desc_b0 + (uint64_t)ky * b_step, idesc, ky > 0 ? 1u : 0u);
             mma_commit(&a_empty[buf]);
             mma_commit(&acc_full[buf]);
+            STADD(5, tw);
           }
         }
       }
+      STFLUSH(3); STFLUSH(4); STFLUSH(5);
     }
-  } else {
+  } else if (warp < STORE_WARP) {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const bool leader = warp == MMA_WARP + 1 && lane == 0;
+    (void)leader;
     const int pw = p.OC;  // panel row = all output channels of a pixel
     const int panel_bytes = BLOCK_M * pw;
     const int chunks = p.OC >> 5;
@@ -304,6 +364,7 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
     const FastQ fq = {p.f_lo1, p.f_hi1, 0u, 0u};
     uint32_t tile = 0;
     bool live = true;
+    STDECL;
     for (int blk = blockIdx.x; live && blk < p.num_blocks; blk += gridDim.x) {
       const int n = blk / p.blocks_per_image;
       const int oy0 = (blk - n * p.blocks_per_image) * p.rows_per_block;
@@ -312,33 +373,27 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
         for (int sg = 0; sg < p.segs; ++sg, ++tile) {
           const int buf = (int)(tile & 1u);
           const uint32_t par = (tile >> 1) & 1u;
+          STSTART(tw);
           if (!mbar_wait(&acc_full[buf], par, &abort_flag, 4)) { live = false; break; }
+          STADD(6, tw);
           tc_fence_after();
           if (!mbar_wait(&out_free[buf], par, &abort_flag, 5)) { live = false; break; }
+          STADD(7, tw);
           uint8_t* panel = out_panels + (size_t)buf * panel_bytes + row_off;
           const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * p.OC);
           const int ox = sg * p.seg_w + row_in_tile;
           const bool valid = row_in_tile < p.seg_w && ox < p.OW;
           const size_t lin0 = (((size_t)n * p.OH + oy) * p.OW + (valid ? ox : 0)) * p.OC;
+          if (p.fast_mode) {
+            if (p.fast_variant & 1) stem_fast_row<1>(fq, p.f_mul, tbase, chunks, bias_s, panel, sw_key);
+            else stem_fast_row<0>(fq, p.f_mul, tbase, chunks, bias_s, panel, sw_key);
+          } else
           for (int ci = 0; ci < chunks; ++ci) {
             int32_t v[32];
             tmem_ld32(tbase + (uint32_t)(ci * 32), v);
             const int4* bp = reinterpret_cast<const int4*>(bias_s + ci * 32);
             uint4 a, b;
-            if (p.fast_mode) {
-              const int mul = p.f_mul;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int4 b4 = bp[j];
-                v[4 * j] = v[4 * j] * mul + b4.x;
-                v[4 * j + 1] = v[4 * j + 1] * mul + b4.y;
-                v[4 * j + 2] = v[4 * j + 2] * mul + b4.z;
-                v[4 * j + 3] = v[4 * j + 3] * mul + b4.w;
-              }
-              const uint4 z = make_uint4(0, 0, 0, 0);
-              if (p.fast_variant & 1) fast_requant<1, 0>(fq, v, z, z, &a, &b);
-              else fast_requant<0, 0>(fq, v, z, z, &a, &b);
-            } else {
+            {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 const int4 b4 = bp[j];
@@ -361,20 +416,36 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
             mbar_arrive(&acc_empty[buf]);
             mbar_arrive(&out_full[buf]);
           }
-          if (leader) {
-            if (!mbar_wait(&out_full[buf], par, &abort_flag, 6)) { live = false; break; }  // all four warps wrote the panel
-            tma_store_3d(&tmap_y, out_panels + (size_t)buf * panel_bytes, 0, sg * p.seg_w, n * p.OH + oy);
-            tma_store_commit();
-            if (tile > 0) {
-              tma_store_wait_read1();  // the previous tile's panel has been read
-              mbar_arrive(&out_free[buf ^ 1]);
-            }
-          }
+          STADD(8, tw);
           if (abort_flag) { live = false; break; }
         }
       }
     }
-    if (leader) tma_store_wait_all();
+#ifdef CVMK_STEM_TIMING
+    if (leader) { STFLUSH(6); STFLUSH(7); STFLUSH(8); STFLUSH(9); }
+#endif
+  } else if (lane == 0) {
+    // ------------------------------------------------------------------ output stores
+    // One thread: waits until the four epilogue warps have written a panel, stores it with TMA,
+    // and hands the previous panel back once the engine has read it.
+    uint32_t tile = 0;
+    bool live = true;
+    const int panel_bytes = BLOCK_M * p.OC;
+    for (int blk = blockIdx.x; live && blk < p.num_blocks; blk += gridDim.x) {
+      const int n = blk / p.blocks_per_image;
+      const int oy0 = (blk - n * p.blocks_per_image) * p.rows_per_block;
+      for (int rr = 0; live && rr < p.rows_per_block && oy0 + rr < p.OH; ++rr) {
+        for (int sg = 0; sg < p.segs; ++sg, ++tile) {
+          const int buf = (int)(tile & 1u);
+          if (!mbar_wait(&out_full[buf], (tile >> 1) & 1u, &abort_flag, 6)) { live = false; break; }
+          tma_store_3d(&tmap_y, out_panels + (size_t)buf * panel_bytes, 0, sg * p.seg_w, n * p.OH + oy0 + rr);
+          tma_store_commit();
+          tma_store_wait_read();  // the engine has read this panel: hand it back at once
+          mbar_arrive(&out_free[buf]);
+        }
+      }
+    }
+    tma_store_wait_all();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -531,3 +602,9 @@ extern "C" int cvmk_conv2d_stem_launch(const cvmk_stem_conv_plan* plan, cvmk_str
   conv_stem_kernel<<<plan->grid, STEM_THREADS, plan->smem_bytes, (cudaStream_t)stream>>>(ty, p);
   return check_cuda(cudaGetLastError(), "conv_stem_kernel launch");
 }
+
+#ifdef CVMK_STEM_TIMING
+extern "C" int cvmk_stem_timing_read(long long* host, int count) {
+  return (int)cudaMemcpyFromSymbol(host, g_stem_timing, sizeof(long long) * (size_t)count);
+}
+#endif
