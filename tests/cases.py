@@ -92,6 +92,8 @@ def op_cases():
     add("conv_stem_fused_4ch_nobias", lambda: conv_case(34, 2, 4, 20, 16, 64, 5, 2, 0, bias=False, shift=8))
     add("conv_stem_fused_1x1", lambda: conv_case(35, 2, 2, 9, 16, 32, 1, 1, 0, shift=3))
     add("conv_stem_fused_s3_rows", lambda: conv_case(36, 1, 3, 37, 32, 64, 7, 3, 2, shift=8, relu=True))
+    # batch 8: the inference uploads the batch in four chunks and runs the stem per chunk
+    add("conv_stem_fused_b8_chunked", lambda: conv_case(38, 8, 3, 20, 16, 32, 3, 2, 1, shift=7, relu=True))
     def stem_generic():
         rng = np.random.RandomState(37)
         g = wl.GraphBuilder(37)
