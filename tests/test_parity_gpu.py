@@ -76,6 +76,36 @@ def test_random_conv_shapes(gpu_run, oracle):
         assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x)), (i, c, oc, k, stride, pad, dil, groups)
 
 
+def test_random_bottlenecks(gpu_run, oracle, wl):
+    """Residual bottleneck blocks on random shapes: 1x1 reduce, 3x3 (stride 1: spatial-patch TMA,
+    stride 2: im2col-mode TMA), 1x1 expand fused with the join, identity or projection shortcut;
+    odd spatial sizes and batches give partial tiles, small channel counts give several
+    (tap, channel block) units per ring stage."""
+    rng = np.random.RandomState(77)
+    for i in range(14):
+        mid = int(rng.choice([32, 64, 128]))
+        out = mid * int(rng.choice([2, 4]))
+        cin = out if rng.rand() < 0.4 else int(rng.choice([32, 64, 96, 256]))
+        stride = 1 if cin == out and rng.rand() < 0.7 else int(rng.choice([1, 2]))
+        batch = int(rng.randint(1, 10))
+        h, w = int(rng.randint(5, 23)), int(rng.randint(5, 23))
+        g = wl.GraphBuilder(300 + i)
+        x = cases.rnd(rng, (batch, cin, h, w), 8)
+        d = g.var("data", x.shape, 8)
+        sc = d
+        if cin != out or stride != 1:
+            sc = g.conv(d, out, 1, stride, 0, relu=False)
+        z = g.conv(d, mid, 1, 1, 0)
+        z = g.conv(z, mid, 3, stride, 1)
+        z = g.conv(z, out, 1, 1, 0, relu=False)
+        a = g.op("elemwise_add", [z, sc] if rng.rand() < 0.5 else [sc, z], g.shape_of(z))
+        if rng.rand() < 0.8:
+            a = g.op("relu", [a], g.shape_of(a))
+        y = g.op("cvm_clip", [a], g.shape_of(a), {"precision": int(rng.choice([8, 8, 7]))})
+        js, pb = g.finish(y)
+        assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x)), (i, cin, mid, out, stride, batch, h, w)
+
+
 def test_input_is_clamped_to_its_precision(gpu_run, oracle, wl):
     """graph_runtime.cc:379-386: -128 enters the network as -127."""
     js, pb, x = wl.conv_chain(batch=1, channels=32, size=8)
