@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libcvm_runtime.so")
 
-KERNEL_SRCS = ["common.cu", "conv_tc.cu", "conv_stem.cu", "conv_direct.cu", "elemwise.cu", "transform.cu", "nms.cu"]
+KERNEL_SRCS = ["common.cu", "conv_tc.cu", "conv_stem.cu", "conv_direct.cu", "elemwise.cu", "transform.cu", "nms.cu", "peak.cu"]
 HOST_SRCS = ["ops.cc", "graph.cc", "executor.cc", "c_api.cc"]
 
 NVCC_FLAGS = [

@@ -49,6 +49,14 @@ class Thrower {
 
 typedef std::vector<int64_t> Shape;
 
+// A refusal this library adds on top of the reference's checks (a model the reference would run
+// with out-of-bounds reads).  It is raised only after every check of the reference has passed, so
+// a model the reference refuses keeps the reference's status class.
+inline std::string& deferred_refusal() {
+  static thread_local std::string text;
+  return text;
+}
+
 inline int64_t shape_size(const Shape& s) {
   int64_t n = 1;
   for (auto d : s) n *= d;

@@ -43,6 +43,7 @@ class Model {
   void LoadParams(const std::string& params) {
     VERIFY_NE(params.size(), 0U);
     g_.LoadParams(params);
+    g_.RaiseRefusal();
     exec_.reset(new Executor(g_, device_id_));
   }
 
@@ -174,12 +175,22 @@ class Model {
 using cvm::Model;
 
 // include/cvm/errors.h:15-36
+static std::string& last_error_text() {
+  static thread_local std::string text;
+  return text;
+}
+static int report(const std::exception& e, int status) {
+  last_error_text() = e.what();
+  printf("ERROR: %s\n", e.what());
+  return status;
+}
+
 #define API_BEGIN() try {
 #define API_END()                                                             \
   }                                                                           \
-  catch (const std::runtime_error& e) { printf("ERROR: %s\n", e.what()); return ERROR_RUNTIME; } \
-  catch (const std::logic_error& e) { printf("ERROR: %s\n", e.what()); return ERROR_LOGIC; }     \
-  catch (const std::exception& e) { printf("ERROR: %s\n", e.what()); return ERROR_RUNTIME; }     \
+  catch (const std::runtime_error& e) { return report(e, ERROR_RUNTIME); }    \
+  catch (const std::logic_error& e) { return report(e, ERROR_LOGIC); }        \
+  catch (const std::exception& e) { return report(e, ERROR_RUNTIME); }        \
   return SUCCEED;
 
 extern "C" {
@@ -275,11 +286,15 @@ int CVMAPIGetGasFromGraphFile(const char* graph_json, unsigned long long* gas) {
   std::string json(graph_json);
   cvm::Graph g;
   g.Init(json);
-  *gas = (unsigned long long)g.GetOps();
+  const int64_t ops = g.GetOps();
+  g.RaiseRefusal();
+  *gas = (unsigned long long)ops;
   API_END();
 }
 
 // ---- measurement helpers (include/cvm/c_api_ext.h); not part of the reference ABI ----------
+
+const char* CVMXLastError(void) { return last_error_text().c_str(); }
 
 int CVMXStepCount(void* net, unsigned long long* n) {
   API_BEGIN();

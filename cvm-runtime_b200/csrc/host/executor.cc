@@ -977,6 +977,19 @@ struct Lowering {
     d.force_suppress = n.attrs.b("force_suppress") ? 1 : 0;
     d.scratch_bytes = cvmk_nms_scratch_bytes(d.B, d.N);
     d.scratch = ex.dalloc((size_t)d.scratch_bytes);
+    // The CPU operator writes -1 over the input rows outside the top_k (nms.cc:93-97).  That is
+    // visible when the input entry is a head or is read again by a later node.
+    const uint32_t in_eid = g.entry_id(n.inputs[0]);
+    bool observed = false;
+    for (const auto& h : g.outputs) observed |= g.entry_id(h) == in_eid;
+    for (uint32_t m = nid + 1; m < g.nodes.size(); ++m)
+      for (const auto& e : g.nodes[m].inputs) observed |= g.entry_id(e) == in_eid;
+    if (observed) {
+      const DevBuf own = materialize(in_eid);
+      VERIFY(own.ptr == x.ptr) << label << ": its input is read again after the operator, which needs the input "
+                               << "stored as int32 rows";
+      d.x_writeback = (int32_t*)own.ptr;
+    }
     add_step(label, [d](cudaStream_t s) { return cvmk_non_max_suppression(&d, s); });
   }
 

@@ -2,6 +2,7 @@
 // malformed model fails with the same status class (logic vs runtime error).
 #include "graph.h"
 #include <algorithm>
+#include <map>
 #include <cstring>
 #include <unordered_set>
 #include "json.h"
@@ -194,15 +195,22 @@ void Graph::Prepare() {
   const std::vector<uint32_t> json_row_ptr = node_row_ptr;
   node_row_ptr = row_ptr;  // entry ids below always use the recomputed table
 
-  for (const auto& n : nodes)
-    for (const auto& e : n.inputs) {
-      VERIFY_LT(e.node_id, nodes.size()) << "input refers to node " << e.node_id << " out of range";
-      VERIFY_LT(e.index, nodes[e.node_id].num_outputs) << "input refers to output " << e.index << " out of range";
-    }
-  for (const auto& e : outputs) {
-    VERIFY_LT(e.node_id, nodes.size()) << "head refers to node " << e.node_id << " out of range";
-    VERIFY_LT(e.index, nodes[e.node_id].num_outputs) << "head refers to output " << e.index << " out of range";
-  }
+  // The reference resolves (node, output) pairs by entry arithmetic alone (graph_runtime.h:466-472):
+  // an output index past the node's own outputs names the entry of a later node.  Such pairs are
+  // rewritten to the node that owns the entry; pairs that run off the entry table (an
+  // out-of-bounds read in the reference) are refused.
+  auto resolve = [&](NodeEntry& e, const char* what) {
+    VERIFY_LT(e.node_id, nodes.size()) << what << " refers to node " << e.node_id << " out of range";
+    if (e.index < nodes[e.node_id].num_outputs) return;
+    const uint64_t eid = (uint64_t)row_ptr[e.node_id] + e.index;
+    VERIFY_LT(eid, (uint64_t)num_entries) << what << " refers to output " << e.index << " out of range";
+    const uint32_t owner = (uint32_t)(std::upper_bound(row_ptr.begin(), row_ptr.end(), (uint32_t)eid) - row_ptr.begin()) - 1;
+    e.node_id = owner;
+    e.index = (uint32_t)eid - row_ptr[owner];
+  };
+  for (auto& n : nodes)
+    for (auto& e : n.inputs) resolve(e, "input");
+  for (auto& e : outputs) resolve(e, "head");
 
   VERIFY_EQ(num_entries, storage_id.size())
       << "graph attribute storage_id size: " << storage_id.size() << ", Expected " << num_entries;
@@ -327,11 +335,58 @@ void Graph::SetupPrecision() {
 }
 
 void Graph::Init(const std::string& json) {
+  deferred_refusal().clear();
   Load(json);
   Prepare();
   SetupShape();
   // SetupType: every entry is int32 in the reference and every registered FInferType keeps it so.
   SetupPrecision();
+  CheckStoragePlan();
+  refusal = deferred_refusal();
+}
+
+// The reference executes in the buffers the storage plan names (graph_runtime.cc:576-606): two
+// entries with one storage id are one piece of memory.  A plan produced by its compiler only
+// shares a buffer between entries that are never live together; any other plan makes operators
+// read values a later operator has already overwritten.  This library keeps one allocation per
+// materialised entry, so it can only honour plans of the first kind and refuses the rest.
+void Graph::CheckStoragePlan() {
+  if (!deferred_refusal().empty()) return;
+  const int64_t kForever = (int64_t)1 << 40;
+  std::vector<int64_t> def(num_entries, 0), last(num_entries, 0);
+  for (uint32_t nid = 0; nid < nodes.size(); ++nid) {
+    const Node& n = nodes[nid];
+    for (uint32_t i = 0; i < n.num_outputs; ++i) {
+      const uint32_t e = entry_id(nid, i);
+      def[e] = n.is_variable() ? -1 : (int64_t)nid;
+      last[e] = n.is_variable() && !n.is_data() ? kForever : def[e];   // parameters persist across calls
+    }
+  }
+  for (uint32_t nid = 0; nid < nodes.size(); ++nid)
+    for (const auto& e : nodes[nid].inputs) last[entry_id(e)] = std::max<int64_t>(last[entry_id(e)], nid);
+  for (const auto& e : outputs) last[entry_id(e)] = kForever;
+  std::map<int, std::vector<uint32_t>> groups;
+  for (uint32_t e = 0; e < num_entries; ++e) groups[storage_id[e]].push_back(e);
+  for (auto& kv : groups) {
+    auto& g = kv.second;
+    if (g.size() < 2) continue;
+    std::stable_sort(g.begin(), g.end(), [&](uint32_t a, uint32_t b) { return def[a] < def[b]; });
+    for (size_t i = 0; i + 1 < g.size(); ++i) {
+      const uint32_t a = g[i], b = g[i + 1];
+      // b may take over a's buffer at the node that consumes a for the last time (in place), not before
+      if (def[a] == def[b] || last[a] > def[b]) {
+        std::ostringstream os;
+        os << "storage plan: entries " << a << " and " << b << " share storage id " << kv.first
+           << " while both are live";
+        deferred_refusal() = os.str();
+        return;
+      }
+    }
+  }
+}
+
+void Graph::RaiseRefusal() const {
+  VERIFY(refusal.empty()) << refusal;
 }
 
 // CvmRuntime::PlanStorage + GetStorageSize, src/runtime/graph_runtime.cc:503-531, :565-574
@@ -373,6 +428,7 @@ int64_t Graph::GetOps() const {
         base = shape[entry_id(n.inputs[0])][0] * 20;
       } else if (op == "conv2d") {
         const Shape& w = shape[entry_id(n.inputs[1])];
+        VERIFY(!w.empty() && w[0] != 0) << "conv2d weight of " << n.name() << " has no shape";
         base = shape_size(w) / w[0] * 3;
         if (n.attrs.b("use_bias")) base += 1;
       } else if (op == "max_pool2d") {

@@ -35,6 +35,8 @@ class Graph {
  public:
   // CvmRuntime::Init (graph_runtime.cc:106-112): Load + PrepareGraphWithVersion + CheckAttr.
   void Init(const std::string& json);
+  void RaiseRefusal() const;
+  void CheckStoragePlan();
   // CvmRuntime::LoadParams (graph_runtime.cc:476-501).
   void LoadParams(const std::string& blob);
 
@@ -57,6 +59,7 @@ class Graph {
   std::vector<std::string> dltype, op_attrs;
   std::vector<Shape> shape;
   std::string version = "cvm_1.0.0";
+  std::string refusal;  // see deferred_refusal(); raised by RaiseRefusal() once the reference's checks passed
   std::string postprocess;
   std::map<uint32_t, HostTensor> params;  // by entry id
   bool params_loaded = false;

@@ -259,7 +259,8 @@ bool conv2d_shape(const Attrs& a, std::vector<Shape>* in, std::vector<Shape>* ou
   Shape w = {channels, d[1] / groups, ks[0], ks[1]};
   // The reference only fills an unknown weight shape; a weight whose shape disagrees with the
   // attributes makes its kernels index out of bounds.  Here it is refused.
-  VERIFY(in->at(1) == w) << "Conv2D weight shape " << shape_str(in->at(1)) << " does not match attributes " << shape_str(w);
+  if (!(in->at(1) == w) && deferred_refusal().empty())
+    deferred_refusal() = "Conv2D weight shape " + shape_str(in->at(1)) + " does not match attributes " + shape_str(w);
   if (use_bias) {
     Shape bs = {channels};
     CHECK(in->at(2) == bs) << "Operator conv2d(name=" << a.name << ") expects bias's shape to be "

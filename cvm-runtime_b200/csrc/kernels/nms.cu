@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(THREADS) gvc_kernel(const int32_t* __restrict_
 // ---------------------------------------------------------------------------------------------
 struct NmsParams {
   const int32_t* x; const int32_t* vc; int32_t* y;
+  int32_t* xw;            // when set: rows outside the top_k best get -1 in the input as well
   int B, N;
   int mos, thr, topk, force;
   uint32_t* scratch;      // per batch: keyA, keyB, idxA, idxB, removed, stop : 6 * npad words
@@ -365,6 +366,13 @@ __global__ void __launch_bounds__(THREADS) nms_kernel(const __grid_constant__ Nm
   }
   const int emitted = min(running, limit);
   for (size_t i = (size_t)emitted * 6 + tid; i < (size_t)N * 6; i += THREADS) yb[i] = -1;
+  // The CPU implementation's side effect on its input (nms.cc:93-97); nothing above reads the rows
+  // past `keep` after the sort.
+  if (p.xw != nullptr && p.topk > 0 && p.topk < vc) {
+    __syncthreads();
+    int32_t* xwb = p.xw + (size_t)b * N * 6;
+    for (int e = p.topk * 6 + tid; e < vc * 6; e += THREADS) xwb[(size_t)order[e / 6] * 6 + e % 6] = -1;
+  }
 }
 
 }  // namespace
@@ -399,7 +407,7 @@ extern "C" int cvmk_non_max_suppression(const cvmk_nms_desc* d, cvmk_stream_t st
     return CVMK_ERR_ARG;
   }
   NmsParams p;
-  p.x = d->x; p.vc = d->valid_count; p.y = d->y;
+  p.x = d->x; p.vc = d->valid_count; p.y = d->y; p.xw = d->x_writeback;
   p.B = d->B; p.N = d->N;
   p.mos = d->max_output_size; p.thr = d->iou_threshold; p.topk = d->top_k; p.force = d->force_suppress;
   p.scratch = reinterpret_cast<uint32_t*>(d->scratch);
@@ -461,7 +469,7 @@ extern "C" int cvmk_non_max_suppression_static(const int32_t* x, const int32_t* 
     attr_of_device[dev] = true;
   }
   NmsParams p;
-  p.x = x; p.vc = valid_count; p.y = y;
+  p.x = x; p.vc = valid_count; p.y = y; p.xw = nullptr;
   p.B = B; p.N = N;
   p.mos = max_output_size; p.thr = iou_threshold; p.topk = top_k; p.force = force_suppress;
   p.scratch = reinterpret_cast<uint32_t*>(scratch_of_device[dev]);

@@ -23,7 +23,7 @@ KERNEL_SYMBOLS = [
     "cvmk_im2col_pack", "cvmk_stem_pack", "cvmk_stem_pack_supported",
     "cvmk_conv2d_stem_supported", "cvmk_conv2d_stem_prepare", "cvmk_conv2d_stem_launch",
     "cvmk_conv2d_tc_supported", "cvmk_conv2d_tc_prepare", "cvmk_conv2d_tc_launch", "cvmk_elemwise",
-    "cvmk_strided", "cvmk_take", "cvmk_where", "cvmk_reduce", "cvmk_max_pool2d", "cvmk_conv2d_direct", "cvmk_get_valid_counts",
+    "cvmk_measure_i8_mma_rate", "cvmk_strided", "cvmk_take", "cvmk_where", "cvmk_reduce", "cvmk_max_pool2d", "cvmk_conv2d_direct", "cvmk_get_valid_counts",
     "cvmk_nms_scratch_bytes", "cvmk_non_max_suppression", "cvmk_non_max_suppression_static",
     "cvmk_last_error",
 ]
@@ -32,9 +32,10 @@ KERNEL_SYMBOLS = [
 class CVMError(RuntimeError):
     """A C-ABI call returned ERROR_LOGIC (1) or ERROR_RUNTIME (2)."""
 
-    def __init__(self, status, what):
-        super().__init__("%s returned status %d" % (what, status))
+    def __init__(self, status, what, text=""):
+        super().__init__("%s returned status %d%s" % (what, status, ": " + text if text else ""))
         self.status = status
+        self.text = text
 
 
 _LIB = None
@@ -48,13 +49,19 @@ def lib():
             raise OSError("%s not found: build it with `python cvm-runtime_b200/build.py`" % LIB_PATH)
         _LIB = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
         _LIB.cvmk_last_error.restype = ctypes.c_char_p
+        _LIB.CVMXLastError.restype = ctypes.c_char_p
         _LIB.cvmk_nms_scratch_bytes.restype = ctypes.c_int64
     return _LIB
 
 
+def last_error():
+    """Text of the last failing C-ABI call of this thread."""
+    return (lib().CVMXLastError() or b"").decode("utf-8", "replace")
+
+
 def check_call(status, what="CVMAPI call"):
     if status != SUCCEED:
-        raise CVMError(status, what)
+        raise CVMError(status, what, last_error())
 
 
 NetworkHandle = ctypes.c_void_p
@@ -167,6 +174,16 @@ def replay_device(net, iters):
     ms = ctypes.c_float()
     check_call(lib().CVMXReplayDevice(net, ctypes.c_int(iters), ctypes.byref(ms)), "CVMXReplayDevice")
     return ms.value
+
+
+def measure_i8_mma_rate(n=256, reps=20000):
+    """Measured int8 tensor-core rate of the current GPU in TOP/s (tcgen05.mma kind::i8, M = 128,
+    N = n, K = 32 issued back to back on every SM)."""
+    tops = ctypes.c_double()
+    rc = lib().cvmk_measure_i8_mma_rate(ctypes.c_int(n), ctypes.c_int(reps), ctypes.byref(tops))
+    if rc != 0:
+        raise RuntimeError("cvmk_measure_i8_mma_rate failed (%d): %s" % (rc, lib().cvmk_last_error().decode()))
+    return tops.value
 
 
 def profile_steps(net, input_data):

@@ -16,6 +16,9 @@
 extern "C" {
 #endif
 
+/* Text of the last error a CVMAPI* / CVMX* call returned on this thread (the reference only prints
+ * it); valid until the next failing call of the thread. */
+CVM_DLL const char* CVMXLastError(void);
 /* Number of kernel launches one inference enqueues (fused operators count once). */
 CVM_DLL int CVMXStepCount(void* net, unsigned long long* n);
 /* Device memory held by the model: weights, activations, staging. */

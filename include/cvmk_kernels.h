@@ -325,7 +325,7 @@ CVMK_API int cvmk_conv2d_stem_launch(const cvmk_stem_conv_plan* plan, cvmk_strea
  * their original order, write their number to valid_count[b], fill the remaining rows with -1.
  * x, y: int32 [B, N, K]; valid_count: int32 [B].
  * non_max_suppression (cpu/ops/nms.cc:65-140, iou :4-40), K = 6, corner boxes at columns 2..5,
- * score at column 1, class id at column 0.  x is read only; `scratch` needs
+ * score at column 1, class id at column 0.  x is read only unless x_writeback is set; `scratch` needs
  * cvmk_nms_scratch_bytes(B, N) bytes (16-byte aligned) and is clobbered.
  * ---------------------------------------------------------------------------------------------- */
 CVMK_API int cvmk_get_valid_counts(const int32_t* x, int32_t* y, int32_t* valid_count, int32_t B,
@@ -339,6 +339,10 @@ typedef struct {
   int32_t max_output_size, iou_threshold, top_k, force_suppress;
   void* scratch;
   int64_t scratch_bytes;
+  /* The CPU implementation overwrites, in its INPUT, the rows that fall outside the top_k best
+   * scores with -1 (cpu/ops/nms.cc:93-97).  A caller whose graph reads that tensor again after the
+   * operator passes x here to get the same side effect; NULL leaves x untouched. */
+  int32_t* x_writeback;
 } cvmk_nms_desc;
 CVMK_API int64_t cvmk_nms_scratch_bytes(int32_t B, int32_t N);
 CVMK_API int cvmk_non_max_suppression(const cvmk_nms_desc* d, cvmk_stream_t stream);
@@ -370,6 +374,12 @@ CVMK_API int cvmk_non_max_suppression_static(const int32_t* x, const int32_t* va
                                              int32_t B, int32_t N, int32_t max_output_size,
                                              int32_t iou_threshold, int32_t top_k,
                                              int32_t force_suppress, cvmk_stream_t stream);
+
+/* Measurement helper (no counterpart in the reference): the int8 tensor-core rate of the current
+ * GPU in TOP/s (2 * MACs), measured by issuing `reps` tcgen05.mma kind::i8 instructions of shape
+ * M = 128, N = n, K = 32 per SM on operands resident in shared memory and timing the launch with
+ * CUDA events.  bench.py uses n = 256 as the denominator of the tensor roofline. */
+CVMK_API int cvmk_measure_i8_mma_rate(int n, int reps, double* tops);
 
 /* Text of the last CUDA / argument error seen by a launcher on this thread. */
 CVMK_API const char* cvmk_last_error(void);

@@ -50,6 +50,11 @@ def golden_status():
 
 
 @pytest.fixture(scope="session")
+def golden_fuzz():
+    return dict(np.load(os.path.join(ROOT, "tests", "golden", "fuzz.npz")))
+
+
+@pytest.fixture(scope="session")
 def gpu_run(rt):
     """Runs (json, params, input) through the C-ABI on cuda:0 and returns the output bytes."""
     def run(js, pb, x, device=0):

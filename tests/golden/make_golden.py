@@ -55,5 +55,83 @@ def main():
         print("  %-28s -> %d" % (k, v))
 
 
+def fuzz_worker(start, path):
+    """Runs mutants start.. against the reference, one JSON line each; a `begin` line first so the
+    parent can tell which mutant took the process down."""
+    import json
+    import fuzz_cases
+    ref = oracle.ref_lib
+    table = fuzz_cases.fuzz_cases()
+    names = list(table)
+    with open(path, "a") as f:
+        for i in range(start, len(names)):
+            js, pb, x, _ = table[names[i]]
+            f.write(json.dumps({"begin": i}) + "\n")
+            f.flush()
+            os.fsync(f.fileno())
+            m = ref.RefModel(js, pb, 0)
+            rec = {"i": i, "load": int(m.status), "infer": -1, "out": "", "gas_status": -1, "gas": 0}
+            if m.loaded:
+                gst, gas = m.gas()
+                rec["gas_status"], rec["gas"] = int(gst), int(gas)
+                if x is not None:
+                    st, y = m.infer(x)
+                    rec["infer"] = int(st)
+                    if st == 0:
+                        rec["out"] = sha(y.tobytes()) + ":%d" % y.nbytes
+                m.free()
+            f.write(json.dumps(rec) + "\n")
+            f.flush()
+
+
+def fuzz_golden():
+    """tests/golden/fuzz.npz: the reference's verdict on every mutant of tests/fuzz_cases.py.
+    load = -100 marks a mutant that crashed or hung the reference process."""
+    import json
+    import fuzz_cases
+    names = list(fuzz_cases.fuzz_cases())
+    path = os.path.join(HERE, "_fuzz_progress.jsonl")
+    if os.path.exists(path):
+        os.remove(path)
+    recs = {}
+    start = 0
+    while start < len(names):
+        try:
+            subprocess.run([sys.executable, os.path.abspath(__file__), "--fuzz-worker", str(start), path],
+                           stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL, timeout=600)
+        except subprocess.TimeoutExpired:
+            pass
+        last_begin = None
+        for line in open(path):
+            r = json.loads(line)
+            if "begin" in r:
+                last_begin = r["begin"]
+            else:
+                recs[r["i"]] = r
+        if last_begin is None:
+            raise SystemExit("fuzz worker produced nothing")
+        if last_begin not in recs:
+            recs[last_begin] = {"i": last_begin, "load": -100, "infer": -1, "out": "", "gas_status": -1, "gas": 0}
+        start = max(recs) + 1
+    os.remove(path)
+    out = {"names": np.array(names)}
+    out["load"] = np.array([recs[i]["load"] for i in range(len(names))], np.int32)
+    out["infer"] = np.array([recs[i]["infer"] for i in range(len(names))], np.int32)
+    out["gas_status"] = np.array([recs[i]["gas_status"] for i in range(len(names))], np.int32)
+    out["gas"] = np.array([recs[i]["gas"] for i in range(len(names))], np.int64)
+    out["out_sha"] = np.array([recs[i]["out"] for i in range(len(names))])   # "sha256:length" or ""
+    np.savez_compressed(os.path.join(HERE, "fuzz.npz"), **out)
+    load = out["load"]
+    print("fuzz: %d mutants: %d accepted (%d inferred), %d logic errors, %d runtime errors, %d crashed the reference"
+          % (len(names), int((load == 0).sum()), int((out["infer"] == 0).sum()), int((load == 1).sum()),
+             int((load == 2).sum()), int((load == -100).sum())))
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "--fuzz-worker":
+        fuzz_worker(int(sys.argv[2]), sys.argv[3])
+    elif len(sys.argv) > 1 and sys.argv[1] == "--fuzz":
+        fuzz_golden()
+    else:
+        main()
+        fuzz_golden()

@@ -59,6 +59,40 @@ def test_malformed_models_fail_like_the_reference(name, rt, golden_status):
     assert st == want
 
 
+def test_fuzzed_models_are_refused_like_the_reference(rt, golden_fuzz):
+    """Every mutant the reference refuses is refused with the same status class; gas of the
+    accepted ones matches (graph-only query, no GPU)."""
+    import fuzz_cases
+    table = fuzz_cases.fuzz_cases()
+    names = list(table)
+    assert names == golden_fuzz["names"].tolist()
+    wrong = []
+    refused = stricter = 0
+    for i, name in enumerate(names):
+        js, pb, _, desc = table[name]
+        want = int(golden_fuzz["load"][i])
+        if want in (1, 2):
+            refused += 1
+            net = ctypes.c_void_p()
+            st = rt.lib().CVMAPILoadModel(js, len(js), pb, len(pb), ctypes.byref(net), 1, 0)
+            if st == 0:
+                rt.lib().CVMAPIFreeModel(net)
+            if st != want:
+                wrong.append((name, desc, want, st))
+        elif want == 0 and int(golden_fuzz["gas_status"][i]) == 0:
+            try:
+                gas = rt.CVMAPIGetGasFromGraphFile(js)
+            except rt.CVMError as e:
+                if e.status == rt.ERROR_LOGIC and fuzz_cases.is_documented_refusal(e.text):
+                    stricter += 1
+                    continue
+                gas = "status %d" % e.status
+            if gas != int(golden_fuzz["gas"][i]):
+                wrong.append((name, desc, "gas %d" % int(golden_fuzz["gas"][i]), gas))
+    assert refused >= 500 and stricter <= 80
+    assert not wrong, wrong
+
+
 def test_null_arguments_are_runtime_errors(rt):
     lib = rt.lib()
     v = ctypes.c_ulonglong()

@@ -159,6 +159,49 @@ def test_accepted_variants_load(rt, golden_status):
         rt.CVMAPIFreeModel(net)
 
 
+def test_fuzzed_models_accepted_like_the_reference(rt, golden_fuzz):
+    """Mutants the reference loads: same load status, same inference status, same output bytes."""
+    import ctypes
+    import hashlib
+    import fuzz_cases
+    table = fuzz_cases.fuzz_cases()
+    names = list(table)
+    assert names == golden_fuzz["names"].tolist()
+    wrong = []
+    ran = 0
+    for i, name in enumerate(names):
+        if int(golden_fuzz["load"][i]) != 0:
+            continue
+        js, pb, x, desc = table[name]
+        net = ctypes.c_void_p()
+        st = rt.lib().CVMAPILoadModel(js, len(js), pb, len(pb), ctypes.byref(net), 1, 0)
+        if st != 0:
+            if not (st == rt.ERROR_LOGIC and fuzz_cases.is_documented_refusal(rt.last_error())):
+                wrong.append((name, desc, "load", st, rt.last_error()))
+            continue
+        try:
+            if x is None:
+                continue
+            n_out = ctypes.c_ulonglong()
+            rt.lib().CVMAPIGetOutputLength(net, ctypes.byref(n_out))
+            out = np.zeros(n_out.value, np.uint8)
+            xc = np.ascontiguousarray(x)
+            ist = rt.lib().CVMAPIInference(net, xc.ctypes.data_as(ctypes.c_char_p), ctypes.c_int(xc.nbytes),
+                                           out.ctypes.data_as(ctypes.c_char_p))
+            want = int(golden_fuzz["infer"][i])
+            if ist != want:
+                wrong.append((name, desc, "infer status", want, ist))
+            elif want == 0:
+                ran += 1
+                digest = "%s:%d" % (hashlib.sha256(out.tobytes()).hexdigest(), out.nbytes)
+                if digest != str(golden_fuzz["out_sha"][i]):
+                    wrong.append((name, desc, "output differs"))
+        finally:
+            rt.lib().CVMAPIFreeModel(net)
+    assert ran >= 250
+    assert not wrong, wrong
+
+
 # ---------------------------------------------------------------------------------------------
 # full-size configurations: size-independent properties
 # ---------------------------------------------------------------------------------------------

@@ -20,7 +20,8 @@ class NmsDesc(ctypes.Structure):
     _fields_ = [("x", ctypes.c_void_p), ("valid_count", ctypes.c_void_p), ("y", ctypes.c_void_p),
                 ("B", ctypes.c_int32), ("N", ctypes.c_int32), ("max_output_size", ctypes.c_int32),
                 ("iou_threshold", ctypes.c_int32), ("top_k", ctypes.c_int32), ("force_suppress", ctypes.c_int32),
-                ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_int64)]
+                ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_int64),
+                ("x_writeback", ctypes.c_void_p)]
 
 
 def _rows(batch, n, seed):
