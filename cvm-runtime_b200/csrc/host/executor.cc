@@ -689,8 +689,8 @@ struct Lowering {
   void lower_reduce(uint32_t nid) {
     const Node& n = g.nodes[nid];
     const uint32_t ei = g.entry_id(n.inputs[0]), eo = g.entry_id(nid, 0);
-    const DevBuf x = materialize(ei);
-    const Shape& xs = x.shape;
+    DevBuf x = materialize(ei);
+    const Shape xs = x.shape;
     const Shape& ysh = g.shape[eo];
     const int xnd = (int)xs.size();
     Shape axis = n.attrs.t("axis");
@@ -724,6 +724,24 @@ struct Lowering {
     }
     const bool out_needs_convert = wants_nhwc(ysh);
     if (!out_needs_convert) { extend_chain(&ch); bind_chain(&ch.ep); }
+    // The reference pairs the output's non-unit dimensions with the input's kept ones from the
+    // right and steps by row-major strides (reduce.cc:66-89).  When unit dimensions make the
+    // pairing land on a dimension of another extent, the walk leaves that dimension and carries
+    // into its neighbours; only the row-major layout reproduces that, so such inputs are read
+    // from a row-major copy.
+    if (x.nhwc && !real.empty()) {
+      std::vector<char> fl(xnd, 0);
+      for (auto a : real) fl[a] = 1;
+      std::vector<int64_t> nz;
+      for (auto v : ysh) if (v != 1) nz.push_back(v);
+      bool straight = true;
+      int xj = xnd - 1;
+      for (int j = (int)nz.size() - 1; j >= 0; --j) {
+        while (xj >= 0 && fl[xj--]) {}
+        straight &= xj + 1 >= 0 && xj + 1 < xnd && xs[xj + 1] == nz[j];
+      }
+      if (!straight) x = canon_view(ei, label);
+    }
     const auto xst = phys_strides(xs, x.nhwc);
     cvmk_reduce_desc d;
     memset(&d, 0, sizeof(d));

@@ -55,6 +55,11 @@ def golden_fuzz():
 
 
 @pytest.fixture(scope="session")
+def golden_random():
+    return dict(np.load(os.path.join(ROOT, "tests", "golden", "random_graphs.npz")))
+
+
+@pytest.fixture(scope="session")
 def gpu_run(rt):
     """Runs (json, params, input) through the C-ABI on cuda:0 and returns the output bytes."""
     def run(js, pb, x, device=0):

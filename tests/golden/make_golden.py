@@ -127,11 +127,79 @@ def fuzz_golden():
              int((load == 2).sum()), int((load == -100).sum())))
 
 
+def random_worker(start, path):
+    import json
+    import random_graphs
+    ref = oracle.ref_lib
+    table = random_graphs.random_cases()
+    names = list(table)
+    with open(path, "a") as f:
+        for i in range(start, len(names)):
+            js, pb, x = table[names[i]]()
+            f.write(json.dumps({"begin": i}) + "\n")
+            f.flush()
+            os.fsync(f.fileno())
+            m = ref.RefModel(js, pb, 0)
+            rec = {"i": i, "load": int(m.status), "infer": -1, "out": ""}
+            if m.loaded:
+                st, y = m.infer(x)
+                rec["infer"] = int(st)
+                if st == 0:
+                    rec["out"] = sha(y.tobytes()) + ":%d" % y.nbytes
+                m.free()
+            f.write(json.dumps(rec) + "\n")
+            f.flush()
+
+
+def random_golden():
+    """tests/golden/random_graphs.npz: the reference's verdict on every graph of tests/random_graphs.py."""
+    import json
+    import random_graphs
+    names = list(random_graphs.random_cases())
+    path = os.path.join(HERE, "_random_progress.jsonl")
+    if os.path.exists(path):
+        os.remove(path)
+    recs = {}
+    start = 0
+    while start < len(names):
+        try:
+            subprocess.run([sys.executable, os.path.abspath(__file__), "--random-worker", str(start), path],
+                           stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL, timeout=900)
+        except subprocess.TimeoutExpired:
+            pass
+        last_begin = None
+        for line in open(path):
+            r = json.loads(line)
+            if "begin" in r:
+                last_begin = r["begin"]
+            else:
+                recs[r["i"]] = r
+        if last_begin is None:
+            raise SystemExit("random-graph worker produced nothing")
+        if last_begin not in recs:
+            recs[last_begin] = {"i": last_begin, "load": -100, "infer": -1, "out": ""}
+        start = max(recs) + 1
+    os.remove(path)
+    out = {"names": np.array(names),
+           "load": np.array([recs[i]["load"] for i in range(len(names))], np.int32),
+           "infer": np.array([recs[i]["infer"] for i in range(len(names))], np.int32),
+           "out_sha": np.array([recs[i]["out"] for i in range(len(names))])}
+    np.savez_compressed(os.path.join(HERE, "random_graphs.npz"), **out)
+    print("random graphs: %d: %d ran, %d refused at load, %d failed at inference, %d crashed the reference"
+          % (len(names), int((out["infer"] == 0).sum()), int(((out["load"] == 1) | (out["load"] == 2)).sum()),
+             int(((out["load"] == 0) & (out["infer"] > 0)).sum()), int((out["load"] == -100).sum())))
+
+
 if __name__ == "__main__":
-    if len(sys.argv) > 1 and sys.argv[1] == "--fuzz-worker":
+    if len(sys.argv) > 1 and sys.argv[1] == "--random-worker":
+        random_worker(int(sys.argv[2]), sys.argv[3])
+    elif len(sys.argv) > 1 and sys.argv[1] == "--random":
+        random_golden()
+    elif len(sys.argv) > 1 and sys.argv[1] == "--fuzz-worker":
         fuzz_worker(int(sys.argv[2]), sys.argv[3])
     elif len(sys.argv) > 1 and sys.argv[1] == "--fuzz":
         fuzz_golden()
     else:
         main()
         fuzz_golden()
+        random_golden()

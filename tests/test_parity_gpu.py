@@ -202,6 +202,48 @@ def test_fuzzed_models_accepted_like_the_reference(rt, golden_fuzz):
     assert not wrong, wrong
 
 
+def test_random_graphs_match_the_reference(rt, golden_random):
+    """Random operator graphs (tests/random_graphs.py): load status, inference status and output
+    bytes as the reference's CPU runtime gave them."""
+    import ctypes
+    import hashlib
+    import random_graphs
+    table = random_graphs.random_cases()
+    names = list(table)
+    assert names == golden_random["names"].tolist()
+    wrong = []
+    ran = 0
+    for i, name in enumerate(names):
+        want_load = int(golden_random["load"][i])
+        if want_load not in (0, 1, 2):
+            continue
+        js, pb, x = table[name]()
+        net = ctypes.c_void_p()
+        st = rt.lib().CVMAPILoadModel(js, len(js), pb, len(pb), ctypes.byref(net), 1, 0)
+        if st != want_load:
+            wrong.append((name, "load", want_load, st, rt.last_error()))
+        if st != 0:
+            continue
+        try:
+            n_out = ctypes.c_ulonglong()
+            rt.lib().CVMAPIGetOutputLength(net, ctypes.byref(n_out))
+            out = np.zeros(n_out.value, np.uint8)
+            ist = rt.lib().CVMAPIInference(net, x.ctypes.data_as(ctypes.c_char_p), ctypes.c_int(x.nbytes),
+                                           out.ctypes.data_as(ctypes.c_char_p))
+            want = int(golden_random["infer"][i])
+            if ist != want:
+                wrong.append((name, "infer status", want, ist, rt.last_error()))
+            elif want == 0:
+                ran += 1
+                digest = "%s:%d" % (hashlib.sha256(out.tobytes()).hexdigest(), out.nbytes)
+                if digest != str(golden_random["out_sha"][i]):
+                    wrong.append((name, "output differs"))
+        finally:
+            rt.lib().CVMAPIFreeModel(net)
+    assert ran >= 400
+    assert not wrong, wrong
+
+
 # ---------------------------------------------------------------------------------------------
 # full-size configurations: size-independent properties
 # ---------------------------------------------------------------------------------------------
