@@ -212,8 +212,61 @@ def random_graph(seed):
     return js, pb, x
 
 
+def random_tail(seed):
+    """A detection tail (get_valid_counts -> non_max_suppression, nms.cc:42-140) on boxes built to
+    hit the corners of the CPU loop: tied scores, negative class ids, identical, empty and inverted
+    boxes, every relation between top_k / max_output_size / valid count, several 512-box sweep
+    blocks, and (sometimes) the operator's input as a second head."""
+    rng = np.random.RandomState(seed)
+    b = int(rng.randint(1, 5))
+    n = int([rng.randint(1, 40), rng.randint(40, 300), rng.randint(500, 1300)][rng.randint(3)])
+    style = rng.randint(3)
+    rows = np.zeros((b, n, 6), np.int32)
+    if style == 0:      # coarse grid: many exact ties and identical boxes
+        rows[..., 0] = rng.randint(-1, 3, size=(b, n))
+        rows[..., 1] = rng.randint(0, 8, size=(b, n)) * 1000
+        rows[..., 2:4] = rng.randint(0, 6, size=(b, n, 2)) * 10
+        rows[..., 4:6] = rows[..., 2:4] + rng.randint(-1, 4, size=(b, n, 2)) * 10
+    elif style == 1:    # ordinary detections
+        rows[..., 0] = rng.randint(0, 5, size=(b, n))
+        rows[..., 1] = rng.randint(0, 1 << 15, size=(b, n))
+        rows[..., 2:4] = rng.randint(0, 200, size=(b, n, 2))
+        rows[..., 4:6] = rows[..., 2:4] + rng.randint(1, 120, size=(b, n, 2))
+    else:               # clustered boxes, a few negative ids, full-range coordinates
+        centers = rng.randint(-3000, 3000, size=(b, 4, 2))
+        pick = rng.randint(0, 4, size=(b, n))
+        rows[..., 0] = np.where(rng.rand(b, n) < 0.1, -1, rng.randint(0, 3, size=(b, n)))
+        rows[..., 1] = rng.randint(0, 300, size=(b, n)) * 100
+        c = centers[np.arange(b)[:, None], pick]
+        rows[..., 2:4] = c + rng.randint(-40, 40, size=(b, n, 2))
+        rows[..., 4:6] = rows[..., 2:4] + rng.randint(0, 90, size=(b, n, 2))
+    rows = np.clip(rows, -32767, 32767).astype(np.int32)
+    g = wl.GraphBuilder(seed)
+    d = g.var("data", (b, n, 6), 16)
+    thr = int([-1, 0, 999, 2000, 5000, 20000, 40000][rng.randint(7)])
+    # An image without a valid box ends the CPU operator (nms.cc:76-79, `return 0`) and leaves the
+    # output rows of every later image uninitialised; only the last image may be empty here.
+    if ((rows[:-1, :, 1] > thr).sum(axis=1) <= 0).any():
+        thr = -1
+    vc, boxes = g.op("get_valid_counts", [d], [(b,), (b, n, 6)], {"score_threshold": thr})
+    y = g.op("non_max_suppression", [boxes, vc], (b, n, 6), {
+        "iou_threshold": int([1, 25, 50, 75, 100, 101, 1000][rng.randint(7)]),
+        "top_k": int([-1, -1, 0, 1, 5, max(1, n // 2), n, n + 5][rng.randint(8)]),
+        "max_output_size": int([-1, -1, 0, 1, 3, n][rng.randint(6)]),
+        "force_suppress": bool(rng.randint(2)), "id_index": 0, "score_index": 1, "coord_start": 2,
+        "return_indices": False, "invalid_to_bottom": True})
+    heads = [y]
+    if rng.randint(4) == 0:
+        heads.append(boxes)
+    js, pb = g.finish(heads)
+    return js, pb, rows
+
+
 COUNT = 600
+TAILS = 300
 
 
-def random_cases(count=COUNT, first_seed=5000):
-    return {"rand_%03d" % i: (lambda s=first_seed + i: random_graph(s)) for i in range(count)}
+def random_cases(count=COUNT, first_seed=5000, tails=TAILS):
+    table = {"rand_%03d" % i: (lambda s=first_seed + i: random_graph(s)) for i in range(count)}
+    table.update({"tail_%03d" % i: (lambda s=first_seed + i: random_tail(s)) for i in range(tails)})
+    return table

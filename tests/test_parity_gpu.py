@@ -240,7 +240,7 @@ def test_random_graphs_match_the_reference(rt, golden_random):
                     wrong.append((name, "output differs"))
         finally:
             rt.lib().CVMAPIFreeModel(net)
-    assert ran >= 400
+    assert ran >= 700
     assert not wrong, wrong
 
 
