@@ -60,7 +60,7 @@ def _step(g, rng, live):
     """Appends one random operator; returns the new tensor or None when nothing applied."""
     t = live[rng.randint(len(live))]
     r = len(t.shape)
-    kind = rng.randint(24)
+    kind = rng.randint(28)
     if kind <= 4 and r == 4:
         if t.prec > 8:
             t = _narrow(g, rng, t)
@@ -179,6 +179,43 @@ def _step(g, rng, live):
         if len(s) > 6:
             return None
         return _T(g.op("expand_dims", [t.e], s, {"axis": 1, "num_newaxis": 1}), s, t.prec)
+    if kind == 24:
+        mates = [u for u in live if len(u.shape) == r and u is not t and any(a < b for a, b in zip(u.shape, t.shape))]
+        if not mates:
+            return None
+        u = mates[rng.randint(len(mates))]
+        axes = [i for i in range(r) if u.shape[i] <= t.shape[i]]
+        if not axes:
+            return None
+        if len(axes) > 1 and rng.randint(2):
+            axes = axes[:rng.randint(1, len(axes))]
+        s = [u.shape[i] if i in axes else t.shape[i] for i in range(r)]
+        attrs = None if len(axes) == r and rng.randint(2) else {"axis": tuple(axes)}
+        return _T(g.op("slice_like", [t.e, u.e], s, attrs), s, t.prec)
+    if kind == 25:
+        axis = None if rng.randint(3) == 0 else int(rng.randint(0, r))
+        ishape = tuple(int(v) for v in rng.randint(1, 5, size=rng.randint(1, 3)))
+        n = int(np.prod(t.shape)) if axis is None else t.shape[axis]
+        idx = rng.randint(-3, n + 3, size=ishape).astype(np.int32)
+        iv = g.var("i%d" % len(g.nodes), ishape, 16, idx)
+        s = list(ishape) if axis is None else t.shape[:axis] + list(ishape) + t.shape[axis + 1:]
+        if len(s) > 6:
+            return None
+        return _T(g.op("take", [t.e, iv], s, None if axis is None else {"axis": axis}), s, t.prec)
+    if kind == 26 and t.prec <= 10:
+        in_dim = int(rng.randint(4, 300))
+        tp = int([8, 12, 16][rng.randint(3)])
+        a = (1 << (tp - 1)) - 1
+        table = rng.randint(-a, a + 1, size=(in_dim,)).astype(np.int32)
+        tv = g.var("t%d" % len(g.nodes), (in_dim,), tp, table)
+        return _T(g.op("cvm_lut", [t.e, tv], t.shape, {"in_dim": in_dim}), t.shape, tp)
+    if kind == 27 and t.prec <= 16:
+        same = [u for u in live if u.shape == t.shape and u is not t]
+        if len(same) < 1:
+            return None
+        u = same[rng.randint(len(same))]
+        v = same[rng.randint(len(same))]
+        return _T(g.op("where", [t.e, u.e, v.e], t.shape), t.shape, max(t.prec, u.prec, v.prec))
     return None
 
 
