@@ -59,9 +59,10 @@ struct ConvParams {
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int block_k, block_n, stages;
   int units;            // (filter tap, channel block) pairs loaded and multiplied per ring stage
-  int a_mode;           // activations: 0 plain 2-D tiles (1x1, dense), 1 im2col-mode TMA, 2 spatial patches
-  int patch_w, patch_h, patch_n;  // a_mode 2: an M tile is patch_w x patch_h output pixels of patch_n images
-  int tiles_w, tiles_h;           // a_mode 2: patches per image row / column
+  int a_mode;           // activations: 0 plain 2-D tiles (1x1, dense), 1 im2col-mode TMA, 2 spatial patches,
+                        // 3 spatial patches whose input halo is staged once per channel block
+  int patch_w, patch_h, patch_n;  // a_mode 2, 3: an M tile is patch_w x patch_h output pixels of patch_n images
+  int tiles_w, tiles_h;           // a_mode 2, 3: patches per image row / column
   int num_m_tiles, num_n_tiles;
   int tmem_cols;
   int* status;
@@ -177,7 +178,7 @@ __device__ __forceinline__ TileOrigin tile_origin(const ConvParams& p, int tile)
   t.n0 = (tile - mt * p.num_n_tiles) * p.block_n;
   t.m0 = mt * BLOCK_M;
   t.cw = t.ch = t.cn = 0;
-  if (p.a_mode == 2) {
+  if (p.a_mode >= 2) {
     const int r = mt / p.tiles_w;
     t.cw = (mt - r * p.tiles_w) * p.patch_w;
     const int tn = r / p.tiles_h;
@@ -209,9 +210,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int a_bytes = BLOCK_M * p.block_k;
   const int b_bytes = p.block_n * p.block_k;
   const int unit_bytes = a_bytes + b_bytes;          // one A tile and the B tile that goes with it
-  const int stage_bytes = p.units * unit_bytes;
   const int num_units = p.kh * p.kw * (p.c / p.block_k);
-  const int num_kb = (num_units + p.units - 1) / p.units;  // ring stages consumed per tile
+  // Halo mode (a_mode 3): a ring stage is one channel block: the (patch_w + kw - 1) x
+  // (patch_h + kh - 1) input pixels the patch touches, loaded once, then the kh * kw weight tiles.
+  // Every filter tap multiplies a window of that halo: the descriptor starts (fy * halo_w + fx)
+  // rows in and steps halo_w rows per 8-pixel group (the swizzle is a function of the shared-memory
+  // address, so any 16-byte aligned start inside the swizzled halo reads consistently).
+  const bool halo = p.a_mode == 3;
+  const int halo_w = p.patch_w + p.kw - 1;
+  const int halo_bytes = halo_w * (p.patch_h + p.kh - 1) * p.block_k;
+  const int halo_pad = (halo_bytes + 1023) & ~1023;
+  const int taps = p.kh * p.kw;
+  const int stage_bytes = halo ? halo_pad + taps * b_bytes : p.units * unit_bytes;
+  const int num_kb = halo ? p.c / p.block_k : (num_units + p.units - 1) / p.units;  // ring stages consumed per tile
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const bool bias_in_smem = (p.bias != nullptr || p.fast_mode) && p.oc <= MAX_BIAS;
 
@@ -279,6 +290,40 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int ox = rem - oy * p.ow;
           base_w = ox * p.stride_w - p.pad_w;
           base_h = oy * p.stride_h - p.pad_h;
+        }
+        if (halo) {
+          for (int cb = 0; cb < num_kb; ++cb) {
+            const bool my_stage = turn == 0;
+            turn ^= 1;
+            if (!my_stage) continue;
+            TSTART(tw);
+            if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
+            TADD(0, tw);
+            const uint32_t sa = smem_base + (uint32_t)(stage * stage_bytes);
+            const uint32_t bar = full0 + 8u * (uint32_t)stage;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                         "r"((uint32_t)(halo_bytes + taps * b_bytes)) : "memory");
+            const int cc = cb * p.block_k;
+            asm volatile(
+                "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)),
+                "r"(bar), "r"(cc), "r"(to.cw - p.pad_w), "r"(to.ch - p.pad_h), "r"(to.cn)
+                : "memory");
+            uint32_t sb = sa + (uint32_t)halo_pad;
+            int kcol = cc;
+            for (int t = 0; t < taps; ++t) {
+              asm volatile(
+                  "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                  " [%0], [%1, {%3, %4}], [%2];" ::"r"(sb), "l"(reinterpret_cast<uint64_t>(&tmap_b)),
+                  "r"(bar), "r"(kcol), "r"(to.n0)
+                  : "memory");
+              sb += (uint32_t)b_bytes;
+              kcol += p.c;
+            }
+            stage += 2;
+            if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
+          }
+          continue;
         }
         // Units (filter tap x channel block) in weight-matrix order; p.units of them share a stage.
         int kcol = 0, fy = 0, fx = 0, cc = 0, slot = 0;
@@ -350,6 +395,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_i8(p.block_n);
       const uint64_t desc_a0 = umma_desc(smem_u32(smem), p.block_k);
+      // halo windows: 8-pixel groups are one halo row (halo_w pixels) apart
+      const uint64_t desc_halo0 = (desc_a0 & ~((uint64_t)0x3FFF << 32)) |
+                                  ((uint64_t)(((uint32_t)(halo_w * p.block_k)) >> 4) << 32);
       const int nk = p.block_k / 32;
       int stage = 0;
       uint32_t phase = 0;
@@ -369,6 +417,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (!mbar_wait(&bar_full[stage], phase, &abort_flag, 3)) { live = false; break; }
           TADD(2, tw);
           tc_fence_after();
+          if (halo) {
+            const uint64_t st = (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
+            uint64_t db = desc_a0 + st + (uint64_t)((uint32_t)halo_pad >> 4);
+            for (int fy = 0; fy < p.kh; ++fy) {
+              uint64_t da = desc_halo0 + st + (uint64_t)((uint32_t)(fy * halo_w * p.block_k) >> 4);
+              for (int fx = 0; fx < p.kw; ++fx) {
+                mma_i8(d_tmem, da, db, idesc, (kb | fy | fx) ? 1u : 0u);
+                for (int j = 1; j < nk; ++j) mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
+                da += (uint64_t)((uint32_t)p.block_k >> 4);
+                db += (uint64_t)((uint32_t)b_bytes >> 4);
+              }
+            }
+            mma_commit(&bar_empty[stage]);
+            if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           // descriptors of this stage: the start-address field counts 16-byte units
           uint64_t da = desc_a0 + (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
           const int in_stage = min(p.units, num_units - unit);
@@ -413,7 +477,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int first_tile = blockIdx.x + group * gridDim.x;
     // patch mode: this thread's pixel inside the patch
     int pr_w = 0, pr_h = 0, pr_n = 0;
-    if (p.a_mode == 2) {
+    if (p.a_mode >= 2) {
       pr_w = row_in_tile % p.patch_w;
       const int r = row_in_tile / p.patch_w;
       pr_h = r % p.patch_h;
@@ -426,7 +490,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const TileOrigin to = tile_origin(p, tile);
       const int n0 = to.n0;
       int row = to.m0 + row_in_tile;  // linear output row; m_total marks a row outside the tensor
-      if (p.a_mode == 2) {
+      if (p.a_mode >= 2) {
         const int ow = to.cw + pr_w, oh = to.ch + pr_h, on = to.cn + pr_n;
         row = (ow < p.ow && oh < p.oh && on * p.oh * p.ow < p.m_total) ? (on * p.oh + oh) * p.ow + ow : p.m_total;
       }
@@ -551,7 +615,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint8_t* dst = buffer_of(g, b);
       mbar_expect_tx(&bar_res[g][b], (uint32_t)buf_bytes);
       for (int q = 0; q < p.panels; ++q) {
-        if (p.a_mode == 2)
+        if (p.a_mode >= 2)
           tma_load_4d(dst + (size_t)q * panel_size, &tmap_r, &bar_res[g][b], to.n0 + q * 128, to.cw, to.ch, to.cn);
         else
           tma_load_2d(dst + (size_t)q * panel_size, &tmap_r, &bar_res[g][b], to.n0 + q * 128, to.m0);
@@ -570,7 +634,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint8_t* src = buffer_of(g, b);
       for (int q = 0; q < p.panels; ++q) {
         if (to.n0 + q * 128 >= p.oc) break;
-        if (p.a_mode == 2) tma_store_4d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.cw, to.ch, to.cn);
+        if (p.a_mode >= 2) tma_store_4d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.cw, to.ch, to.cn);
         else tma_store_2d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.m0);
       }
       tma_store_commit();
@@ -729,6 +793,22 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   if (plan->a_im2col && d->stride_h == 1 && d->stride_w == 1 && !getenv("CVM_B200_NO_PATCH") &&
       pick_patch(*d, &patch_w, &patch_h, &patch_n))
     plan->a_im2col = 2;
+  // Halo mode: 3x3 (or any small) stride-1 undilated filters over at most 128 channels and output
+  // channels.  The M tile is an 8 x 16 pixel patch of one image; its 10 x 18 input halo is loaded
+  // once per 64-channel block and every filter tap multiplies a window of it, so the activations
+  // cross L2 -> shared memory about 1.4 times instead of kh * kw times.
+  bool halo = false;
+  if (plan->a_im2col == 2 && d->dil_h == 1 && d->dil_w == 1 && d->KH == 3 && d->KW == 3 && d->C % 64 == 0 &&
+      d->C <= 128 && bn <= 128 && d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !getenv("CVM_B200_NO_HALO")) {
+    const int64_t linear = ((int64_t)d->N * d->OH * d->OW + BLOCK_M - 1) / BLOCK_M;
+    const int64_t tiles = (int64_t)((d->OW + 7) / 8) * ((d->OH + 15) / 16) * d->N;
+    if (tiles * 20 <= linear * 27) {
+      halo = true;
+      plan->a_im2col = 3;
+      patch_w = 8; patch_h = 16; patch_n = 1;
+      bk = 64;
+    }
+  }
   plan->reserved[0] = patch_w; plan->reserved[1] = patch_h; plan->reserved[2] = patch_n;
 
   // Output path: int8 tiles leave through shared memory and a TMA store; the first int8 tensor
@@ -754,7 +834,10 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   const int64_t k_all = (int64_t)d->KH * d->KW * d->C;
   const int budget = SMEM_DYNAMIC_MAX - 1024;
   plan->io_bufs = 1;
-  if (plan->tma_out && !getenv("CVM_B200_SINGLE_STAGING")) {
+  const int halo_stage = halo ? (((10 * 18 * bk) + 1023) & ~1023) + d->KH * d->KW * bn * bk : 0;
+  if (halo) {
+    if (plan->tma_out && (budget - 4 * group_bytes) / halo_stage >= 3) plan->io_bufs = 2;
+  } else if (plan->tma_out && !getenv("CVM_B200_SINGLE_STAGING")) {
     auto ring_depth = [&](int k) { return (budget - 4 * group_bytes) / ((BLOCK_M + bn) * k); };
     if (ring_depth(bk) >= 3) plan->io_bufs = 2;
     else if (bk == 128 && k_all <= 512 && ring_depth(64) >= 3) { plan->io_bufs = 2; bk = 64; }
@@ -772,8 +855,9 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   if (const char* e = getenv("CVM_B200_UNITS")) units = atoi(e);
   while (units > 1 && (budget - io_bytes) / (units * unit_bytes) < 3) --units;
   if (units < 1) units = 1;
+  if (halo) units = d->KH * d->KW;
   plan->reserved[3] = units;
-  const int stage_bytes = units * unit_bytes;
+  const int stage_bytes = halo ? halo_stage : units * unit_bytes;
   int stages = (budget - io_bytes) / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) { set_error("conv2d_tc_prepare: tile does not fit shared memory"); return CVMK_ERR_UNSUPPORTED; }
@@ -786,7 +870,10 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   CUtensorMap* ta = reinterpret_cast<CUtensorMap*>(plan->tmap_a);
   CUtensorMap* tb = reinterpret_cast<CUtensorMap*>(plan->tmap_b);
   CUresult r;
-  if (plan->a_im2col == 2) {
+  if (plan->a_im2col == 3) {
+    r = encode_nhwc(enc_tiled, ta, d->x, d->N, d->H, d->W, d->C, bk, patch_w + d->KW - 1, patch_h + d->KH - 1, 1,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+  } else if (plan->a_im2col == 2) {
     r = encode_nhwc(enc_tiled, ta, d->x, d->N, d->H, d->W, d->C, bk, patch_w, patch_h, patch_n,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
   } else if (plan->a_im2col) {
@@ -808,7 +895,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   if (plan->tma_out) {
     auto encode_out = [&](unsigned char* map, const void* base, CUtensorMapL2promotion promo) {
       CUtensorMap* m = reinterpret_cast<CUtensorMap*>(map);
-      if (plan->a_im2col == 2)
+      if (plan->a_im2col >= 2)
         return encode_nhwc(enc_tiled, m, base, d->N, d->OH, d->OW, d->OC, plan->panel_bytes, patch_w, patch_h,
                            patch_n, promo);
       return encode_rows(enc_tiled, m, base, m_total, d->OC, plan->panel_bytes, BLOCK_M, promo);
@@ -821,7 +908,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
     }
   }
   int64_t num_m_tiles = (m_total + BLOCK_M - 1) / BLOCK_M;
-  if (plan->a_im2col == 2)
+  if (plan->a_im2col >= 2)
     num_m_tiles = (int64_t)((d->OW + patch_w - 1) / patch_w) * ((d->OH + patch_h - 1) / patch_h) *
                   ((d->N + patch_n - 1) / patch_n);
   const int64_t num_n_tiles = (d->OC + bn - 1) / bn;
@@ -851,7 +938,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.stages = plan->stages; p.a_mode = plan->a_im2col;
   p.units = plan->reserved[3] > 0 ? plan->reserved[3] : 1;
   p.num_m_tiles = (p.m_total + BLOCK_M - 1) / BLOCK_M;
-  if (p.a_mode == 2) {
+  if (p.a_mode >= 2) {
     p.patch_w = plan->reserved[0]; p.patch_h = plan->reserved[1]; p.patch_n = plan->reserved[2];
     p.tiles_w = (d.OW + p.patch_w - 1) / p.patch_w;
     p.tiles_h = (d.OH + p.patch_h - 1) / p.patch_h;

@@ -127,7 +127,7 @@ typedef struct __attribute__((aligned(64))) {
   cvmk_conv_desc d;
   int32_t block_k;    /* bytes of K per pipeline stage: 32, 64 or 128 */
   int32_t block_n;    /* output channels per tile: 32..256 */
-  int32_t a_im2col;   /* activations: 0 plain 2-D tiles, 1 im2col-mode tensor map, 2 spatial patches (4-D tiled map) */
+  int32_t a_im2col;   /* activations: 0 plain 2-D tiles, 1 im2col-mode tensor map, 2 spatial patches (4-D tiled map), 3 patches with the input halo staged once per channel block */
   int32_t stages;
   int32_t grid;
   int32_t smem_bytes;
@@ -136,7 +136,7 @@ typedef struct __attribute__((aligned(64))) {
   int32_t panels, panel_bytes;  /* staging: 128-column panels per tile, bytes per panel row */
   int32_t io_bufs;    /* staging buffers per epilogue group: 1 or 2 */
   int32_t ring_bytes; /* bytes of the operand ring in shared memory */
-  int32_t reserved[4];  /* [0..2] patch width / height / images (a_im2col = 2), [3] (tap, channel block) units per ring stage */
+  int32_t reserved[4];  /* [0..2] patch width / height / images (a_im2col = 2, 3), [3] (tap, channel block) units per ring stage */
 } cvmk_conv_plan;
 
 CVMK_API int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d);

@@ -133,6 +133,28 @@ def op_cases():
     add("conv_join_rsub_clip", join_case(15, True, False, ("cvm_clip", {"precision": 7}), other_first=True))
     add("conv_join_add_oc48", join_case(16, False, True, ("cvm_clip", {"precision": 8}), oc=48))
 
+    # 3x3 stride-1 filters over 64 / 128 channels: the M tile is an 8 x 16 pixel patch whose input
+    # halo is staged once per 64-channel block (partial patches at the right / bottom edges, one
+    # and two channel blocks, both output widths, padding 0 and 2, relu, residual join)
+    add("conv_halo_c64_56", lambda: conv_case(40, 2, 64, 56, 56, 64, 3, 1, 1, shift=9, relu=True))
+    add("conv_halo_c128_28", lambda: conv_case(41, 3, 128, 28, 28, 128, 3, 1, 1, shift=10))
+    add("conv_halo_c64_oc128_edges", lambda: conv_case(42, 2, 64, 37, 27, 128, 3, 1, 1, shift=9, relu=True))
+    add("conv_halo_c128_oc32_pad0", lambda: conv_case(43, 1, 128, 34, 42, 32, 3, 1, 0, shift=10, bias=False))
+    add("conv_halo_c64_pad2", lambda: conv_case(44, 2, 64, 30, 30, 64, 3, 1, 2, shift=9))
+
+    def halo_join():
+        rng = np.random.RandomState(45)
+        g = wl.GraphBuilder(45)
+        x = rnd(rng, (2, 64, 40, 48), 8)
+        d = g.var("data", x.shape, 8)
+        y = g.conv(d, 64, 3, 1, 1, relu=False, shift=9)
+        z = g.op("elemwise_add", [y, d], g.shape_of(y))
+        z = g.op("relu", [z], g.shape_of(z))
+        z = g.op("cvm_clip", [z], g.shape_of(z), {"precision": 8})
+        js, pb = g.finish(z)
+        return js, pb, x
+    add("conv_halo_join", halo_join)
+
     def dense_case(seed, m, k, units, bias=True):
         def f():
             g = wl.GraphBuilder(seed)
