@@ -339,9 +339,12 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
             STADD(4, tw);
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.OC);
-            const uint64_t da = desc_a0 + (uint64_t)buf * (uint64_t)p.KH * a_step;
-            for (int ky = 0; ky < p.KH; ++ky)
-              mma_i8(d_tmem, da + (uint64_t)ky * a_step, desc_b0 + (uint64_t)ky * b_step, idesc, ky > 0 ? 1u : 0u);
+            // one 32-bit add per operand and instruction (only the low descriptor word moves)
+            uint32_t al = (uint32_t)desc_a0 + (uint32_t)buf * (uint32_t)p.KH * (uint32_t)a_step;
+            uint32_t bl = (uint32_t)desc_b0;
+            const uint32_t a_hi = (uint32_t)(desc_a0 >> 32), b_hi = (uint32_t)(desc_b0 >> 32);
+            for (int ky = 0; ky < p.KH; ++ky, al += (uint32_t)a_step, bl += (uint32_t)b_step)
+              mma_i8_k<1>(d_tmem, al, a_hi, bl, b_hi, idesc, (uint32_t)ky);
             mma_commit(&a_empty[buf]);
             mma_commit(&acc_full[buf]);
             STADD(5, tw);

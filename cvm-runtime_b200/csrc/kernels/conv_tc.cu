@@ -159,11 +159,13 @@ __device__ __forceinline__ void fast_row(const ConvParams& p, uint32_t tbase, in
 #ifdef CVMK_CONV_TIMING
 __device__ long long g_conv_timing[148 * 16];
 #define TSTART(var) long long var = clock64()
+#define TSET(var) var = clock64()
 #define TADD(slot, var) do { const long long now__ = clock64(); tacc[slot] += now__ - var; var = now__; } while (0)
 #define TDECL long long tacc[16] = {0}
 #define TFLUSH(slot) do { if (blockIdx.x < 148) g_conv_timing[blockIdx.x * 16 + (slot)] = tacc[slot]; } while (0)
 #else
 #define TSTART(var) do {} while (0)
+#define TSET(var) do {} while (0)
 #define TADD(slot, var) do {} while (0)
 #define TDECL do {} while (0)
 #define TFLUSH(slot) do {} while (0)
@@ -387,7 +389,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       TADD(12, tk);
 #ifdef CVMK_CONV_TIMING
-      if (which == 0) { TFLUSH(0); TFLUSH(12); TFLUSH(13); TFLUSH(14); TFLUSH(15); }
+      if (which == 0) { TFLUSH(0); TFLUSH(12); }
 #endif
     }
   } else if (warp == 1) {
@@ -399,6 +401,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint64_t desc_halo0 = (desc_a0 & ~((uint64_t)0x3FFF << 32)) |
                                   ((uint64_t)(((uint32_t)(halo_w * p.block_k)) >> 4) << 32);
       const int nk = p.block_k / 32;
+      // descriptor halves and steps in 16-byte address units
+      const uint32_t a_lo0 = (uint32_t)desc_a0, a_hi = (uint32_t)(desc_a0 >> 32);
+      const uint32_t halo_hi = (uint32_t)(desc_halo0 >> 32);
+      const uint32_t stage_q = (uint32_t)stage_bytes >> 4, unit_q = (uint32_t)unit_bytes >> 4;
+      const uint32_t a_q = (uint32_t)a_bytes >> 4, b_q = (uint32_t)b_bytes >> 4;
+      const uint32_t halo_pad_q = (uint32_t)halo_pad >> 4, halo_row_q = (uint32_t)(halo_w * p.block_k) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -417,31 +425,38 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (!mbar_wait(&bar_full[stage], phase, &abort_flag, 3)) { live = false; break; }
           TADD(2, tw);
           tc_fence_after();
+          const uint32_t st = a_lo0 + stage_q * (uint32_t)stage;
           if (halo) {
-            const uint64_t st = (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
-            uint64_t db = desc_a0 + st + (uint64_t)((uint32_t)halo_pad >> 4);
-            for (int fy = 0; fy < p.kh; ++fy) {
-              uint64_t da = desc_halo0 + st + (uint64_t)((uint32_t)(fy * halo_w * p.block_k) >> 4);
-              for (int fx = 0; fx < p.kw; ++fx) {
-                mma_i8(d_tmem, da, db, idesc, (kb | fy | fx) ? 1u : 0u);
-                for (int j = 1; j < nk; ++j) mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
-                da += (uint64_t)((uint32_t)p.block_k >> 4);
-                db += (uint64_t)((uint32_t)b_bytes >> 4);
+            // 3 x 3 taps x two K slices of the 64-channel block, straight line
+            TSTART(ti);
+            uint32_t bl = st + halo_pad_q;
+#pragma unroll
+            for (int fy = 0; fy < 3; ++fy) {
+              uint32_t al = st + (uint32_t)fy * halo_row_q;
+#pragma unroll
+              for (int fx = 0; fx < 3; ++fx) {
+                mma_i8_k<2>(d_tmem, al, halo_hi, bl, a_hi, idesc, (uint32_t)(kb | fy | fx));
+                al += 4u;   // one pixel of 64 channels
+                bl += b_q;
               }
             }
+            TADD(13, ti);
             mma_commit(&bar_empty[stage]);
+            TADD(14, ti);
+            TSET(tw);
             if (++stage == p.stages) { stage = 0; phase ^= 1; }
             continue;
           }
-          // descriptors of this stage: the start-address field counts 16-byte units
-          uint64_t da = desc_a0 + (uint64_t)((uint32_t)(stage * stage_bytes) >> 4);
           const int in_stage = min(p.units, num_units - unit);
-          for (int u = 0; u < in_stage; ++u, ++unit) {
-            const uint64_t db = da + (uint64_t)((uint32_t)a_bytes >> 4);
-            mma_i8(d_tmem, da, db, idesc, unit > 0 ? 1u : 0u);
-            for (int j = 1; j < nk; ++j) mma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, 1u);
-            da += (uint64_t)((uint32_t)unit_bytes >> 4);
+          uint32_t al = st;
+          if (nk == 4) {
+            for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<4>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+          } else if (nk == 2) {
+            for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<2>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+          } else {
+            for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<1>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
           }
+          unit += in_stage;
           mma_commit(&bar_empty[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -454,6 +469,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       TFLUSH(1);
       TFLUSH(2);
       TFLUSH(3);
+      TFLUSH(13);
+      TFLUSH(14);
     }
   } else if (warp < IO_WARP) {
     // ------------------------------------------------------------------ epilogue warps

@@ -119,6 +119,40 @@ __device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// NK back-to-back instructions over K slices 32 bytes apart (descriptor address units of 16
+// bytes: +2 each).  The descriptors come as 32-bit halves: only the low word (start address)
+// changes from instruction to instruction, so the issuing thread spends one 32-bit add per
+// operand and instruction.  That matters: the issuing warp shares its scheduler with epilogue
+// warps, and every instruction of its loop waits its turn.
+template <int NK>
+__device__ __forceinline__ void mma_i8_k(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                         uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+#pragma unroll
+  for (int j = 1; j < NK; ++j) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 da, db;\n"
+        "setp.eq.b32 p, 0, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo + 2u * (uint32_t)j), "r"(a_hi), "r"(b_lo + 2u * (uint32_t)j), "r"(b_hi), "r"(idesc)
+        : "memory");
+  }
+}
 // Arrive on `bar` once every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
