@@ -106,6 +106,28 @@ def test_random_bottlenecks(gpu_run, oracle, wl):
         assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x)), (i, cin, mid, out, stride, batch, h, w)
 
 
+def test_random_halo_convolutions(gpu_run, oracle, wl):
+    """3x3 stride-1 filters over 64 / 128 channels on random shapes: the halo form of the patch
+    tile (8 x 16 pixel patches, partial at the right / bottom edges, one or two 64-channel blocks,
+    32..128 output channels, padding 0..2), bare, with relu, and fused with a residual join."""
+    rng = np.random.RandomState(91)
+    for i in range(12):
+        c = int(rng.choice([64, 128]))
+        oc = int(rng.choice([32, 64, 96, 128]))
+        pad = int(rng.choice([0, 1, 1, 2]))
+        batch = int(rng.randint(1, 4))
+        h, w = int(rng.randint(9, 61)), int(rng.randint(9, 61))
+        g = wl.GraphBuilder(500 + i)
+        x = cases.rnd(rng, (batch, c, h, w), 8)
+        d = g.var("data", x.shape, 8)
+        y = g.conv(d, oc, 3, 1, pad, relu=bool(rng.randint(2)), shift=int(rng.randint(7, 12)), bias=bool(rng.randint(3)))
+        if pad == 1 and oc == c and rng.rand() < 0.7:
+            y = g.op("elemwise_add", [y, d], g.shape_of(y))
+            y = g.op("cvm_clip", [y], g.shape_of(y), {"precision": 8})
+        js, pb = g.finish(y)
+        assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x)), (i, c, oc, pad, batch, h, w)
+
+
 def test_input_is_clamped_to_its_precision(gpu_run, oracle, wl):
     """graph_runtime.cc:379-386: -128 enters the network as -127."""
     js, pb, x = wl.conv_chain(batch=1, channels=32, size=8)
