@@ -60,7 +60,8 @@ struct ConvParams {
   int block_k, block_n, stages;
   int units;            // (filter tap, channel block) pairs loaded and multiplied per ring stage
   int a_mode;           // activations: 0 plain 2-D tiles (1x1, dense), 1 im2col-mode TMA, 2 spatial patches,
-                        // 3 spatial patches whose input halo is staged once per channel block
+                        // 3 spatial patches whose input halo is staged once per channel block,
+                        // 4 the same with the whole weight matrix resident in shared memory
   int patch_w, patch_h, patch_n;  // a_mode 2, 3: an M tile is patch_w x patch_h output pixels of patch_n images
   int tiles_w, tiles_h;           // a_mode 2, 3: patches per image row / column
   int num_m_tiles, num_n_tiles;
@@ -201,6 +202,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ uint64_t bar_acc_empty[2];
   __shared__ uint64_t bar_res[2][2];     // [group][buffer]: staging buffer free / operand tile landed in it
   __shared__ uint64_t bar_staged[2][2];  // [group][buffer]: the group has written its tile into the buffer
+  __shared__ uint64_t bar_weights;       // a_mode 4: the resident weight matrix has landed
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int abort_flag;
   __shared__ __align__(16) int32_t bias_s[MAX_BIAS];
@@ -218,12 +220,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // Every filter tap multiplies a window of that halo: the descriptor starts (fy * halo_w + fx)
   // rows in and steps halo_w rows per 8-pixel group (the swizzle is a function of the shared-memory
   // address, so any 16-byte aligned start inside the swizzled halo reads consistently).
-  const bool halo = p.a_mode == 3;
+  // a_mode 4 is the halo mode with the whole weight matrix resident in shared memory (one channel
+  // block, one N tile): the weights are loaded once per CTA in front of the ring and a stage is
+  // the halo alone.
+  const bool halo = p.a_mode >= 3;
+  const bool w_resident = p.a_mode == 4;
   const int halo_w = p.patch_w + p.kw - 1;
   const int halo_bytes = halo_w * (p.patch_h + p.kh - 1) * p.block_k;
   const int halo_pad = (halo_bytes + 1023) & ~1023;
   const int taps = p.kh * p.kw;
-  const int stage_bytes = halo ? halo_pad + taps * b_bytes : p.units * unit_bytes;
+  const int resident_bytes = w_resident ? taps * b_bytes : 0;
+  uint8_t* const ring = smem + resident_bytes;
+  const int stage_bytes = w_resident ? halo_pad : (halo ? halo_pad + taps * b_bytes : p.units * unit_bytes);
   const int num_kb = halo ? p.c / p.block_k : (num_units + p.units - 1) / p.units;  // ring stages consumed per tile
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const bool bias_in_smem = (p.bias != nullptr || p.fast_mode) && p.oc <= MAX_BIAS;
@@ -241,6 +249,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         mbar_init(&bar_staged[a][b], NUM_EPI_WARPS / 2);
       }
     }
+    mbar_init(&bar_weights, 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -279,8 +288,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // The loop below runs on one thread, so its own instruction latency bounds the rate of
       // loads: the filter taps are walked with nested counters (no divisions), and everything
       // that is constant for a tile is computed once per tile.
-      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t smem_base = smem_u32(ring);
       const uint32_t full0 = smem_u32(&bar_full[0]);
+      if (w_resident && which == 0) {  // the weight matrix, once (every tile of this CTA has n0 = 0)
+        const uint32_t wb = smem_u32(&bar_weights);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wb), "r"((uint32_t)resident_bytes) : "memory");
+        uint32_t dst = smem_u32(smem);
+        int kcol = 0;
+        for (int t = 0; t < taps; ++t) {
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+              " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(wb),
+              "r"(kcol), "r"(0)
+              : "memory");
+          dst += (uint32_t)b_bytes;
+          kcol += p.c;
+        }
+      }
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
         const TileOrigin to = tile_origin(p, tile);
         const int m0 = to.m0;
@@ -304,7 +328,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t sa = smem_base + (uint32_t)(stage * stage_bytes);
             const uint32_t bar = full0 + 8u * (uint32_t)stage;
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                         "r"((uint32_t)(halo_bytes + taps * b_bytes)) : "memory");
+                         "r"((uint32_t)(halo_bytes + (w_resident ? 0 : taps * b_bytes))) : "memory");
             const int cc = cb * p.block_k;
             asm volatile(
                 "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
@@ -313,7 +337,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 : "memory");
             uint32_t sb = sa + (uint32_t)halo_pad;
             int kcol = cc;
-            for (int t = 0; t < taps; ++t) {
+            for (int t = 0; t < (w_resident ? 0 : taps); ++t) {
               asm volatile(
                   "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                   " [%0], [%1, {%3, %4}], [%2];" ::"r"(sb), "l"(reinterpret_cast<uint64_t>(&tmap_b)),
@@ -396,7 +420,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_i8(p.block_n);
-      const uint64_t desc_a0 = umma_desc(smem_u32(smem), p.block_k);
+      const uint64_t desc_a0 = umma_desc(smem_u32(ring), p.block_k);
+      const uint32_t w_lo0 = (uint32_t)umma_desc(smem_u32(smem), p.block_k);  // resident weights (a_mode 4)
       // halo windows: 8-pixel groups are one halo row (halo_w pixels) apart
       const uint64_t desc_halo0 = (desc_a0 & ~((uint64_t)0x3FFF << 32)) |
                                   ((uint64_t)(((uint32_t)(halo_w * p.block_k)) >> 4) << 32);
@@ -414,6 +439,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool live = true;
       TDECL;
       TSTART(tl);
+      if (w_resident && blockIdx.x < num_tiles && !mbar_wait(&bar_weights, 0u, &abort_flag, 7)) live = false;
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
         TSTART(tw);
         if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1, &abort_flag, 2)) { live = false; break; }
@@ -429,7 +455,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (halo) {
             // 3 x 3 taps x two K slices of the 64-channel block, straight line
             TSTART(ti);
-            uint32_t bl = st + halo_pad_q;
+            uint32_t bl = w_resident ? w_lo0 : st + halo_pad_q;
 #pragma unroll
             for (int fy = 0; fy < 3; ++fy) {
               uint32_t al = st + (uint32_t)fy * halo_row_q;
@@ -851,9 +877,17 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   const int64_t k_all = (int64_t)d->KH * d->KW * d->C;
   const int budget = SMEM_DYNAMIC_MAX - 1024;
   plan->io_bufs = 1;
-  const int halo_stage = halo ? (((10 * 18 * bk) + 1023) & ~1023) + d->KH * d->KW * bn * bk : 0;
+  // Weights resident in shared memory: one 64-channel block and one N tile, i.e. every tile of the
+  // launch multiplies the same 9 * bn * 64 bytes.  A ring stage is then the 12 KB halo alone.
+  const int halo_pad = ((10 * 18 * bk) + 1023) & ~1023;
+  int resident = 0;
+  if (halo && d->C == 64 && d->OC <= bn && !getenv("CVM_B200_NO_RESIDENT_WEIGHTS")) {
+    resident = d->KH * d->KW * bn * bk;
+    plan->a_im2col = 4;
+  }
+  const int halo_stage = halo ? (resident ? halo_pad : halo_pad + d->KH * d->KW * bn * bk) : 0;
   if (halo) {
-    if (plan->tma_out && (budget - 4 * group_bytes) / halo_stage >= 3) plan->io_bufs = 2;
+    if (plan->tma_out && (budget - resident - 4 * group_bytes) / halo_stage >= 3) plan->io_bufs = 2;
   } else if (plan->tma_out && !getenv("CVM_B200_SINGLE_STAGING")) {
     auto ring_depth = [&](int k) { return (budget - 4 * group_bytes) / ((BLOCK_M + bn) * k); };
     if (ring_depth(bk) >= 3) plan->io_bufs = 2;
@@ -875,11 +909,11 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   if (halo) units = d->KH * d->KW;
   plan->reserved[3] = units;
   const int stage_bytes = halo ? halo_stage : units * unit_bytes;
-  int stages = (budget - io_bytes) / stage_bytes;
+  int stages = (budget - io_bytes - resident) / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) { set_error("conv2d_tc_prepare: tile does not fit shared memory"); return CVMK_ERR_UNSUPPORTED; }
   plan->stages = stages;
-  plan->ring_bytes = stages * stage_bytes;
+  plan->ring_bytes = resident + stages * stage_bytes;  // resident weights (a_im2col 4) sit in front of the ring
   plan->smem_bytes = plan->ring_bytes + io_bytes + 1024;
 
   const int64_t m_total = (int64_t)d->N * d->OH * d->OW;
@@ -887,7 +921,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   CUtensorMap* ta = reinterpret_cast<CUtensorMap*>(plan->tmap_a);
   CUtensorMap* tb = reinterpret_cast<CUtensorMap*>(plan->tmap_b);
   CUresult r;
-  if (plan->a_im2col == 3) {
+  if (plan->a_im2col >= 3) {
     r = encode_nhwc(enc_tiled, ta, d->x, d->N, d->H, d->W, d->C, bk, patch_w + d->KW - 1, patch_h + d->KH - 1, 1,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
   } else if (plan->a_im2col == 2) {

@@ -127,7 +127,7 @@ typedef struct __attribute__((aligned(64))) {
   cvmk_conv_desc d;
   int32_t block_k;    /* bytes of K per pipeline stage: 32, 64 or 128 */
   int32_t block_n;    /* output channels per tile: 32..256 */
-  int32_t a_im2col;   /* activations: 0 plain 2-D tiles, 1 im2col-mode tensor map, 2 spatial patches (4-D tiled map), 3 patches with the input halo staged once per channel block */
+  int32_t a_im2col;   /* activations: 0 plain 2-D tiles, 1 im2col-mode tensor map, 2 spatial patches (4-D tiled map), 3 patches with the input halo staged once per channel block, 4 the same with the weights resident in shared memory */
   int32_t stages;
   int32_t grid;
   int32_t smem_bytes;
