@@ -256,15 +256,29 @@ struct PoolParams {
   int64_t total;  // output vectors
   int cvec;       // vectors per pixel
 };
-template <int DT>
+// IDX32: the output has fewer than 2^31 vectors, so the index split runs on 32-bit divisions (the
+// 64-bit ones cost more instructions than the nine taps of a 3x3 window).
+template <int DT, bool IDX32>
 __global__ void __launch_bounds__(256) pool_vec_kernel(const __grid_constant__ PoolParams p) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
-    const int cv = (int)(i % p.cvec);
-    int64_t pix = i / p.cvec;
-    const int ox = (int)(pix % p.OW); pix /= p.OW;
-    const int oy = (int)(pix % p.OH);
-    const int n = (int)(pix / p.OH);
+    int cv, ox, oy, n;
+    if (IDX32) {
+      const uint32_t u = (uint32_t)i;
+      uint32_t pix = u / (uint32_t)p.cvec;
+      cv = (int)(u - pix * (uint32_t)p.cvec);
+      const uint32_t r1 = pix / (uint32_t)p.OW;
+      ox = (int)(pix - r1 * (uint32_t)p.OW);
+      const uint32_t r2 = r1 / (uint32_t)p.OH;
+      oy = (int)(r1 - r2 * (uint32_t)p.OH);
+      n = (int)r2;
+    } else {
+      cv = (int)(i % p.cvec);
+      int64_t pix = i / p.cvec;
+      ox = (int)(pix % p.OW); pix /= p.OW;
+      oy = (int)(pix % p.OH);
+      n = (int)(pix / p.OH);
+    }
     // Taps outside the image are read from a clamped (valid) address and replaced by the
     // identity of max, so the loads of a window are independent of each other.  Signed bytes are
     // compared as s16x2: even and odd bytes are moved into the high byte of each half.
@@ -495,8 +509,14 @@ extern "C" int cvmk_max_pool2d(const cvmk_pool_desc* d, cvmk_stream_t stream) {
   if (d->C % vec == 0 && aligned16(d->x) && aligned16(d->y)) {
     p.cvec = d->C / vec;
     p.total = (int64_t)d->N * d->OH * d->OW * p.cvec;
-    if (d->dtype == CVMK_I8) pool_vec_kernel<CVMK_I8><<<grid_for(p.total, threads), threads, 0, s>>>(p);
-    else pool_vec_kernel<CVMK_I32><<<grid_for(p.total, threads), threads, 0, s>>>(p);
+    const bool idx32 = p.total < ((int64_t)1 << 31);
+    if (d->dtype == CVMK_I8) {
+      if (idx32) pool_vec_kernel<CVMK_I8, true><<<grid_for(p.total, threads), threads, 0, s>>>(p);
+      else pool_vec_kernel<CVMK_I8, false><<<grid_for(p.total, threads), threads, 0, s>>>(p);
+    } else {
+      if (idx32) pool_vec_kernel<CVMK_I32, true><<<grid_for(p.total, threads), threads, 0, s>>>(p);
+      else pool_vec_kernel<CVMK_I32, false><<<grid_for(p.total, threads), threads, 0, s>>>(p);
+    }
   } else {
     p.cvec = 0;
     p.total = (int64_t)d->N * d->OH * d->OW * d->C;
