@@ -118,38 +118,52 @@ __device__ __forceinline__ void store_vals(const ConvParams& p, size_t lin, cons
 // biased (the rounding addend is part of the staged bias), requantised and written to the
 // swizzled staging panels, in place of the tensor operand when there is one.
 template <int RELU1, int KIND>
+__device__ __forceinline__ void fast_chunk(const ConvParams& p, const FastQ& fq, int32_t (&v)[32], int ci,
+                                           const int32_t* bias_row, uint8_t* io_base, int panel_size,
+                                           uint32_t row_off, uint32_t sw) {
+  // (acc + bias + rounding addend) << (16 - shift) as one multiply-add per element: bits
+  // [16, 32) of the result are bits [shift, shift + 16) of the biased sum, i.e. the low half of
+  // its arithmetic right shift, which is all the packed arithmetic below needs.
+  const int4* bp = reinterpret_cast<const int4*>(bias_row + ci * 32);
+  const int mul = p.f_mul;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int4 b4 = bp[j];
+    v[4 * j] = v[4 * j] * mul + b4.x;
+    v[4 * j + 1] = v[4 * j + 1] * mul + b4.y;
+    v[4 * j + 2] = v[4 * j + 2] * mul + b4.z;
+    v[4 * j + 3] = v[4 * j + 3] * mul + b4.w;
+  }
+  const int c0 = ci * 32;
+  uint8_t* pb = io_base + (size_t)(c0 >> 7) * panel_size + row_off;
+  const uint32_t j0 = (uint32_t)(c0 & 127) >> 4;
+  uint4* q0 = reinterpret_cast<uint4*>(pb + ((j0 ^ sw) << 4));
+  uint4* q1 = reinterpret_cast<uint4*>(pb + (((j0 + 1) ^ sw) << 4));
+  uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
+  if (KIND != 0) { r0 = *q0; r1 = *q1; }
+  uint4 a, b;
+  fast_requant<RELU1, KIND>(fq, v, r0, r1, &a, &b);
+  *q0 = a;
+  *q1 = b;
+}
+
+template <int RELU1, int KIND>
 __device__ __forceinline__ void fast_row(const ConvParams& p, uint32_t tbase, int chunks, const int32_t* bias_row,
                                          uint8_t* io_base, int panel_size, int row_in_tile, int pw) {
   const FastQ fq = {p.f_lo1, p.f_hi1, p.f_lo2, p.f_hi2};
   const uint32_t row_off = (uint32_t)row_in_tile * (uint32_t)pw;
   const uint32_t sw = (row_off >> 7) & (((uint32_t)pw - 1u) >> 4);  // swizzle key of this row, as in panel_offset()
-  for (int ci = 0; ci < chunks; ++ci) {
+  int ci = 0;
+  for (; ci + 2 <= chunks; ci += 2) {  // two chunks per TMEM round trip
+    int32_t v0[32], v1[32];
+    tmem_ld64(tbase + (uint32_t)(ci * 32), v0, v1);
+    fast_chunk<RELU1, KIND>(p, fq, v0, ci, bias_row, io_base, panel_size, row_off, sw);
+    fast_chunk<RELU1, KIND>(p, fq, v1, ci + 1, bias_row, io_base, panel_size, row_off, sw);
+  }
+  if (ci < chunks) {
     int32_t v[32];
     tmem_ld32(tbase + (uint32_t)(ci * 32), v);
-    // (acc + bias + rounding addend) << (16 - shift) as one multiply-add per element: bits
-    // [16, 32) of the result are bits [shift, shift + 16) of the biased sum, i.e. the low half of
-    // its arithmetic right shift, which is all the packed arithmetic below needs.
-    const int4* bp = reinterpret_cast<const int4*>(bias_row + ci * 32);
-    const int mul = p.f_mul;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int4 b4 = bp[j];
-      v[4 * j] = v[4 * j] * mul + b4.x;
-      v[4 * j + 1] = v[4 * j + 1] * mul + b4.y;
-      v[4 * j + 2] = v[4 * j + 2] * mul + b4.z;
-      v[4 * j + 3] = v[4 * j + 3] * mul + b4.w;
-    }
-    const int c0 = ci * 32;
-    uint8_t* pb = io_base + (size_t)(c0 >> 7) * panel_size + row_off;
-    const uint32_t j0 = (uint32_t)(c0 & 127) >> 4;
-    uint4* q0 = reinterpret_cast<uint4*>(pb + ((j0 ^ sw) << 4));
-    uint4* q1 = reinterpret_cast<uint4*>(pb + (((j0 + 1) ^ sw) << 4));
-    uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
-    if (KIND != 0) { r0 = *q0; r1 = *q1; }
-    uint4 a, b;
-    fast_requant<RELU1, KIND>(fq, v, r0, r1, &a, &b);
-    *q0 = a;
-    *q1 = b;
+    fast_chunk<RELU1, KIND>(p, fq, v, ci, bias_row, io_base, panel_size, row_off, sw);
   }
 }
 
