@@ -73,7 +73,11 @@ struct Lowering {
   Lowering(Executor& e, const Graph& gr) : ex(e), g(gr) {}
 
   void add_step(const std::string& label, std::function<int(cudaStream_t)> fn) {
-    ex.steps_.push_back({label, std::move(fn)});
+    ex.steps_.push_back({label, std::move(fn), {}});
+  }
+  // Batch chunks for upload / compute overlap: four when the batch divides, else none.
+  static int batch_chunks(int64_t n) {
+    return (n % 4 == 0 && n >= 8 && !getenv("CVM_B200_NO_UPLOAD_OVERLAP")) ? 4 : 1;
   }
 
   // ------------------------------------------------------------------ analysis
@@ -453,10 +457,6 @@ struct Lowering {
           KERNEL_OK(cvmk_conv2d_stem_prepare(&cd, ex.stem_plans_.back().get()));
           plans.push_back(ex.stem_plans_.back().get());
         }
-        if (chunks > 1) {
-          ex.stem_chunks_ = plans;
-          ex.stem_chunk_bytes_ = (size_t)per * C * H * W;
-        }
         add_step(label + "[stem]", [plans](cudaStream_t s) {
           for (auto* pl : plans) {
             const int rc = cvmk_conv2d_stem_launch(pl, s);
@@ -464,6 +464,11 @@ struct Lowering {
           }
           return (int)CVMK_OK;
         });
+        if (chunks > 1) {
+          ex.chunk_bytes_ = (size_t)per * C * H * W;
+          for (auto* pl : plans)
+            ex.steps_.back().chunk.push_back([pl](cudaStream_t s) { return cvmk_conv2d_stem_launch(pl, s); });
+        }
         return;
       }
     }
@@ -516,6 +521,29 @@ struct Lowering {
       cvmk_conv_plan* plan = ex.plans_.back().get();
       KERNEL_OK(cvmk_conv2d_tc_prepare(&d, plan));
       add_step(label + "[tc]", [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
+      // Quarter-batch plans (every operand is batch-major, so a chunk is a contiguous slice).
+      const int chunks = batch_chunks(d.N);
+      if (chunks > 1 && xin.nhwc && out.nhwc) {
+        const int per = d.N / chunks;
+        const size_t out_elems = (size_t)per * d.OH * d.OW * d.OC;
+        for (int c = 0; c < chunks; ++c) {
+          cvmk_conv_desc cd = d;
+          cd.N = per;
+          cd.x = d.x + (size_t)c * per * d.H * d.W * d.C;
+          cd.y = (char*)d.y + (size_t)c * out_elems * d.y_dtype;
+          for (int i = 0; i < cd.ep.n; ++i) {
+            cvmk_ep_step& st = cd.ep.s[i];
+            if ((st.op == CVMK_EP_ADD_T || st.op == CVMK_EP_SUB_T || st.op == CVMK_EP_RSUB_T) && st.ptr)
+              st.ptr = (const char*)st.ptr + (size_t)c * out_elems * st.ptr_dtype;
+          }
+          void* cmem = nullptr;
+          CHECK(posix_memalign(&cmem, 64, sizeof(cvmk_conv_plan)) == 0);
+          ex.plans_.emplace_back((cvmk_conv_plan*)cmem, plan_deleter);
+          cvmk_conv_plan* cp = ex.plans_.back().get();
+          KERNEL_OK(cvmk_conv2d_tc_prepare(&cd, cp));
+          ex.steps_.back().chunk.push_back([cp](cudaStream_t s) { return cvmk_conv2d_tc_launch(cp, s); });
+        }
+      }
     } else {
       DevBuf& xin = materialize(ex_);
       cvmk_conv_direct_desc d;
@@ -615,6 +643,17 @@ struct Lowering {
     d.stride_h = (int)n.attrs.t("strides")[0]; d.stride_w = (int)n.attrs.t("strides")[1];
     d.pad_h = (int)pad[0]; d.pad_w = (int)(pad.size() == 2 ? pad[1] : pad[0]);
     add_step("max_pool2d:" + n.name(), [d](cudaStream_t s) { return cvmk_max_pool2d(&d, s); });
+    const int chunks = batch_chunks(d.N);
+    if (chunks > 1 && x.nhwc && y.nhwc) {
+      const int per = d.N / chunks;
+      for (int c = 0; c < chunks; ++c) {
+        cvmk_pool_desc cd = d;
+        cd.N = per;
+        cd.x = (const char*)d.x + (size_t)c * per * d.H * d.W * d.C * d.dtype;
+        cd.y = (char*)d.y + (size_t)c * per * d.OH * d.OW * d.C * d.dtype;
+        ex.steps_.back().chunk.push_back([cd](cudaStream_t s) { return cvmk_max_pool2d(&cd, s); });
+      }
+    }
   }
 
   void lower_upsampling(uint32_t nid) {
@@ -1093,12 +1132,19 @@ struct Lowering {
       for (const auto& pr : order)
         for (auto& s : per_root[pr.second]) ex.steps_.push_back(std::move(s));
     }
-    // upload / stem overlap only when the stem is the very first step of the inference
+    // Upload / compute overlap: when the inference starts with the stem, the leading run of steps
+    // that can be cut along the batch (about as much work as the upload takes) is launched per
+    // chunk, outside the graph.
     {
       const std::string tag = "[stem]";
-      const bool first = !ex.steps_.empty() && ex.steps_[0].label.size() >= tag.size() &&
+      const bool first = !ex.steps_.empty() && ex.steps_[0].chunk.size() == 4 && ex.steps_[0].label.size() >= tag.size() &&
                          ex.steps_[0].label.compare(ex.steps_[0].label.size() - tag.size(), tag.size(), tag) == 0;
-      if (!first) ex.stem_chunks_.clear();
+      size_t cap = 6;   // ResNet-50: stem, pooling and the first bottleneck block take about as long as the upload
+      if (const char* e = getenv("CVM_B200_PREFIX_STEPS")) cap = (size_t)atoi(e);
+      ex.prefix_steps_ = 0;
+      if (first)
+        while (ex.prefix_steps_ < ex.steps_.size() && ex.prefix_steps_ < cap && ex.steps_[ex.prefix_steps_].chunk.size() == 4)
+          ++ex.prefix_steps_;
     }
     // heads: row-major staging + pinned host mirrors
     for (const auto& e : g.outputs) {
@@ -1135,14 +1181,14 @@ Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
   Enqueue(stream_);
   CUDA_OK(cudaStreamSynchronize(stream_));
   if (use_graph_) {
-    if (!stem_chunks_.empty()) {
+    if (prefix_steps_ > 0) {
       CUDA_OK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
-      chunk_events_.resize(stem_chunks_.size());
+      chunk_events_.resize(4);
       for (auto& e : chunk_events_) CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     }
     cudaGraph_t graph = nullptr;
     CUDA_OK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
-    Enqueue(stream_, stem_chunks_.empty() ? 0 : 1);  // the chunked stem is launched outside the graph
+    Enqueue(stream_, prefix_steps_);  // the chunked prefix is launched outside the graph
     CUDA_OK(cudaStreamEndCapture(stream_, &graph));
     CUDA_OK(cudaGraphInstantiate(&graph_exec_, graph, 0));
     CUDA_OK(cudaGraphDestroy(graph));
@@ -1198,13 +1244,16 @@ void Executor::Enqueue(cudaStream_t s, size_t first) {
 void Executor::Run(const void* input, size_t input_bytes) {
   CHECK(input_bytes == in_bytes_) << "input size " << input_bytes << " vs. " << in_bytes_;
   CUDA_OK(cudaSetDevice(device_));
-  if (graph_exec_ && !stem_chunks_.empty()) {
-    // chunk c of the batch is uploaded on the copy stream while the stem runs on chunk c - 1
-    for (size_t c = 0; c < stem_chunks_.size(); ++c) {
-      UploadRange(input, c * stem_chunk_bytes_, stem_chunk_bytes_, copy_stream_);
+  if (graph_exec_ && prefix_steps_ > 0) {
+    // chunk c of the batch is uploaded on the copy stream while the leading steps run on chunk c - 1
+    for (size_t c = 0; c < 4; ++c) {
+      UploadRange(input, c * chunk_bytes_, chunk_bytes_, copy_stream_);
       CUDA_OK(cudaEventRecord(chunk_events_[c], copy_stream_));
       CUDA_OK(cudaStreamWaitEvent(stream_, chunk_events_[c], 0));
-      KERNEL_OK(cvmk_conv2d_stem_launch(stem_chunks_[c], stream_));
+      for (size_t k = 0; k < prefix_steps_; ++k) {
+        const int rc = steps_[k].chunk[c](stream_);
+        CHECK(rc == CVMK_OK) << "step " << steps_[k].label << " (chunk) failed (" << rc << "): " << cvmk_last_error();
+      }
     }
     CUDA_OK(cudaGraphLaunch(graph_exec_, stream_));
   } else {

@@ -35,6 +35,9 @@ struct DevBuf {
 struct Step {
   std::string label;
   std::function<int(cudaStream_t)> launch;
+  // The same operator on one quarter of the batch each (empty when the step cannot be cut along
+  // the batch): the leading steps of an inference run chunk by chunk while later chunks upload.
+  std::vector<std::function<int(cudaStream_t)>> chunk;
 };
 
 struct HeadOut {
@@ -67,6 +70,8 @@ class Executor {
   int device_;
   cudaStream_t stream_ = nullptr;
   std::vector<Step> steps_;
+  size_t prefix_steps_ = 0;   // leading steps launched per batch chunk, outside the graph
+  size_t chunk_bytes_ = 0;    // input bytes of one batch chunk
   std::vector<HeadOut> heads_;
   std::vector<void*> allocs_;
   std::vector<void*> pinned_;
@@ -83,8 +88,6 @@ class Executor {
   cudaGraphExec_t kernels_exec_ = nullptr;
   bool use_graph_ = true;
   // upload / stem overlap: per-chunk stem plans, the copy stream and one event per chunk
-  std::vector<cvmk_stem_conv_plan*> stem_chunks_;
-  size_t stem_chunk_bytes_ = 0;
   cudaStream_t copy_stream_ = nullptr;
   std::vector<cudaEvent_t> chunk_events_;
 

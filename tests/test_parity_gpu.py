@@ -289,6 +289,15 @@ def test_resnet50_batch256_batch_independence(rt, gpu_run, oracle, wl):
         rt.CVMAPIFreeModel(net)
 
 
+def test_chunked_prefix_matches_oracle(gpu_run, oracle, wl):
+    """Batch 8 divides into four chunks: the stem, the pooling and the first bottleneck blocks run
+    chunk by chunk (upload / compute overlap) before the rest of the network runs on the batch."""
+    js, pb, x = wl.resnet50(batch=8, size=64)
+    assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x))
+    js, pb, x = wl.vgg19(batch=8, size=32, fc=64)
+    assert np.array_equal(gpu_run(js, pb, x), oracle.run_model(js, pb, x))
+
+
 @pytest.mark.parametrize("builder,batch,small", [("mobilenet_v1", 64, 2), ("vgg19", 16, 1)])
 def test_large_batch_matches_small_batches(builder, batch, small, gpu_run, oracle, wl):
     js, pb, x = getattr(wl, builder)(batch=batch)
