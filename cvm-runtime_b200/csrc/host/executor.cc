@@ -75,9 +75,19 @@ struct Lowering {
   void add_step(const std::string& label, std::function<int(cudaStream_t)> fn) {
     ex.steps_.push_back({label, std::move(fn), {}});
   }
-  // Batch chunks for upload / compute overlap: four when the batch divides, else none.
+  // Batch chunks for upload / compute overlap: four (CVM_B200_UPLOAD_CHUNKS) when the batch
+  // divides, else none.
+  static int upload_chunks() {
+    static const int k = [] {
+      const char* e = getenv("CVM_B200_UPLOAD_CHUNKS");
+      const int v = e ? atoi(e) : 4;
+      return v >= 2 && v <= 16 ? v : 4;
+    }();
+    return k;
+  }
   static int batch_chunks(int64_t n) {
-    return (n % 4 == 0 && n >= 8 && !getenv("CVM_B200_NO_UPLOAD_OVERLAP")) ? 4 : 1;
+    const int k = upload_chunks();
+    return (n % k == 0 && n >= 2 * k && !getenv("CVM_B200_NO_UPLOAD_OVERLAP")) ? k : 1;
   }
 
   // ------------------------------------------------------------------ analysis
@@ -442,8 +452,7 @@ struct Lowering {
         sd.w = wsdev;
         // The batch is cut into chunks with a plan each, so that an inference can run the stem on
         // the first images while the later ones are still being uploaded.
-        const int chunks = (N % 4 == 0 && N >= 8 && uses[ex_] == 1 && !is_head[ex_] &&
-                            !getenv("CVM_B200_NO_UPLOAD_OVERLAP")) ? 4 : 1;
+        const int chunks = (uses[ex_] == 1 && !is_head[ex_]) ? batch_chunks(N) : 1;
         const int per = N / chunks;
         std::vector<cvmk_stem_conv_plan*> plans;
         for (int c = 0; c < chunks; ++c) {
@@ -1137,13 +1146,13 @@ struct Lowering {
     // chunk, outside the graph.
     {
       const std::string tag = "[stem]";
-      const bool first = !ex.steps_.empty() && ex.steps_[0].chunk.size() == 4 && ex.steps_[0].label.size() >= tag.size() &&
+      const bool first = !ex.steps_.empty() && ex.steps_[0].chunk.size() > 1 && ex.steps_[0].label.size() >= tag.size() &&
                          ex.steps_[0].label.compare(ex.steps_[0].label.size() - tag.size(), tag.size(), tag) == 0;
       size_t cap = 6;   // ResNet-50: stem, pooling and the first bottleneck block take about as long as the upload
       if (const char* e = getenv("CVM_B200_PREFIX_STEPS")) cap = (size_t)atoi(e);
       ex.prefix_steps_ = 0;
       if (first)
-        while (ex.prefix_steps_ < ex.steps_.size() && ex.prefix_steps_ < cap && ex.steps_[ex.prefix_steps_].chunk.size() == 4)
+        while (ex.prefix_steps_ < ex.steps_.size() && ex.prefix_steps_ < cap && ex.steps_[ex.prefix_steps_].chunk.size() == ex.steps_[0].chunk.size())
           ++ex.prefix_steps_;
     }
     // heads: row-major staging + pinned host mirrors
@@ -1183,7 +1192,7 @@ Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
   if (use_graph_) {
     if (prefix_steps_ > 0) {
       CUDA_OK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
-      chunk_events_.resize(4);
+      chunk_events_.resize(steps_[0].chunk.size());
       for (auto& e : chunk_events_) CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     }
     cudaGraph_t graph = nullptr;
@@ -1246,7 +1255,7 @@ void Executor::Run(const void* input, size_t input_bytes) {
   CUDA_OK(cudaSetDevice(device_));
   if (graph_exec_ && prefix_steps_ > 0) {
     // chunk c of the batch is uploaded on the copy stream while the leading steps run on chunk c - 1
-    for (size_t c = 0; c < 4; ++c) {
+    for (size_t c = 0; c < steps_[0].chunk.size(); ++c) {
       UploadRange(input, c * chunk_bytes_, chunk_bytes_, copy_stream_);
       CUDA_OK(cudaEventRecord(chunk_events_[c], copy_stream_));
       CUDA_OK(cudaStreamWaitEvent(stream_, chunk_events_[c], 0));
