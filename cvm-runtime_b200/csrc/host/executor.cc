@@ -179,6 +179,21 @@ struct Lowering {
       });
       return;
     }
+    // NCHW <-> NHWC of one element type: a batched matrix transpose through shared memory
+    if (src.nhwc != dst.nhwc && src.shape == dst.shape && src.shape.size() == 4 && src.dtype == dst.dtype &&
+        (!ep || ep->n == 0 || (ep->n == 1 && ep->s[0].op == CVMK_EP_CLIP)) && !getenv("CVM_B200_NO_TILED_TRANSPOSE")) {
+      const Shape& sh = src.shape;
+      const int64_t batch = sh[0];
+      const int64_t c = sh[1], hw = sh[2] * sh[3];
+      const int rows = (int)(src.nhwc ? hw : c), cols = (int)(src.nhwc ? c : hw);
+      const int clamp = ep && ep->n == 1;
+      const int lo = clamp ? ep->s[0].a : 0, hi = clamp ? ep->s[0].b : 0;
+      const DevBuf a = src, b = dst;
+      add_step(label, [a, b, batch, rows, cols, clamp, lo, hi](cudaStream_t s_) {
+        return cvmk_transpose_batched(a.ptr, b.ptr, a.dtype, batch, rows, cols, clamp, lo, hi, s_);
+      });
+      return;
+    }
     cvmk_strided_desc d;
     memset(&d, 0, sizeof(d));
     d.op = CVMK_OP_COPY;

@@ -48,6 +48,48 @@ __global__ void __launch_bounds__(256) where_kernel(const __grid_constant__ Wher
   }
 }
 
+// Batched matrix transpose through shared memory: y[b][c][r] = clamp(x[b][r][c]) for b < batch,
+// r < rows, c < cols.  This is the NCHW <-> NHWC change of a 4-D tensor (rows = C, cols = H * W or
+// the other way round).  A CTA moves a TILE x TILE block: reads and writes are both runs along
+// the contiguous dimension of their side (int8: 4 bytes per thread, 64-byte runs per row of the
+// tile), where the generic strided copy reads single bytes a whole plane apart.
+struct TransposeParams {
+  const void* x; void* y;
+  int rows, cols;
+  int tiles_r, tiles_c;
+  int64_t total_tiles;
+  int lo, hi, clamp;
+};
+template <typename T, int TILE>
+__global__ void __launch_bounds__(256) transpose_kernel(const __grid_constant__ TransposeParams p) {
+  __shared__ T tile[TILE][TILE + (sizeof(T) == 1 ? 4 : 1)];
+  const T* x = reinterpret_cast<const T*>(p.x);
+  T* y = reinterpret_cast<T*>(p.y);
+  for (int64_t t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+    const int tc = (int)(t % p.tiles_c);
+    const int64_t q = t / p.tiles_c;
+    const int tr = (int)(q % p.tiles_r);
+    const int64_t b = q / p.tiles_r;
+    const int r0 = tr * TILE, c0 = tc * TILE;
+    const T* xb = x + b * (int64_t)p.rows * p.cols;
+    T* yb = y + b * (int64_t)p.rows * p.cols;
+    for (int e = threadIdx.x; e < TILE * TILE; e += 256) {   // consecutive threads along cols
+      const int r = e / TILE, c = e % TILE;
+      if (r0 + r < p.rows && c0 + c < p.cols) {
+        T v = xb[(int64_t)(r0 + r) * p.cols + c0 + c];
+        if (p.clamp) v = (T)min(max((int)v, p.lo), p.hi);
+        tile[r][c] = v;
+      }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < TILE * TILE; e += 256) {   // consecutive threads along rows
+      const int c = e / TILE, r = e % TILE;
+      if (r0 + r < p.rows && c0 + c < p.cols) yb[(int64_t)(c0 + c) * p.rows + r0 + r] = tile[r][c];
+    }
+    __syncthreads();
+  }
+}
+
 int grid_for(int64_t total, int threads) {
   const int64_t want = (total + threads - 1) / threads;
   const int64_t cap = 148 * 16;
@@ -88,4 +130,24 @@ extern "C" int cvmk_where(const cvmk_where_desc* d, cvmk_stream_t stream) {
   p.total = d->n; p.inner = d->inner;
   where_kernel<<<grid_for(p.total, 256), 256, 0, (cudaStream_t)stream>>>(p);
   return check_cuda(cudaGetLastError(), "where_kernel launch");
+}
+
+extern "C" int cvmk_transpose_batched(const void* x, void* y, int32_t dtype, int64_t batch, int32_t rows,
+                                      int32_t cols, int32_t clamp, int32_t lo, int32_t hi, cvmk_stream_t stream) {
+  if (!x || !y || !dtype_ok(dtype) || batch < 1 || rows < 1 || cols < 1) {
+    set_error("transpose_batched: bad argument");
+    return CVMK_ERR_ARG;
+  }
+  TransposeParams p;
+  p.x = x; p.y = y; p.rows = rows; p.cols = cols;
+  p.lo = lo; p.hi = hi; p.clamp = clamp;
+  const int tile = dtype == CVMK_I8 ? 64 : 32;
+  p.tiles_r = (rows + tile - 1) / tile;
+  p.tiles_c = (cols + tile - 1) / tile;
+  p.total_tiles = batch * p.tiles_r * p.tiles_c;
+  const int64_t cap = 148 * 8;
+  const int grid = (int)(p.total_tiles < cap ? p.total_tiles : cap);
+  if (dtype == CVMK_I8) transpose_kernel<int8_t, 64><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  else transpose_kernel<int32_t, 32><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  return check_cuda(cudaGetLastError(), "transpose_kernel launch");
 }

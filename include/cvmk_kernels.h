@@ -375,6 +375,15 @@ CVMK_API int cvmk_non_max_suppression_static(const int32_t* x, const int32_t* va
                                              int32_t iou_threshold, int32_t top_k,
                                              int32_t force_suppress, cvmk_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Batched matrix transpose, y[b][c][r] = x[b][r][c] (optionally clamped to [lo, hi] on the way):
+ * the NCHW <-> NHWC change of layout of a 4-D tensor (rows = C, cols = H * W, or the reverse).
+ * No operator of the reference corresponds to it; the executor uses it where a tensor enters or
+ * leaves the channels-last layout the convolution kernels work in.
+ * ---------------------------------------------------------------------------------------------- */
+CVMK_API int cvmk_transpose_batched(const void* x, void* y, int32_t dtype, int64_t batch, int32_t rows,
+                                    int32_t cols, int32_t clamp, int32_t lo, int32_t hi, cvmk_stream_t stream);
+
 /* Measurement helper (no counterpart in the reference): the int8 tensor-core rate of the current
  * GPU in TOP/s (2 * MACs), measured by issuing `reps` tcgen05.mma kind::i8 instructions of shape
  * M = 128, N = n, K = 32 per SM on operands resident in shared memory and timing the launch with
