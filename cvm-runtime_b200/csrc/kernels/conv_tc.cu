@@ -84,6 +84,8 @@ struct ConvParams {
   uint32_t f_lo2, f_hi2;  // clamp after the tensor step
   int f_sub;            // tensor step subtracts its operand
   int dbg;              // development builds: bit 0 skips the weight loads (timing experiments only)
+  int fast_wide;        // the biased sum may exceed the multiply-add's range: clamp it first (f_pre_lo / f_pre_hi)
+  int f_pre_lo, f_pre_hi;
   int fast_variant;     // (first clamp starts at 0) + 2 * kind; kind: 0 none, 1 add + clamp from 0, 2 add, 3 subtract
   DevChain chain;
 };
@@ -117,7 +119,7 @@ __device__ __forceinline__ void store_vals(const ConvParams& p, size_t lin, cons
 // One thread's row of a tile on the fast path: `chunks` groups of 32 columns are read from TMEM,
 // biased (the rounding addend is part of the staged bias), requantised and written to the
 // swizzled staging panels, in place of the tensor operand when there is one.
-template <int RELU1, int KIND>
+template <int RELU1, int KIND, int WIDE>
 __device__ __forceinline__ void fast_chunk(const ConvParams& p, const FastQ& fq, int32_t (&v)[32], int ci,
                                            const int32_t* bias_row, uint8_t* io_base, int panel_size,
                                            uint32_t row_off, uint32_t sw) {
@@ -126,13 +128,27 @@ __device__ __forceinline__ void fast_chunk(const ConvParams& p, const FastQ& fq,
   // its arithmetic right shift, which is all the packed arithmetic below needs.
   const int4* bp = reinterpret_cast<const int4*>(bias_row + ci * 32);
   const int mul = p.f_mul;
+  if (WIDE) {
+    // Sums too wide for the multiply-add: the staged bias is the plain one; the biased sum is
+    // first clamped to the range the chain's own clamp keeps (after which it fits), then scaled.
+    const int lo = p.f_pre_lo, hi = p.f_pre_hi, am = p.f_add * mul;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int4 b4 = bp[j];
-    v[4 * j] = v[4 * j] * mul + b4.x;
-    v[4 * j + 1] = v[4 * j + 1] * mul + b4.y;
-    v[4 * j + 2] = v[4 * j + 2] * mul + b4.z;
-    v[4 * j + 3] = v[4 * j + 3] * mul + b4.w;
+    for (int j = 0; j < 8; ++j) {
+      const int4 b4 = bp[j];
+      v[4 * j] = min(max(v[4 * j] + b4.x, lo), hi) * mul + am;
+      v[4 * j + 1] = min(max(v[4 * j + 1] + b4.y, lo), hi) * mul + am;
+      v[4 * j + 2] = min(max(v[4 * j + 2] + b4.z, lo), hi) * mul + am;
+      v[4 * j + 3] = min(max(v[4 * j + 3] + b4.w, lo), hi) * mul + am;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int4 b4 = bp[j];
+      v[4 * j] = v[4 * j] * mul + b4.x;
+      v[4 * j + 1] = v[4 * j + 1] * mul + b4.y;
+      v[4 * j + 2] = v[4 * j + 2] * mul + b4.z;
+      v[4 * j + 3] = v[4 * j + 3] * mul + b4.w;
+    }
   }
   const int c0 = ci * 32;
   uint8_t* pb = io_base + (size_t)(c0 >> 7) * panel_size + row_off;
@@ -147,7 +163,7 @@ __device__ __forceinline__ void fast_chunk(const ConvParams& p, const FastQ& fq,
   *q1 = b;
 }
 
-template <int RELU1, int KIND>
+template <int RELU1, int KIND, int WIDE>
 __device__ __forceinline__ void fast_row(const ConvParams& p, uint32_t tbase, int chunks, const int32_t* bias_row,
                                          uint8_t* io_base, int panel_size, int row_in_tile, int pw) {
   const FastQ fq = {p.f_lo1, p.f_hi1, p.f_lo2, p.f_hi2};
@@ -157,13 +173,13 @@ __device__ __forceinline__ void fast_row(const ConvParams& p, uint32_t tbase, in
   for (; ci + 2 <= chunks; ci += 2) {  // two chunks per TMEM round trip
     int32_t v0[32], v1[32];
     tmem_ld64(tbase + (uint32_t)(ci * 32), v0, v1);
-    fast_chunk<RELU1, KIND>(p, fq, v0, ci, bias_row, io_base, panel_size, row_off, sw);
-    fast_chunk<RELU1, KIND>(p, fq, v1, ci + 1, bias_row, io_base, panel_size, row_off, sw);
+    fast_chunk<RELU1, KIND, WIDE>(p, fq, v0, ci, bias_row, io_base, panel_size, row_off, sw);
+    fast_chunk<RELU1, KIND, WIDE>(p, fq, v1, ci + 1, bias_row, io_base, panel_size, row_off, sw);
   }
   if (ci < chunks) {
     int32_t v[32];
     tmem_ld32(tbase + (uint32_t)(ci * 32), v);
-    fast_chunk<RELU1, KIND>(p, fq, v, ci, bias_row, io_base, panel_size, row_off, sw);
+    fast_chunk<RELU1, KIND, WIDE>(p, fq, v, ci, bias_row, io_base, panel_size, row_off, sw);
   }
 }
 
@@ -279,7 +295,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     {
       const int32_t b = i < p.oc && p.bias ? __ldg(p.bias + i) : 0;
       // fast path: (bias + rounding addend) pre-multiplied by 2^(16 - shift), see fast_row()
-      bias_s[i] = p.fast_mode ? (int32_t)((uint32_t)(b + p.f_add) * (uint32_t)p.f_mul) : b;
+      bias_s[i] = (p.fast_mode && !p.fast_wide) ? (int32_t)((uint32_t)(b + p.f_add) * (uint32_t)p.f_mul) : b;
     }
   }
   tc_fence_before();
@@ -567,15 +583,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (p.fast_mode) {
           const int chunks = min(p.block_n, p.oc - n0) >> 5;  // OC is a multiple of 32 on this path
           const int32_t* brow = bias_s + n0;
-          switch (p.fast_variant) {
-            case 0: fast_row<0, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 1: fast_row<1, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 2: fast_row<0, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 3: fast_row<1, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 4: fast_row<0, 2>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 5: fast_row<1, 2>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 6: fast_row<0, 3>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            default: fast_row<1, 3>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+          switch (p.fast_variant + 8 * p.fast_wide) {
+            case 0: fast_row<0, 0, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 1: fast_row<1, 0, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 2: fast_row<0, 1, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 3: fast_row<1, 1, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 4: fast_row<0, 2, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 5: fast_row<1, 2, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 6: fast_row<0, 3, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 7: fast_row<1, 3, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 8: fast_row<0, 0, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 9: fast_row<1, 0, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 10: fast_row<0, 1, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 11: fast_row<1, 1, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 12: fast_row<0, 2, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 13: fast_row<1, 2, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 14: fast_row<0, 3, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            default: fast_row<1, 3, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
           }
         } else {
         int32_t v[32];
@@ -1057,7 +1081,12 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
       const bool no_overflow = d.acc_bound + add < (int64_t)INT32_MAX;
       const bool fits16 = ((d.acc_bound + add) >> sh) < 32767;
       const bool clamp_ok = lo1 >= -32767 && hi1 <= 32767 && lo1 <= hi1 && sh <= 16;
-      if (no_overflow && fits16 && clamp_ok) {
+      // Without fits16 the sum is clamped to [rs.a, rs.b] before it is scaled (fast_wide); the
+      // clamped value plus the rounding addend then stays below 2^(15 + shift).
+      const bool wide_ok = (int64_t)rs.b + add < ((int64_t)1 << (15 + sh)) && (int64_t)rs.a + add > -((int64_t)1 << (15 + sh));
+      p.fast_wide = 0;
+      if (no_overflow && (fits16 || wide_ok) && clamp_ok) {
+        if (!fits16) { p.fast_wide = 1; p.f_pre_lo = rs.a; p.f_pre_hi = rs.b; }
         auto x2 = [](int64_t v) { return (uint32_t)((uint32_t)(uint16_t)(int16_t)v | ((uint32_t)(uint16_t)(int16_t)v << 16)); };
         if (left == 1) {
           p.fast_mode = 1;
