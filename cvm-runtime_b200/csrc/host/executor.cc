@@ -343,7 +343,11 @@ struct Lowering {
     auto it = g.params.find(eid);
     if (it != g.params.end()) {  // the usual case: upload the int32 vector once
       const auto& v = it->second.data;
-      void* p = ex.dalloc(v.size() * 4);
+      // zero padded to a multiple of 32 entries: a convolution whose output channels are padded
+      // for the tensor-core kernel reads that far
+      const size_t padded = (v.size() + 31) / 32 * 32;
+      void* p = ex.dalloc(padded * 4);
+      CUDA_OK(cudaMemset(p, 0, padded * 4));
       CUDA_OK(cudaMemcpy(p, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
       return reinterpret_cast<const int32_t*>(p);
     }
@@ -423,8 +427,23 @@ struct Lowering {
                           (KW - 1) * dw <= 4095 && (KH - 1) * dh <= 2047 &&
                           cvmk_conv2d_tc_supported(&packed) && !getenv("CVM_B200_NO_TC");
 
+    // Output channel counts the tensor-core kernel does not take (not a multiple of 8: detection
+    // heads with anchors x classes channels) run on it with zero weight rows up to a multiple of
+    // 32 and a copy of the real channels afterwards, when nothing in the chain indexes the
+    // output tensor (no fused tensor operand) and the bias is a parameter.
+    const int OCp = (OC + 31) / 32 * 32;
+    bool tc_pad = false;
+    if (!tc && !dense && groups == 1 && OC % 8 != 0 && !depthwise && !getenv("CVM_B200_NO_TC")) {
+      cvmk_conv_desc pp = probe;
+      pp.OC = OCp;
+      bool plain_chain = true;
+      for (int i = 0; i < ch.ep.n; ++i)
+        plain_chain &= !(ch.ep.s[i].op == CVMK_EP_ADD_T || ch.ep.s[i].op == CVMK_EP_SUB_T || ch.ep.s[i].op == CVMK_EP_RSUB_T);
+      const bool bias_param = !use_bias || g.params.count(g.entry_id(n.inputs[2])) > 0;
+      tc_pad = cvmk_conv2d_tc_supported(&pp) && plain_chain && bias_param && safe8[ex_] && out.shape.size() == 4;
+    }
     // weights: OIHW int32 -> int8, [OC, KH, KW, C/groups] (depthwise: [KH, KW, C])
-    std::vector<int8_t> w8((size_t)OC * KH * KW * icg);
+    std::vector<int8_t> w8((size_t)(tc_pad ? OCp : OC) * KH * KW * icg);
     if (depthwise && !tc) {
       for (int c = 0; c < C; ++c)
         for (int k = 0; k < KH * KW; ++k) w8[(size_t)k * C + c] = (int8_t)wt.data[(size_t)c * KH * KW + k];
@@ -530,6 +549,30 @@ struct Lowering {
       cvmk_conv_plan* plan = ex.plans_.back().get();
       KERNEL_OK(cvmk_conv2d_tc_prepare(&d, plan));
       add_step(label + "[tc]", [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
+      return;
+    }
+
+    if (tc_pad) {
+      DevBuf xin = i8_view(ex_, label);
+      DevBuf tmp = out;
+      tmp.shape = Shape{(int64_t)N, (int64_t)OCp, (int64_t)OH, (int64_t)OW};
+      tmp.nhwc = true;
+      tmp.ptr = ex.dalloc(tmp.bytes());
+      cvmk_conv_desc d = probe;
+      d.OC = OCp;
+      d.x = (const int8_t*)xin.ptr; d.w = wdev; d.y = tmp.ptr; d.y_dtype = tmp.dtype;
+      d.status = ex.status_dev_;
+      d.ep = ch.ep;
+      void* mem = nullptr;
+      CHECK(posix_memalign(&mem, 64, sizeof(cvmk_conv_plan)) == 0);
+      ex.plans_.emplace_back((cvmk_conv_plan*)mem, plan_deleter);
+      cvmk_conv_plan* plan = ex.plans_.back().get();
+      KERNEL_OK(cvmk_conv2d_tc_prepare(&d, plan));
+      add_step(label + "[tc]", [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
+      const auto ss = phys_strides(tmp.shape, true), ds = phys_strides(out.shape, out.nhwc);
+      std::vector<GDim> dims;
+      for (int k = 0; k < 4; ++k) dims.push_back({out.shape[k], ss[k], ds[k]});
+      emit_gather(tmp, 0, out, dims, label + ":channels");
       return;
     }
 

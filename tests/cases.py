@@ -142,6 +142,12 @@ def op_cases():
     add("conv_halo_c128_oc32_pad0", lambda: conv_case(43, 1, 128, 34, 42, 32, 3, 1, 0, shift=10, bias=False))
     add("conv_halo_c64_pad2", lambda: conv_case(44, 2, 64, 30, 30, 64, 3, 1, 2, shift=9))
 
+    # output channel counts that are not a multiple of 8 (detection heads): tensor-core kernel on
+    # channels padded to 32, real channels copied out; int32 and int8 outputs
+    add("conv_tc_oc126_int32", lambda: conv_case(46, 2, 64, 9, 11, 126, 3, 1, 1, shift=0))
+    add("conv_tc_oc84_shift", lambda: conv_case(47, 3, 96, 7, 5, 84, 3, 1, 1, shift=9, relu=True))
+    add("conv_tc_oc21_1x1", lambda: conv_case(48, 2, 32, 6, 6, 21, 1, 1, 0, shift=7, bias=False))
+
     def halo_join():
         rng = np.random.RandomState(45)
         g = wl.GraphBuilder(45)
