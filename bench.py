@@ -1,7 +1,7 @@
 """Benchmark of the operator hot path: int8 ResNet-50 images/s through the C-ABI on N B200s.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload resnet50|mobilenet|vgg19|conv_chain|ssd_tail|ssd_backbone] [--batch B]
+                    [--workload resnet50|mobilenet|vgg19|conv_chain|ssd_tail|ssd_backbone|ssd_full] [--batch B]
 
 One step = one inference of the per-GPU batch (default: synthetic MRT-style quantized ResNet-50
 v1, batch 256).  With N > 1 (launched through torch.distributed.run) every rank holds its own
@@ -30,7 +30,7 @@ import __graft_entry__ as ge  # noqa: E402
 
 METRIC = "int8 ResNet-50 images/s"
 UNITS = {"resnet50": "images/s", "mobilenet": "images/s", "vgg19": "images/s", "conv_chain": "images/s",
-         "ssd_tail": "boxes/s", "ssd_backbone": "images/s"}
+         "ssd_tail": "boxes/s", "ssd_backbone": "images/s", "ssd_full": "images/s"}
 
 
 def make_workload(wl, name, batch):
@@ -46,6 +46,8 @@ def make_workload(wl, name, batch):
         return wl.ssd_tail(batch)
     if name == "ssd_backbone":
         return wl.ssd_backbone(batch)
+    if name == "ssd_full":   # image -> boxes in one graph: backbone, heads, transposes / concats, valid counts, NMS
+        return wl.ssd_full(batch, size=512, classes=21)
     raise SystemExit("unknown workload " + name)
 
 
@@ -202,7 +204,7 @@ def run_reference(args, wl, oracle, rank, world):
     if rank != 0:
         return
     sample_batch = {"resnet50": 8, "mobilenet": 16, "vgg19": 2, "conv_chain": 32, "ssd_tail": 8,
-                    "ssd_backbone": 2}[args.workload]
+                    "ssd_backbone": 2, "ssd_full": 2}[args.workload]
     vals = []
     base = None
     for i in range(args.warmup + args.steps):
@@ -239,7 +241,7 @@ def main():
     if args.batch is None:
         # VGG-19: the reference refuses graphs whose int32 pool exceeds 4 GiB, i.e. batch 256 in one
         # graph; its configuration is batch 256 over 8 GPUs = 32 per handle
-        args.batch = {"ssd_tail": 64, "vgg19": 32, "ssd_backbone": 32}.get(args.workload, 256)
+        args.batch = {"ssd_tail": 64, "vgg19": 32, "ssd_backbone": 32, "ssd_full": 8}.get(args.workload, 256)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
@@ -367,7 +369,7 @@ def main():
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
-        sample = {"resnet50": 16, "mobilenet": 32, "vgg19": 4, "conv_chain": 64, "ssd_tail": 16, "ssd_backbone": 2}[args.workload]
+        sample = {"resnet50": 16, "mobilenet": 32, "vgg19": 4, "conv_chain": 64, "ssd_tail": 16, "ssd_backbone": 2, "ssd_full": 2}[args.workload]
         cpu = cpu_baseline(ge.load_oracle(), wl, args.workload, sample, repeats=2)
         cpu.pop("seconds_per_step", None)
 
