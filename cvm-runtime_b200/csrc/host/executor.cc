@@ -413,6 +413,7 @@ struct Lowering {
         }
       }
       probe.acc_bound = (int64_t)icg * KH * KW * 128 * 128 + bias_max;
+      probe.bias_static = (!use_bias || g.params.count(g.entry_id(n.inputs[2])) > 0) ? 1 : 0;
     }
     const bool tc = groups == 1 && cvmk_conv2d_tc_supported(&probe) && !getenv("CVM_B200_NO_TC");
     const bool depthwise = !dense && groups == C && OC == C && C % 16 == 0 && safe8[ex_];

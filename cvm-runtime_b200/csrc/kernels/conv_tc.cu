@@ -87,6 +87,9 @@ struct ConvParams {
   int fast_wide;        // the biased sum may exceed the multiply-add's range: clamp it first (f_pre_lo / f_pre_hi)
   int f_pre_lo, f_pre_hi;
   int fast_variant;     // (first clamp starts at 0) + 2 * kind; kind: 0 none, 1 add + clamp from 0, 2 add, 3 subtract
+  int bias_static;      // the bias vector is a parameter: it may be read before the previous kernel has finished
+  const int8_t* w;      // the weight matrix [oc, kh * kw * c] and its size, for the L2 warm-up
+  unsigned w_bytes;
   DevChain chain;
 };
 
@@ -194,7 +197,11 @@ __device__ long long g_conv_timing[148 * 16];
 #define TADD(slot, var) do { const long long now__ = clock64(); tacc[slot] += now__ - var; var = now__; } while (0)
 #define TDECL long long tacc[16] = {0}
 #define TFLUSH(slot) do { if (blockIdx.x < 148) g_conv_timing[blockIdx.x * 16 + (slot)] = tacc[slot]; } while (0)
+// Event trace of CTA 0: g_conv_trace[role * 512 + seq] = clock of the seq-th event of that role.
+__device__ long long g_conv_trace[17 * 512];
+#define TRACE(role, seq) do { if (blockIdx.x == 0 && (seq) < 512) g_conv_trace[(role) * 512 + (seq)] = clock64(); } while (0)
 #else
+#define TRACE(role, seq) do {} while (0)
 #define TSTART(var) do {} while (0)
 #define TSET(var) do {} while (0)
 #define TADD(slot, var) do {} while (0)
@@ -239,8 +246,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
-  const int warp = threadIdx.x >> 5;
+  // The warp index comes out of a shuffle so that the compiler knows it is the same for the whole
+  // warp: the loops of the single-issuer roles below are then run by all 32 lanes on the uniform
+  // datapath (loop counters, shared-memory addresses and descriptors stay in uniform registers, which
+  // is where TMA and tcgen05 instructions take their operands from) and only the instructions with a
+  // side effect are predicated on one elected lane.  Run by lane 0 alone, every operand had to be
+  // moved from a per-thread register first, several hundred cycles per TMA / MMA instruction.
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TRACE(16, 0);
   const int a_bytes = BLOCK_M * p.block_k;
   const int b_bytes = p.block_n * p.block_k;
   const int unit_bytes = a_bytes + b_bytes;          // one A tile and the B tile that goes with it
@@ -285,34 +299,58 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
   if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
   // Programmatic dependent launch: the next kernel of the stream may start its own prologue on SMs
-  // this grid has left; everything up to here touched no global memory, and nothing below runs
-  // before the previous kernel of the stream has completed and flushed its writes.
+  // this grid has left.  Until griddepcontrol.wait returns, the previous kernel of the stream may
+  // still be running, so only memory that no kernel writes is touched before it: the tensor maps
+  // and the parameter block (both in the kernel's own argument space), the weights, and the bias
+  // when it is a model parameter.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (bias_in_smem) {
+  if (warp == IO_WARP) {
+    // Warm the descriptor cache with the tensor maps.
+    if (lane < 4) {
+      const CUtensorMap* m = lane == 0 ? &tmap_a : (lane == 1 ? &tmap_b : (lane == 2 ? &tmap_y : &tmap_r));
+      if (lane < 2 || (p.tma_out && (lane == 2 || p.res_step >= 0)))
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+    }
+  } else if (warp == PRODUCER2_WARP && lane == 0) {
+    // L2 warm-up: this CTA's share of the weight matrix (every CTA reads most of it soon).
+    const unsigned per = ((p.w_bytes + gridDim.x - 1) / gridDim.x + 15u) & ~15u;
+    const unsigned begin = blockIdx.x * per;
+    if (begin < p.w_bytes) {
+      const unsigned n = min(per, p.w_bytes - begin) & ~15u;
+      if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.w + begin), "r"(n) : "memory");
+    }
+  }
+  auto stage_bias = [&]() {
     const int padded = min(MAX_BIAS, (p.oc + 31) & ~31);
-    for (int i = threadIdx.x; i < padded; i += NUM_THREADS)
-    {
+    for (int i = threadIdx.x; i < padded; i += NUM_THREADS) {
       const int32_t b = i < p.oc && p.bias ? __ldg(p.bias + i) : 0;
       // fast path: (bias + rounding addend) pre-multiplied by 2^(16 - shift), see fast_row()
       bias_s[i] = (p.fast_mode && !p.fast_wide) ? (int32_t)((uint32_t)(b + p.f_add) * (uint32_t)p.f_mul) : b;
     }
-  }
+  };
+  if (bias_in_smem && p.bias_static) stage_bias();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0) TRACE(16, 1);
+  if (bias_in_smem && !p.bias_static) stage_bias();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  if (threadIdx.x == 0) TRACE(16, 2);
 
   if (warp == 0 || warp == PRODUCER2_WARP) {
     // ------------------------------------------------------------------ TMA producers
     // Producer `which` issues the K blocks whose running number (over all tiles of this CTA) is
     // congruent to it modulo 2; both walk the same sequence of ring slots.
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       const int which = warp == 0 ? 0 : 1;
+      if (which == 0 && leader) TRACE(16, 6);
       int stage = which % p.stages;
       uint32_t phase = which >= p.stages ? 1u : 0u;
       int turn = which;  // 0: the next stage is this producer's
       bool live = true;
+      int pseq = 0; (void)pseq;
       TDECL;
       TSTART(tk);
       // The loop below runs on one thread, so its own instruction latency bounds the rate of
@@ -322,11 +360,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t full0 = smem_u32(&bar_full[0]);
       if (w_resident && which == 0) {  // the weight matrix, once (every tile of this CTA has n0 = 0)
         const uint32_t wb = smem_u32(&bar_weights);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wb), "r"((uint32_t)resident_bytes) : "memory");
+        if (leader) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wb), "r"((uint32_t)resident_bytes) : "memory");
         uint32_t dst = smem_u32(smem);
         int kcol = 0;
         for (int t = 0; t < taps; ++t) {
-          asm volatile(
+          if (leader) asm volatile(
               "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
               " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(wb),
               "r"(kcol), "r"(0)
@@ -338,6 +376,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
         const TileOrigin to = tile_origin(p, tile);
         const int m0 = to.m0;
+        if (which == 0 && tile == (int)blockIdx.x && leader) TRACE(16, 7);
         int img = 0, base_w = 0, base_h = 0;
         if (p.a_mode == 1) {
           img = m0 / (p.oh * p.ow);
@@ -355,12 +394,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             TSTART(tw);
             if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
             TADD(0, tw);
+            if (leader) TRACE(which * 2, pseq);
             const uint32_t sa = smem_base + (uint32_t)(stage * stage_bytes);
             const uint32_t bar = full0 + 8u * (uint32_t)stage;
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+            if (leader) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
                          "r"((uint32_t)(halo_bytes + (w_resident ? 0 : taps * b_bytes))) : "memory");
             const int cc = cb * p.block_k;
-            asm volatile(
+            if (leader) asm volatile(
                 "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                 " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)),
                 "r"(bar), "r"(cc), "r"(to.cw - p.pad_w), "r"(to.ch - p.pad_h), "r"(to.cn)
@@ -368,7 +408,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t sb = sa + (uint32_t)halo_pad;
             int kcol = cc;
             for (int t = 0; t < (w_resident ? 0 : taps); ++t) {
-              asm volatile(
+              if (leader) asm volatile(
                   "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                   " [%0], [%1, {%3, %4}], [%2];" ::"r"(sb), "l"(reinterpret_cast<uint64_t>(&tmap_b)),
                   "r"(bar), "r"(kcol), "r"(to.n0)
@@ -376,6 +416,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               sb += (uint32_t)b_bytes;
               kcol += p.c;
             }
+            if (leader) TRACE(which * 2 + 1, pseq);
+            ++pseq;
             stage += 2;
             if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
           }
@@ -390,17 +432,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mine = turn == 0;
             turn ^= 1;
             if (mine) {
+              if (which == 0 && pseq == 0 && leader) TRACE(16, 8);
               TSTART(tw);
               if (!mbar_wait(&bar_empty[stage], phase ^ 1, &abort_flag, 1)) { live = false; break; }
               TADD(0, tw);
+              if (leader) TRACE(which * 2, pseq);
               sa = smem_base + (uint32_t)(stage * stage_bytes);
               bar = full0 + 8u * (uint32_t)stage;
               const int in_stage = min(p.units, num_units - unit);
-              asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+              if (leader) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
                            "r"((uint32_t)(in_stage * unit_bytes)) : "memory");
             }
           }
-          if (mine) {
+          if (mine && leader) {
             const int off_w = fx * p.dil_w, off_h = fy * p.dil_h;
             if (p.a_mode == 2)  // the patch of this tile, shifted by the filter tap; zero fill outside the image
               asm volatile(
@@ -426,8 +470,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa + (uint32_t)a_bytes), "l"(reinterpret_cast<uint64_t>(&tmap_b)),
                 "r"(bar), "r"(kcol), "r"(to.n0)
                 : "memory");
-            sa += (uint32_t)unit_bytes;
           }
+          if (mine) sa += (uint32_t)unit_bytes;
           // next unit
           kcol += p.block_k;
           cc += p.block_k;
@@ -435,6 +479,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (++slot == p.units || unit + 1 == num_units) {
             slot = 0;
             if (mine) {
+              if (leader) TRACE(which * 2 + 1, pseq);
+              ++pseq;
               stage += 2;
               if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
             }
@@ -443,12 +489,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       TADD(12, tk);
 #ifdef CVMK_CONV_TIMING
-      if (which == 0) { TFLUSH(0); TFLUSH(12); }
+      if (which == 0 && leader) { TFLUSH(0); TFLUSH(12); }
 #endif
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       const uint32_t idesc = umma_idesc_i8(p.block_n);
       const uint64_t desc_a0 = umma_desc(smem_u32(ring), p.block_k);
       const uint32_t w_lo0 = (uint32_t)umma_desc(smem_u32(smem), p.block_k);  // resident weights (a_mode 4)
@@ -467,6 +514,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int acc = 0;
       uint32_t acc_phase = 0;
       bool live = true;
+      int mseq = 0, tseq = 0; (void)mseq; (void)tseq;
       TDECL;
       TSTART(tl);
       if (w_resident && blockIdx.x < num_tiles && !mbar_wait(&bar_weights, 0u, &abort_flag, 7)) live = false;
@@ -474,12 +522,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         TSTART(tw);
         if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1, &abort_flag, 2)) { live = false; break; }
         TADD(1, tw);
+        if (leader) TRACE(6, tseq);
+        ++tseq;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.block_n);
         int unit = 0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&bar_full[stage], phase, &abort_flag, 3)) { live = false; break; }
           TADD(2, tw);
+          if (leader) TRACE(4, mseq);
           tc_fence_after();
           const uint32_t st = a_lo0 + stage_q * (uint32_t)stage;
           if (halo) {
@@ -491,13 +542,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               uint32_t al = st + (uint32_t)fy * halo_row_q;
 #pragma unroll
               for (int fx = 0; fx < 3; ++fx) {
-                mma_i8_k<2>(d_tmem, al, halo_hi, bl, a_hi, idesc, (uint32_t)(kb | fy | fx));
+                if (leader) mma_i8_k<2>(d_tmem, al, halo_hi, bl, a_hi, idesc, (uint32_t)(kb | fy | fx));
                 al += 4u;   // one pixel of 64 channels
                 bl += b_q;
               }
             }
             TADD(13, ti);
-            mma_commit(&bar_empty[stage]);
+            if (leader) mma_commit(&bar_empty[stage]);
+            if (leader) TRACE(5, mseq);
+            ++mseq;
             TADD(14, ti);
             TSET(tw);
             if (++stage == p.stages) { stage = 0; phase ^= 1; }
@@ -505,28 +558,30 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           const int in_stage = min(p.units, num_units - unit);
           uint32_t al = st;
-          if (nk == 4) {
-            for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<4>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
-          } else if (nk == 2) {
-            for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<2>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
-          } else {
-            for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<1>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+          if (leader) {
+            if (nk == 4) {
+              for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<4>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+            } else if (nk == 2) {
+              for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<2>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+            } else {
+              for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<1>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+            }
+            mma_commit(&bar_empty[stage]);
+            TRACE(5, mseq);
           }
           unit += in_stage;
-          mma_commit(&bar_empty[stage]);
+          ++mseq;
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (!live) break;
-        mma_commit(&bar_acc_full[acc]);
+        if (leader) mma_commit(&bar_acc_full[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
       TADD(3, tl);
-      TFLUSH(1);
-      TFLUSH(2);
-      TFLUSH(3);
-      TFLUSH(13);
-      TFLUSH(14);
+#ifdef CVMK_CONV_TIMING
+      if (leader) { TFLUSH(1); TFLUSH(2); TFLUSH(3); TFLUSH(13); TFLUSH(14); }
+#endif
     }
   } else if (warp < IO_WARP) {
     // ------------------------------------------------------------------ epilogue warps
@@ -573,10 +628,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       TSTART(tw);
       bool ok = mbar_wait(&bar_acc_full[acc], (uint32_t)(k & 1), &abort_flag, 4);
       TADD(4 + 4 * group, tw);
+      if (leader) TRACE(7 + 3 * group, k);
       tc_fence_after();
       // the staging buffer is ours: its previous store has been read, or the operand tile landed
       if (ok && p.tma_out) ok = mbar_wait(&bar_res[group][buf], use & 1u, &abort_flag, 5);
       TADD(5 + 4 * group, tw);
+      if (leader) TRACE(8 + 3 * group, k);
       if (!ok) break;
       if (ok) {
         const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.block_n);
@@ -674,12 +731,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (p.tma_out) mbar_arrive(&bar_staged[group][buf]);
       }
       TADD(6 + 4 * group, tw);
+      if (leader) TRACE(9 + 3 * group, k);
       if (abort_flag) break;
     }
 #ifdef CVMK_CONV_TIMING
     if (leader) { TFLUSH(4 + 4 * group); TFLUSH(5 + 4 * group); TFLUSH(6 + 4 * group); TFLUSH(7 + 4 * group); }
 #endif
-  } else if (p.tma_out && lane == 0) {
+  } else if (p.tma_out) {
+    const bool leader = elect_one();
     // ------------------------------------------------------------------ IO warp
     // Moves the staged tiles: waits until a group has written a buffer, stores it with TMA, waits
     // until the TMA engine has read it, then hands the buffer back -- directly, or by loading the
@@ -691,15 +750,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     auto buffer_of = [&](int g, int b) { return io_all + (size_t)(g * p.io_bufs + b) * buf_bytes; };
     auto hand_back = [&](int g, int b, int next_tile) {
       if (next_tile >= num_tiles) return;
-      if (!has_res) { mbar_arrive(&bar_res[g][b]); return; }
+      if (!has_res) { if (leader) mbar_arrive(&bar_res[g][b]); return; }
       const TileOrigin to = tile_origin(p, next_tile);
       uint8_t* dst = buffer_of(g, b);
-      mbar_expect_tx(&bar_res[g][b], (uint32_t)buf_bytes);
-      for (int q = 0; q < p.panels; ++q) {
-        if (p.a_mode >= 2)
-          tma_load_4d(dst + (size_t)q * panel_size, &tmap_r, &bar_res[g][b], to.n0 + q * 128, to.cw, to.ch, to.cn);
-        else
-          tma_load_2d(dst + (size_t)q * panel_size, &tmap_r, &bar_res[g][b], to.n0 + q * 128, to.m0);
+      if (leader) {
+        mbar_expect_tx(&bar_res[g][b], (uint32_t)buf_bytes);
+        for (int q = 0; q < p.panels; ++q) {
+          if (p.a_mode >= 2)
+            tma_load_4d(dst + (size_t)q * panel_size, &tmap_r, &bar_res[g][b], to.n0 + q * 128, to.cw, to.ch, to.cn);
+          else
+            tma_load_2d(dst + (size_t)q * panel_size, &tmap_r, &bar_res[g][b], to.n0 + q * 128, to.m0);
+        }
       }
     };
     // every buffer starts free (or with the operand of its first tile on the way)
@@ -711,24 +772,34 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int b = p.io_bufs == 2 ? (k & 1) : 0;
       const uint32_t use = (uint32_t)(p.io_bufs == 2 ? (k >> 1) : k);
       if (!mbar_wait(&bar_staged[g][b], use & 1u, &abort_flag, 6)) break;
+      if (leader) TRACE(13, i);
       const TileOrigin to = tile_origin(p, tile);
       const uint8_t* src = buffer_of(g, b);
-      for (int q = 0; q < p.panels; ++q) {
-        if (to.n0 + q * 128 >= p.oc) break;
-        if (p.a_mode >= 2) tma_store_4d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.cw, to.ch, to.cn);
-        else tma_store_2d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.m0);
+      if (leader) {
+        for (int q = 0; q < p.panels; ++q) {
+          if (to.n0 + q * 128 >= p.oc) break;
+          if (p.a_mode >= 2) tma_store_4d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.cw, to.ch, to.cn);
+          else tma_store_2d(&tmap_y, src + (size_t)q * panel_size, to.n0 + q * 128, to.m0);
+        }
+        tma_store_commit();
+        tma_store_wait_read();
+        TRACE(14, i);
       }
-      tma_store_commit();
-      tma_store_wait_read();
+      __syncwarp();
       hand_back(g, b, tile + 2 * p.io_bufs * (int)gridDim.x);
+      if (leader) TRACE(15, i);
     }
-    tma_store_wait_all();
+    // Every store has been read out of shared memory (wait_group.read above); the writes
+    // themselves complete with the grid, which is what the next kernel's griddepcontrol.wait
+    // (or the stream order) waits for.
   }
 
   // ------------------------------------------------------------------ teardown
   __syncwarp();
+  if (threadIdx.x == 0) TRACE(16, 3);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(16, 4);
   if (abort_flag) {
     // Give copies that may still be in flight time to land before shared memory is released.
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -738,6 +809,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    if (lane == 0) TRACE(16, 5);
   }
 }
 
@@ -1039,6 +1111,9 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   while (pow2 < cols) pow2 *= 2;
   p.tmem_cols = pow2;
   p.status = d.status;
+  p.bias_static = d.bias_static;
+  p.w = d.w;
+  p.w_bytes = (unsigned)std::min<int64_t>((int64_t)d.OC * d.KH * d.KW * d.C, (int64_t)1 << 30);
   p.tma_out = plan->tma_out; p.res_step = plan->res_step;
 #ifdef CVMK_CONV_TIMING
   p.dbg = getenv("CVM_DBG") ? atoi(getenv("CVM_DBG")) : 0;
@@ -1145,5 +1220,12 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
 #ifdef CVMK_CONV_TIMING
 extern "C" int cvmk_conv_timing_read(long long* host, int count) {
   return (int)cudaMemcpyFromSymbol(host, g_conv_timing, sizeof(long long) * (size_t)count);
+}
+extern "C" int cvmk_conv_trace_read(long long* host, int count) {
+  return (int)cudaMemcpyFromSymbol(host, g_conv_trace, sizeof(long long) * (size_t)count);
+}
+extern "C" int cvmk_conv_trace_clear() {
+  static long long zero[17 * 512];
+  return (int)cudaMemcpyToSymbol(g_conv_trace, zero, sizeof(zero));
 }
 #endif

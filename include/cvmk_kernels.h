@@ -116,6 +116,11 @@ typedef struct {
    * ranges (0 = unknown).  When it shows that the rounding shift cannot overflow and that its
    * result fits 16 bits, the kernel requantises two elements per instruction. */
   int64_t acc_bound;
+  /* 1: the ADD_C vector of the chain (the bias) is a model parameter that no kernel ever writes,
+   * like w.  The kernel may then read both before the previous kernel of the stream has finished
+   * (it stages the bias and warms L2 with the weights while it waits for its turn). */
+  int32_t bias_static;
+  int32_t reserved0;
   cvmk_epilogue ep;
 } cvmk_conv_desc;
 
