@@ -49,6 +49,25 @@ constexpr int PRODUCER2_WARP = IO_WARP + 1;
 constexpr int SMEM_DYNAMIC_MAX = 227 * 1024 - 8704;  // 227 KB per CTA minus the static part (bias, barriers)
 constexpr int MAX_BIAS = 2048;          // bias vectors up to this length are staged in shared memory
 
+// Division of a non-negative 31-bit number by a divisor fixed at launch: q = umulhi(n, mul) >> shr
+// (mul = ceil(2^(31 + ceil(log2 d)) / d)); d = 1 is flagged by mul = 0.  Every thread that walks
+// tiles divides several times per tile, and a hardware-emulated 32-bit division is a dependent
+// chain of some twenty instructions.
+struct FastDiv { uint32_t mul, shr; };
+__device__ __forceinline__ int fdiv(int n, const FastDiv& d) {
+  return d.mul ? (int)(__umulhi((uint32_t)n, d.mul) >> d.shr) : n;
+}
+inline FastDiv make_fastdiv(int d) {
+  FastDiv f = {0, 0};
+  if (d <= 1) return f;
+  int lg = 0;
+  while ((1LL << lg) < d) ++lg;
+  const int pw = 31 + lg;
+  f.mul = (uint32_t)((((uint64_t)1 << pw) + (uint64_t)d - 1) / (uint64_t)d);
+  f.shr = (uint32_t)(pw - 32);
+  return f;
+}
+
 struct ConvParams {
   void* y;
   int y_dtype;
@@ -64,7 +83,10 @@ struct ConvParams {
                         // 4 the same with the whole weight matrix resident in shared memory
   int patch_w, patch_h, patch_n;  // a_mode 2, 3: an M tile is patch_w x patch_h output pixels of patch_n images
   int tiles_w, tiles_h;           // a_mode 2, 3: patches per image row / column
+  int patch_w_log2, patch_h_log2; // patch sides are powers of two
   int num_m_tiles, num_n_tiles;
+  int num_units, num_kb;          // (tap, channel block) pairs per tile; ring stages consumed per tile
+  FastDiv fd_n_tiles, fd_tiles_w, fd_tiles_h, fd_ohow, fd_ow;
   int tmem_cols;
   int* status;
   const int32_t* bias;  // per-channel add applied first (nullptr: none)
@@ -214,14 +236,14 @@ __device__ long long g_conv_trace[17 * 512];
 struct TileOrigin { int n0, m0, cw, ch, cn; };
 __device__ __forceinline__ TileOrigin tile_origin(const ConvParams& p, int tile) {
   TileOrigin t;
-  const int mt = tile / p.num_n_tiles;
+  const int mt = fdiv(tile, p.fd_n_tiles);
   t.n0 = (tile - mt * p.num_n_tiles) * p.block_n;
   t.m0 = mt * BLOCK_M;
   t.cw = t.ch = t.cn = 0;
   if (p.a_mode >= 2) {
-    const int r = mt / p.tiles_w;
+    const int r = fdiv(mt, p.fd_tiles_w);
     t.cw = (mt - r * p.tiles_w) * p.patch_w;
-    const int tn = r / p.tiles_h;
+    const int tn = fdiv(r, p.fd_tiles_h);
     t.ch = (r - tn * p.tiles_h) * p.patch_h;
     t.cn = tn * p.patch_n;
   }
@@ -258,7 +280,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int a_bytes = BLOCK_M * p.block_k;
   const int b_bytes = p.block_n * p.block_k;
   const int unit_bytes = a_bytes + b_bytes;          // one A tile and the B tile that goes with it
-  const int num_units = p.kh * p.kw * (p.c / p.block_k);
+  const int num_units = p.num_units;
   // Halo mode (a_mode 3): a ring stage is one channel block: the (patch_w + kw - 1) x
   // (patch_h + kh - 1) input pixels the patch touches, loaded once, then the kh * kw weight tiles.
   // Every filter tap multiplies a window of that halo: the descriptor starts (fy * halo_w + fx)
@@ -276,7 +298,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int resident_bytes = w_resident ? taps * b_bytes : 0;
   uint8_t* const ring = smem + resident_bytes;
   const int stage_bytes = w_resident ? halo_pad : (halo ? halo_pad + taps * b_bytes : p.units * unit_bytes);
-  const int num_kb = halo ? p.c / p.block_k : (num_units + p.units - 1) / p.units;  // ring stages consumed per tile
+  const int num_kb = p.num_kb;  // ring stages consumed per tile
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const bool bias_in_smem = (p.bias != nullptr || p.fast_mode) && p.oc <= MAX_BIAS;
 
@@ -329,9 +351,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   };
   if (bias_in_smem && p.bias_static) stage_bias();
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (threadIdx.x == 0) TRACE(16, 1);
-  if (bias_in_smem && !p.bias_static) stage_bias();
+  if (bias_in_smem && !p.bias_static) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    stage_bias();
+  }
+  // Every role below finishes its own set-up arithmetic first and executes griddepcontrol.wait just
+  // before its loop, so that the set-up overlaps the tail of the previous kernel.
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -346,7 +371,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const bool leader = elect_one();
       const int which = warp == 0 ? 0 : 1;
       if (which == 0 && leader) TRACE(16, 6);
-      int stage = which % p.stages;
+      int stage = which;  // the ring has at least two stages
       uint32_t phase = which >= p.stages ? 1u : 0u;
       int turn = which;  // 0: the next stage is this producer's
       bool live = true;
@@ -373,15 +398,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           kcol += p.c;
         }
       }
+      const TileOrigin to_first = tile_origin(p, (int)blockIdx.x);
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (which == 0 && leader) TRACE(16, 1);
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
-        const TileOrigin to = tile_origin(p, tile);
+        const TileOrigin to = tile == (int)blockIdx.x ? to_first : tile_origin(p, tile);
         const int m0 = to.m0;
         if (which == 0 && tile == (int)blockIdx.x && leader) TRACE(16, 7);
         int img = 0, base_w = 0, base_h = 0;
         if (p.a_mode == 1) {
-          img = m0 / (p.oh * p.ow);
+          img = fdiv(m0, p.fd_ohow);
           const int rem = m0 - img * (p.oh * p.ow);
-          const int oy = rem / p.ow;
+          const int oy = fdiv(rem, p.fd_ow);
           const int ox = rem - oy * p.ow;
           base_w = ox * p.stride_w - p.pad_w;
           base_h = oy * p.stride_h - p.pad_h;
@@ -517,6 +545,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int mseq = 0, tseq = 0; (void)mseq; (void)tseq;
       TDECL;
       TSTART(tl);
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       if (w_resident && blockIdx.x < num_tiles && !mbar_wait(&bar_weights, 0u, &abort_flag, 7)) live = false;
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
         TSTART(tw);
@@ -606,14 +635,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // patch mode: this thread's pixel inside the patch
     int pr_w = 0, pr_h = 0, pr_n = 0;
     if (p.a_mode >= 2) {
-      pr_w = row_in_tile % p.patch_w;
-      const int r = row_in_tile / p.patch_w;
-      pr_h = r % p.patch_h;
-      pr_n = r / p.patch_h;
+      pr_w = row_in_tile & (p.patch_w - 1);
+      const int r = row_in_tile >> p.patch_w_log2;
+      pr_h = r & (p.patch_h - 1);
+      pr_n = r >> p.patch_h_log2;
     }
     int k = 0;  // index of this group's tile
     TDECL;
     (void)leader;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int tile = first_tile; tile < num_tiles; tile += stride_tiles, ++k) {
       const TileOrigin to = tile_origin(p, tile);
       const int n0 = to.n0;
@@ -763,6 +793,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
     };
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // every buffer starts free (or with the operand of its first tile on the way)
     for (int g = 0; g < 2; ++g)
       for (int b = 0; b < p.io_bufs; ++b) hand_back(g, b, (int)blockIdx.x + (2 * b + g) * (int)gridDim.x);
@@ -1103,9 +1134,18 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
     p.patch_w = plan->reserved[0]; p.patch_h = plan->reserved[1]; p.patch_n = plan->reserved[2];
     p.tiles_w = (d.OW + p.patch_w - 1) / p.patch_w;
     p.tiles_h = (d.OH + p.patch_h - 1) / p.patch_h;
+    while ((1 << p.patch_w_log2) < p.patch_w) ++p.patch_w_log2;
+    while ((1 << p.patch_h_log2) < p.patch_h) ++p.patch_h_log2;
     p.num_m_tiles = p.tiles_w * p.tiles_h * ((d.N + p.patch_n - 1) / p.patch_n);
   }
   p.num_n_tiles = (d.OC + plan->block_n - 1) / plan->block_n;
+  p.num_units = d.KH * d.KW * (d.C / plan->block_k);
+  p.num_kb = p.a_mode >= 3 ? d.C / plan->block_k : (p.num_units + p.units - 1) / p.units;
+  p.fd_n_tiles = make_fastdiv(p.num_n_tiles);
+  p.fd_tiles_w = make_fastdiv(p.tiles_w);
+  p.fd_tiles_h = make_fastdiv(p.tiles_h);
+  p.fd_ohow = make_fastdiv(d.OH * d.OW);
+  p.fd_ow = make_fastdiv(d.OW);
   int cols = 2 * plan->block_n;
   int pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
