@@ -6,12 +6,24 @@
 // every malformed model maps to the status the reference returns.
 #pragma once
 #include <cstdint>
+#include <cstdlib>
 #include <sstream>
 #include <stdexcept>
 #include <string>
 #include <vector>
 
 namespace cvm {
+
+// Environment variables that re-route operators exist for experiments only: honoured in builds
+// made with -DCVM_B200_DEV_SWITCHES, ignored by the shipped library.
+inline const char* dev_env(const char* name) {
+#ifdef CVM_B200_DEV_SWITCHES
+  return getenv(name);
+#else
+  (void)name;
+  return nullptr;
+#endif
+}
 
 struct ParamError : public std::runtime_error {
   explicit ParamError(const std::string& s) : std::runtime_error(s) {}

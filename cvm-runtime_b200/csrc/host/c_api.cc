@@ -333,4 +333,11 @@ int CVMXProfileSteps(void* net, const char* input_data, int input_len, char* tex
   API_END();
 }
 
+int CVMXSetStatusWord(void* net, int code) {
+  API_BEGIN();
+  CHECK(net != nullptr);
+  static_cast<Model*>(net)->executor().SetStatusWord(code);
+  API_END();
+}
+
 }  // extern "C"

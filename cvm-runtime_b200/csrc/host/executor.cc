@@ -79,7 +79,7 @@ struct Lowering {
   // divides, else none.
   static int upload_chunks() {
     static const int k = [] {
-      const char* e = getenv("CVM_B200_UPLOAD_CHUNKS");
+      const char* e = dev_env("CVM_B200_UPLOAD_CHUNKS");
       const int v = e ? atoi(e) : 4;
       return v >= 2 && v <= 16 ? v : 4;
     }();
@@ -87,7 +87,7 @@ struct Lowering {
   }
   static int batch_chunks(int64_t n) {
     const int k = upload_chunks();
-    return (n % k == 0 && n >= 2 * k && !getenv("CVM_B200_NO_UPLOAD_OVERLAP")) ? k : 1;
+    return (n % k == 0 && n >= 2 * k && !dev_env("CVM_B200_NO_UPLOAD_OVERLAP")) ? k : 1;
   }
 
   // ------------------------------------------------------------------ analysis
@@ -181,7 +181,7 @@ struct Lowering {
     }
     // NCHW <-> NHWC of one element type: a batched matrix transpose through shared memory
     if (src.nhwc != dst.nhwc && src.shape == dst.shape && src.shape.size() == 4 && src.dtype == dst.dtype &&
-        (!ep || ep->n == 0 || (ep->n == 1 && ep->s[0].op == CVMK_EP_CLIP)) && !getenv("CVM_B200_NO_TILED_TRANSPOSE")) {
+        (!ep || ep->n == 0 || (ep->n == 1 && ep->s[0].op == CVMK_EP_CLIP)) && !dev_env("CVM_B200_NO_TILED_TRANSPOSE")) {
       const Shape& sh = src.shape;
       const int64_t batch = sh[0];
       const int64_t c = sh[1], hw = sh[2] * sh[3];
@@ -415,7 +415,7 @@ struct Lowering {
       probe.acc_bound = (int64_t)icg * KH * KW * 128 * 128 + bias_max;
       probe.bias_static = (!use_bias || g.params.count(g.entry_id(n.inputs[2])) > 0) ? 1 : 0;
     }
-    const bool tc = groups == 1 && cvmk_conv2d_tc_supported(&probe) && !getenv("CVM_B200_NO_TC");
+    const bool tc = groups == 1 && cvmk_conv2d_tc_supported(&probe) && !dev_env("CVM_B200_NO_TC");
     const bool depthwise = !dense && groups == C && OC == C && C % 16 == 0 && safe8[ex_];
     // Few-channel convolutions (image stems): gather patches into a [M, Kp] matrix, then run the
     // tensor-core kernel on it as a 1x1 convolution.
@@ -426,7 +426,7 @@ struct Lowering {
     packed.dil_h = packed.dil_w = 1;
     const bool via_pack = !tc && !dense && groups == 1 && safe8[ex_] && C <= 255 && kflat <= 8192 &&
                           (KW - 1) * dw <= 4095 && (KH - 1) * dh <= 2047 &&
-                          cvmk_conv2d_tc_supported(&packed) && !getenv("CVM_B200_NO_TC");
+                          cvmk_conv2d_tc_supported(&packed) && !dev_env("CVM_B200_NO_TC");
 
     // Output channel counts the tensor-core kernel does not take (not a multiple of 8: detection
     // heads with anchors x classes channels) run on it with zero weight rows up to a multiple of
@@ -434,7 +434,7 @@ struct Lowering {
     // output tensor (no fused tensor operand) and the bias is a parameter.
     const int OCp = (OC + 31) / 32 * 32;
     bool tc_pad = false;
-    if (!tc && !dense && groups == 1 && OC % 8 != 0 && !depthwise && !getenv("CVM_B200_NO_TC")) {
+    if (!tc && !dense && groups == 1 && OC % 8 != 0 && !depthwise && !dev_env("CVM_B200_NO_TC")) {
       cvmk_conv_desc pp = probe;
       pp.OC = OCp;
       bool plain_chain = true;
@@ -464,7 +464,7 @@ struct Lowering {
 
     // Stem on the tensor cores without a patch matrix: the network input itself, few channels.
     if (via_pack && ex_ == data_eid && raw_in.dtype == CVMK_I8 && dh == 1 && dw == 1 && out.dtype == CVMK_I8 &&
-        !getenv("CVM_B200_NO_STEM_FUSED")) {
+        !dev_env("CVM_B200_NO_STEM_FUSED")) {
       cvmk_stem_conv_desc sd;
       memset(&sd, 0, sizeof(sd));
       sd.x = (const int8_t*)raw_in.ptr; sd.y = out.ptr;
@@ -526,7 +526,7 @@ struct Lowering {
       sp.stride_h = sh; sp.stride_w = sw; sp.pad_h = ph; sp.pad_w = pw; sp.dil_h = dh; sp.dil_w = dw;
       sp.Kp = kp; sp.clamp = data_range;
       const bool from_raw = ex_ == data_eid && raw_in.dtype == CVMK_I8 && cvmk_stem_pack_supported(&sp) &&
-                            !getenv("CVM_B200_NO_STEM_PACK");
+                            !dev_env("CVM_B200_NO_STEM_PACK");
       if (from_raw) {  // gather straight from the NCHW input: no channels-last copy of it is needed
         add_step(label + "[stem_pack]", [sp](cudaStream_t s) { return cvmk_stem_pack(&sp, s); });
       }
@@ -1208,7 +1208,7 @@ struct Lowering {
       const bool first = !ex.steps_.empty() && ex.steps_[0].chunk.size() > 1 && ex.steps_[0].label.size() >= tag.size() &&
                          ex.steps_[0].label.compare(ex.steps_[0].label.size() - tag.size(), tag.size(), tag) == 0;
       size_t cap = 6;   // ResNet-50: stem, pooling and the first bottleneck block take about as long as the upload
-      if (const char* e = getenv("CVM_B200_PREFIX_STEPS")) cap = (size_t)atoi(e);
+      if (const char* e = dev_env("CVM_B200_PREFIX_STEPS")) cap = (size_t)atoi(e);
       ex.prefix_steps_ = 0;
       if (first)
         while (ex.prefix_steps_ < ex.steps_.size() && ex.prefix_steps_ < cap && ex.steps_[ex.prefix_steps_].chunk.size() == ex.steps_[0].chunk.size())
@@ -1241,7 +1241,7 @@ Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
   CUDA_OK(cudaMallocHost((void**)&status_host_, 256));
   pinned_.push_back(status_host_);
   *status_host_ = 0;
-  use_graph_ = getenv("CVM_B200_NO_GRAPH") == nullptr;
+  use_graph_ = dev_env("CVM_B200_NO_GRAPH") == nullptr;
   Lowering low(*this, g);
   low.run();
   // One eager pass sets per-kernel attributes and surfaces launch errors before capture.
@@ -1337,6 +1337,13 @@ void Executor::Run(const void* input, size_t input_bytes) {
     cudaStreamSynchronize(stream_);
     FATAL() << "a device-side wait ran out (status word 0x" << std::hex << code << ")";
   }
+}
+
+void Executor::SetStatusWord(int code) {
+  CUDA_OK(cudaSetDevice(device_));
+  const int32_t v = code;
+  CUDA_OK(cudaMemcpyAsync(status_dev_, &v, sizeof(v), cudaMemcpyHostToDevice, stream_));
+  CUDA_OK(cudaStreamSynchronize(stream_));
 }
 
 float Executor::ReplayDevice(int iters) {

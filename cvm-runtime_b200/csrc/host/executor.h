@@ -63,6 +63,8 @@ class Executor {
   // Replays only the kernels (input already in device memory, no upload / download) `iters`
   // times and returns the device time in milliseconds measured with CUDA events on the stream.
   float ReplayDevice(int iters);
+  // Writes `code` into the device status word the kernels report their expired waits in.
+  void SetStatusWord(int code);
 
  private:
   struct Impl;

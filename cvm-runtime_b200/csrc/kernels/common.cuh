@@ -2,9 +2,22 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "cvmk_kernels.h"
 
 namespace cvmk {
+
+// Environment variables that re-route operators or resize tiles exist for experiments only: they
+// are honoured in builds made with -DCVM_B200_DEV_SWITCHES and ignored by the shipped library, whose
+// results and code paths must not depend on the environment of the process that loads it.
+inline const char* dev_env(const char* name) {
+#ifdef CVM_B200_DEV_SWITCHES
+  return getenv(name);
+#else
+  (void)name;
+  return nullptr;
+#endif
+}
 
 void set_error(const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);

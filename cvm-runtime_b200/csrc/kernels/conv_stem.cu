@@ -575,7 +575,7 @@ extern "C" int cvmk_conv2d_stem_launch(const cvmk_stem_conv_plan* plan, cvmk_str
   }
   // packed requantisation: chain = [bias] rs_clamp, same proof obligations as the general kernel
   if (d.acc_bound > 0 && p.chain.n - p.first_step == 1 && p.chain.s[p.first_step].op == K_RS_CLAMP &&
-      !getenv("CVM_B200_NO_FAST_REQUANT")) {
+      !dev_env("CVM_B200_NO_FAST_REQUANT")) {
     const DevStep& rs = p.chain.s[p.first_step];
     const int64_t add = rs.c;
     const int sh = rs.d;

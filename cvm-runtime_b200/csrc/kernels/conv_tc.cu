@@ -966,7 +966,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   memset(plan, 0, sizeof(*plan));
   plan->d = *d;
   int bk = pick_block_k(d->C);
-  if (const char* e = getenv("CVM_B200_BK")) {  // experiments: a smaller K block (must divide C)
+  if (const char* e = dev_env("CVM_B200_BK")) {  // experiments: a smaller K block (must divide C)
     const int v = atoi(e);
     if ((v == 32 || v == 64 || v == 128) && d->C % v == 0 && v <= bk) bk = v;
   }
@@ -974,7 +974,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   plan->block_n = bn;
   int patch_w = 0, patch_h = 0, patch_n = 0;
   plan->a_im2col = is_pointwise(*d) ? 0 : 1;
-  if (plan->a_im2col && d->stride_h == 1 && d->stride_w == 1 && !getenv("CVM_B200_NO_PATCH") &&
+  if (plan->a_im2col && d->stride_h == 1 && d->stride_w == 1 && !dev_env("CVM_B200_NO_PATCH") &&
       pick_patch(*d, &patch_w, &patch_h, &patch_n))
     plan->a_im2col = 2;
   // Halo mode: 3x3 (or any small) stride-1 undilated filters over at most 128 channels and output
@@ -983,7 +983,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   // cross L2 -> shared memory about 1.4 times instead of kh * kw times.
   bool halo = false;
   if (plan->a_im2col == 2 && d->dil_h == 1 && d->dil_w == 1 && d->KH == 3 && d->KW == 3 && d->C % 64 == 0 &&
-      d->C <= 128 && bn <= 128 && d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !getenv("CVM_B200_NO_HALO")) {
+      d->C <= 128 && bn <= 128 && d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !dev_env("CVM_B200_NO_HALO")) {
     const int64_t linear = ((int64_t)d->N * d->OH * d->OW + BLOCK_M - 1) / BLOCK_M;
     const int64_t tiles = (int64_t)((d->OW + 7) / 8) * ((d->OH + 15) / 16) * d->N;
     if (tiles * 20 <= linear * 27) {
@@ -997,7 +997,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
 
   // Output path: int8 tiles leave through shared memory and a TMA store; the first int8 tensor
   // operand of the chain (a residual join) comes in by TMA as well.
-  plan->tma_out = d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !getenv("CVM_B200_NO_TMA_STORE");
+  plan->tma_out = d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !dev_env("CVM_B200_NO_TMA_STORE");
   plan->res_step = -1;
   if (plan->tma_out) {
     for (int i = 0; i < d->ep.n; ++i) {
@@ -1022,14 +1022,14 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   // launch multiplies the same 9 * bn * 64 bytes.  A ring stage is then the 12 KB halo alone.
   const int halo_pad = ((10 * 18 * bk) + 1023) & ~1023;
   int resident = 0;
-  if (halo && d->C == 64 && d->OC <= bn && !getenv("CVM_B200_NO_RESIDENT_WEIGHTS")) {
+  if (halo && d->C == 64 && d->OC <= bn && !dev_env("CVM_B200_NO_RESIDENT_WEIGHTS")) {
     resident = d->KH * d->KW * bn * bk;
     plan->a_im2col = 4;
   }
   const int halo_stage = halo ? (resident ? halo_pad : halo_pad + d->KH * d->KW * bn * bk) : 0;
   if (halo) {
     if (plan->tma_out && (budget - resident - 4 * group_bytes) / halo_stage >= 3) plan->io_bufs = 2;
-  } else if (plan->tma_out && !getenv("CVM_B200_SINGLE_STAGING")) {
+  } else if (plan->tma_out && !dev_env("CVM_B200_SINGLE_STAGING")) {
     auto ring_depth = [&](int k) { return (budget - 4 * group_bytes) / ((BLOCK_M + bn) * k); };
     if (ring_depth(bk) >= 3) plan->io_bufs = 2;
     else if (bk == 128 && k_all <= 512 && ring_depth(64) >= 3) { plan->io_bufs = 2; bk = 64; }
@@ -1044,7 +1044,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   int units = 48 * 1024 / unit_bytes;
   if (units > 4) units = 4;
   if (units > num_units) units = num_units;
-  if (const char* e = getenv("CVM_B200_UNITS")) units = atoi(e);
+  if (const char* e = dev_env("CVM_B200_UNITS")) units = atoi(e);
   while (units > 1 && (budget - io_bytes) / (units * unit_bytes) < 3) --units;
   if (units < 1) units = 1;
   if (halo) units = d->KH * d->KW;
@@ -1185,7 +1185,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
 
   // Packed requantisation: chain = [bias] rs_clamp [add_t|sub_t (the TMA-served operand) clip].
   p.fast_mode = 0;
-  if (p.tma_out && d.acc_bound > 0 && d.OC <= MAX_BIAS && !getenv("CVM_B200_NO_FAST_REQUANT")) {
+  if (p.tma_out && d.acc_bound > 0 && d.OC <= MAX_BIAS && !dev_env("CVM_B200_NO_FAST_REQUANT")) {
     const int i0 = p.first_step;
     const int left = p.chain.n - i0;
     if (left >= 1 && p.chain.s[i0].op == K_RS_CLAMP) {
@@ -1251,7 +1251,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
-  static const bool pdl = getenv("CVM_B200_NO_PDL") == nullptr;
+  static const bool pdl = dev_env("CVM_B200_NO_PDL") == nullptr;
   cfg.attrs = &attr;
   cfg.numAttrs = pdl ? 1 : 0;
   return check_cuda(cudaLaunchKernelEx(&cfg, conv_tc_kernel, ta, tb, ty, tr, p), "conv_tc_kernel launch");

@@ -62,8 +62,8 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_
 // Bounded wait (about a second in all).  Returns false when it gave up, or when another role of
 // this CTA already did.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int code) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+                                          int code, uint32_t limit = SPIN_LIMIT) {
+  for (uint32_t i = 0; i < limit; ++i) {
 #ifdef CVMK_CONV_TIMING
     if (mbar_try(bar, parity, g_wait_hint)) return true;
 #else

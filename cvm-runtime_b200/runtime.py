@@ -10,6 +10,8 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libcvm_runtime.so")
+MEASURE_LIB_PATH = os.path.join(HERE, "libcvm_measure.so")
+MEASURE_SYMBOLS = ["cvmk_measure_i8_mma_rate", "cvmk_measure_wait_timeout", "cvmk_measure_last_error"]
 
 SUCCEED, ERROR_LOGIC, ERROR_RUNTIME = 0, 1, 2
 
@@ -23,7 +25,7 @@ KERNEL_SYMBOLS = [
     "cvmk_im2col_pack", "cvmk_stem_pack", "cvmk_stem_pack_supported",
     "cvmk_conv2d_stem_supported", "cvmk_conv2d_stem_prepare", "cvmk_conv2d_stem_launch",
     "cvmk_conv2d_tc_supported", "cvmk_conv2d_tc_prepare", "cvmk_conv2d_tc_launch", "cvmk_elemwise",
-    "cvmk_measure_i8_mma_rate", "cvmk_transpose_batched", "cvmk_strided", "cvmk_take", "cvmk_where", "cvmk_reduce", "cvmk_max_pool2d", "cvmk_conv2d_direct", "cvmk_get_valid_counts",
+    "cvmk_transpose_batched", "cvmk_strided", "cvmk_take", "cvmk_where", "cvmk_reduce", "cvmk_max_pool2d", "cvmk_conv2d_direct", "cvmk_get_valid_counts",
     "cvmk_nms_scratch_bytes", "cvmk_non_max_suppression", "cvmk_non_max_suppression_static",
     "cvmk_last_error",
 ]
@@ -52,6 +54,20 @@ def lib():
         _LIB.CVMXLastError.restype = ctypes.c_char_p
         _LIB.cvmk_nms_scratch_bytes.restype = ctypes.c_int64
     return _LIB
+
+
+_MEASURE = None
+
+
+def measure_lib():
+    """libcvm_measure.so: measurement and self-test helpers, kept out of the runtime library."""
+    global _MEASURE
+    if _MEASURE is None:
+        if not os.path.exists(MEASURE_LIB_PATH):
+            raise OSError("%s not found: build it with `python cvm-runtime_b200/build.py`" % MEASURE_LIB_PATH)
+        _MEASURE = ctypes.CDLL(MEASURE_LIB_PATH)
+        _MEASURE.cvmk_measure_last_error.restype = ctypes.c_char_p
+    return _MEASURE
 
 
 def last_error():
@@ -180,10 +196,26 @@ def measure_i8_mma_rate(n=256, reps=20000):
     """Measured int8 tensor-core rate of the current GPU in TOP/s (tcgen05.mma kind::i8, M = 128,
     N = n, K = 32 issued back to back on every SM)."""
     tops = ctypes.c_double()
-    rc = lib().cvmk_measure_i8_mma_rate(ctypes.c_int(n), ctypes.c_int(reps), ctypes.byref(tops))
+    rc = measure_lib().cvmk_measure_i8_mma_rate(ctypes.c_int(n), ctypes.c_int(reps), ctypes.byref(tops))
     if rc != 0:
-        raise RuntimeError("cvmk_measure_i8_mma_rate failed (%d): %s" % (rc, lib().cvmk_last_error().decode()))
+        raise RuntimeError("cvmk_measure_i8_mma_rate failed (%d): %s" % (rc, measure_lib().cvmk_measure_last_error().decode()))
     return tops.value
+
+
+def wait_timeout(limit=64):
+    """Lets a bounded device-side wait run out (a barrier nothing arrives at, `limit` polls of about
+    2 us); returns (status word, SM clocks waited)."""
+    word, clocks = ctypes.c_int(0), ctypes.c_longlong(0)
+    rc = measure_lib().cvmk_measure_wait_timeout(ctypes.c_uint(limit), ctypes.byref(word), ctypes.byref(clocks))
+    if rc != 0:
+        raise RuntimeError("cvmk_measure_wait_timeout failed (%d): %s" % (rc, measure_lib().cvmk_measure_last_error().decode()))
+    return word.value, clocks.value
+
+
+def set_status_word(net, code):
+    """Writes `code` into the model's device status word, as a kernel whose bounded wait ran out
+    would (include/cvm/c_api_ext.h)."""
+    check_call(lib().CVMXSetStatusWord(net, ctypes.c_int(code)), "CVMXSetStatusWord")
 
 
 def profile_steps(net, input_data):

@@ -32,6 +32,12 @@ CVM_DLL int CVMXReplayDevice(void* net, int iters, float* total_ms);
 CVM_DLL int CVMXProfileSteps(void* net, const char* input_data, int input_len, char* text,
                              int text_len);
 
+/* Writes `code` into the model's device status word: the word every tensor-core kernel ORs a
+ * non-zero value into when one of its bounded waits runs out.  The next CVMAPIInference on the
+ * handle then answers ERROR_RUNTIME, clears the word and leaves the handle usable.  Exists so that
+ * this error path can be exercised without making a kernel fail. */
+CVM_DLL int CVMXSetStatusWord(void* net, int code);
+
 #ifdef __cplusplus
 }
 #endif

@@ -370,6 +370,8 @@ CVMK_API int cvmk_non_max_suppression(const cvmk_nms_desc* d, cvmk_stream_t stre
  *   - The first call on each device resolves the device address of the array (one
  *     cudaGetSymbolAddress); make that first call before starting a stream capture.  No call
  *     allocates or frees memory.
+ *   - x is never written: the variant has no x_writeback (the top_k side effect of the CPU operator
+ *     on its input, see cvmk_nms_desc); a caller that needs it uses cvmk_non_max_suppression().
  *   - All calls on a device share the one array and it keeps whatever the previous call left.
  *     The kernel writes every scratch word before reading it, so nothing has to be cleared, but
  *     two calls whose kernels overlap on the GPU (different streams) race on it: serialise them.
@@ -388,12 +390,6 @@ CVMK_API int cvmk_non_max_suppression_static(const int32_t* x, const int32_t* va
  * ---------------------------------------------------------------------------------------------- */
 CVMK_API int cvmk_transpose_batched(const void* x, void* y, int32_t dtype, int64_t batch, int32_t rows,
                                     int32_t cols, int32_t clamp, int32_t lo, int32_t hi, cvmk_stream_t stream);
-
-/* Measurement helper (no counterpart in the reference): the int8 tensor-core rate of the current
- * GPU in TOP/s (2 * MACs), measured by issuing `reps` tcgen05.mma kind::i8 instructions of shape
- * M = 128, N = n, K = 32 per SM on operands resident in shared memory and timing the launch with
- * CUDA events.  bench.py uses n = 256 as the denominator of the tensor roofline. */
-CVMK_API int cvmk_measure_i8_mma_rate(int n, int reps, double* tops);
 
 /* Text of the last CUDA / argument error seen by a launcher on this thread. */
 CVMK_API const char* cvmk_last_error(void);

@@ -69,6 +69,27 @@ def model_cases():
     }
 
 
+def fullsize_cases():
+    """The benchmark configurations at (or near) their real sizes.  Too large for byte fixtures: the
+    golden file keeps the SHA-256 and the length of the reference CPU runtime's output."""
+    return {
+        "conv_chain_b16": lambda: wl.conv_chain(batch=16),
+        "resnet50_b32": lambda: wl.resnet50(batch=32),
+        "mobilenet_b32": lambda: wl.mobilenet_v1(batch=32),
+        "vgg19_b4": lambda: wl.vgg19(batch=4),
+        "ssd_tail_b64_t16384": lambda: wl.ssd_tail(batch=64),
+        "ssd_tail_b64_t100": lambda: wl.ssd_tail(batch=64, score_threshold=100),
+        # fewer valid rows than top_k (about 125 of 24564 score above 32600)
+        "ssd_tail_b64_t32600": lambda: wl.ssd_tail(batch=64, score_threshold=32600),
+        # no top_k limit: every valid row (about half of them) goes through the suppression sweep
+        "ssd_tail_b4_all_rows": lambda: wl.ssd_tail(batch=4, top_k=-1),
+        "ssd_tail_b4_force_out100": lambda: wl.ssd_tail(batch=4, top_k=2000, max_output_size=100, force_suppress=True),
+        "ssd_backbone_512_b1": lambda: wl.ssd_backbone(batch=1),
+        "ssd_full_512_b1": lambda: wl.ssd_full(batch=1, size=512, classes=21),
+        "ssd_full_512_b2": lambda: wl.ssd_full(batch=2, size=512, classes=21),
+    }
+
+
 def op_cases():
     """name -> thunk for single-operator graphs, edge cases included."""
     c = {}

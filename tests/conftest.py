@@ -60,6 +60,13 @@ def golden_random():
 
 
 @pytest.fixture(scope="session")
+def golden_fullsize():
+    d = np.load(os.path.join(ROOT, "tests", "golden", "fullsize.npz"))
+    return {n: (str(s), int(b), str(i)) for n, s, b, i in zip(d["names"].tolist(), d["sha"].tolist(),
+                                                              d["nbytes"].tolist(), d["input_sha"].tolist())}
+
+
+@pytest.fixture(scope="session")
 def gpu_run(rt):
     """Runs (json, params, input) through the C-ABI on cuda:0 and returns the output bytes."""
     def run(js, pb, x, device=0):

@@ -2,7 +2,8 @@
 `make -C oracle ref` from the unmodified reference sources).  Run in a container that has the
 reference tree; the fixtures it writes are committed and travel where the reference does not.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py              # everything
+    python tests/golden/make_golden.py --fullsize   # only the digests of the full-size configurations
 """
 import hashlib
 import os
@@ -53,6 +54,26 @@ def main():
     print("wrote %d outputs, %d load statuses" % (len(out) // 3, len(status)))
     for k, v in status.items():
         print("  %-28s -> %d" % (k, v))
+
+
+def fullsize_golden():
+    """tests/golden/fullsize.npz: SHA-256 and length of the reference's output on the full-size
+    configurations of tests/cases.py (one process each: some of them hold gigabytes)."""
+    names = list(cases.fullsize_cases())
+    digests, sizes, inputs = [], [], []
+    for name in names:
+        code = ("import sys, hashlib; sys.path.insert(0, %r); import cases, numpy as np; o = cases.ge.load_oracle(); "
+                "js, pb, x = cases.fullsize_cases()[%r](); y = o.ref_lib.run_model(js, pb, x); "
+                "sys.stdout.write('\\nDIGEST %%s %%d %%s\\n' %% (hashlib.sha256(y.tobytes()).hexdigest(), y.nbytes, "
+                "hashlib.sha256(np.ascontiguousarray(x).tobytes()).hexdigest()))" % (os.path.dirname(HERE), name))
+        out = subprocess.run([sys.executable, "-c", code], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, check=True).stdout
+        line = [l for l in out.splitlines() if l.startswith("DIGEST ")][-1].split()
+        digests.append(line[1])
+        sizes.append(int(line[2]))
+        inputs.append(line[3])
+        print("  %-24s %s %d" % (name, line[1][:16], int(line[2])))
+    np.savez(os.path.join(HERE, "fullsize.npz"), names=np.array(names), sha=np.array(digests),
+             nbytes=np.array(sizes, np.int64), input_sha=np.array(inputs))
 
 
 def fuzz_worker(start, path):
@@ -199,7 +220,10 @@ if __name__ == "__main__":
         fuzz_worker(int(sys.argv[2]), sys.argv[3])
     elif len(sys.argv) > 1 and sys.argv[1] == "--fuzz":
         fuzz_golden()
+    elif len(sys.argv) > 1 and sys.argv[1] == "--fullsize":
+        fullsize_golden()
     else:
         main()
         fuzz_golden()
         random_golden()
+        fullsize_golden()

@@ -30,6 +30,17 @@ def test_library_exports_every_declared_symbol(rt):
         assert hasattr(lib, n), "libcvm_runtime.so does not export " + n
 
 
+def test_measure_library_exports_its_symbols(rt):
+    """libcvm_measure.so (measurement / self-test helpers) is a library of its own: the runtime
+    library exports none of its symbols."""
+    text = open(os.path.join(ROOT, "include/cvmk_measure.h")).read()
+    names = re.findall(r"^CVMK_API\s+[\w\s\*]*?\b(\w+)\s*\(", text, flags=re.M)
+    assert sorted(names) == sorted(rt.MEASURE_SYMBOLS)
+    for n in names:
+        assert hasattr(rt.measure_lib(), n), "libcvm_measure.so does not export " + n
+        assert not hasattr(rt.lib(), n), "libcvm_runtime.so should not export " + n
+
+
 def test_gas_matches_reference(rt, golden):
     for group, table in (("model", cases.model_cases()), ("op", cases.op_cases())):
         for name, thunk in table.items():

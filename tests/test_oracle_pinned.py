@@ -44,6 +44,17 @@ def test_oracle_matches_reference_library(name, oracle):
     assert np.array_equal(oracle.run_model(js, pb, x), oracle.ref_lib.run_model(js, pb, x))
 
 
+@pytest.mark.parametrize("name", ["conv_chain_b16", "ssd_tail_b64_t32600", "ssd_full_512_b1"])
+def test_oracle_matches_fullsize_digest(name, oracle, golden_fullsize):
+    """The numpy restatement against the reference's digests of the full-size configurations (the
+    ones it finishes in seconds; the GPU suite checks all of them)."""
+    js, pb, x = cases.fullsize_cases()[name]()
+    want_sha, want_len, input_sha = golden_fullsize[name]
+    assert hashlib.sha256(np.ascontiguousarray(x).tobytes()).hexdigest() == input_sha
+    out = oracle.run_model(js, pb, x)
+    assert out.nbytes == want_len and hashlib.sha256(out.tobytes()).hexdigest() == want_sha
+
+
 def test_right_shift_corners(oracle):
     """Branch structure of cpu/ops/elemwise.cc:129-147 on hand-checked values."""
     f = oracle.cvm_oracle.cvm_right_shift

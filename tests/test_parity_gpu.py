@@ -267,6 +267,26 @@ def test_random_graphs_match_the_reference(rt, golden_random):
 
 
 # ---------------------------------------------------------------------------------------------
+# full-size configurations: SHA-256 of the reference CPU runtime's own output
+# ---------------------------------------------------------------------------------------------
+FULLSIZE = list(cases.fullsize_cases())
+
+
+@pytest.mark.parametrize("name", FULLSIZE)
+def test_fullsize_matches_reference_digest(name, gpu_run, golden_fullsize):
+    """The benchmark configurations at their real sizes (512 x 512 SSD graphs, 24564-anchor tails at
+    batch 64, ResNet-50 / MobileNet batch 32, VGG-19 batch 4): the bytes CVMAPIInference returns
+    hash to what the reference CPU runtime returned for the same model and input."""
+    import hashlib
+    js, pb, x = cases.fullsize_cases()[name]()
+    want_sha, want_len, input_sha = golden_fullsize[name]
+    assert hashlib.sha256(np.ascontiguousarray(x).tobytes()).hexdigest() == input_sha, "the seeded input changed"
+    got = gpu_run(js, pb, x)
+    assert got.nbytes == want_len
+    assert hashlib.sha256(got.tobytes()).hexdigest() == want_sha, "differs from the reference's output"
+
+
+# ---------------------------------------------------------------------------------------------
 # full-size configurations: size-independent properties
 # ---------------------------------------------------------------------------------------------
 def test_resnet50_batch256_batch_independence(rt, gpu_run, oracle, wl):
