@@ -306,8 +306,29 @@ struct Lowering {
     return true;
   }
 
-  // Greedily absorb single-consumer element-wise successors of entry `start`.
+  // non_max_suppression nodes that overwrite rows of their INPUT entry (the CPU operator's side
+  // effect, nms.cc:93-97, reproduced when that entry is read again): (node, entry) pairs.  They are
+  // the only in-place writers of the graph, so they are the only thing a deferred read can miss.
+  std::vector<std::pair<uint32_t, uint32_t>> input_writers;
+  void find_input_writers() {
+    for (uint32_t nid = 0; nid < g.nodes.size(); ++nid) {
+      const Node& n = g.nodes[nid];
+      if (n.is_variable() || n.op->name != "non_max_suppression" || n.attrs.i("top_k") <= 0) continue;
+      const uint32_t in_eid = g.entry_id(n.inputs[0]);
+      bool observed = false;
+      for (const auto& h : g.outputs) observed |= g.entry_id(h) == in_eid;
+      for (uint32_t m = nid + 1; m < g.nodes.size(); ++m)
+        for (const auto& e : g.nodes[m].inputs) observed |= g.entry_id(e) == in_eid;
+      if (observed) input_writers.emplace_back(nid, in_eid);
+    }
+  }
+
+  // Greedily absorb single-consumer element-wise successors of entry `start`.  A fused group runs
+  // at the position of its last member, so every read of the group happens there: a member that
+  // reads an entry BEFORE a node that overwrites it in place must not be carried past that node.
   void extend_chain(Chain* c) {
+    std::vector<std::pair<uint32_t, uint32_t>> reads;   // (entry, reading node)
+    for (const auto& e : g.nodes[c->tail_nid].inputs) reads.emplace_back(g.entry_id(e), c->tail_nid);
     while (c->ep.n < CVMK_MAX_EP_STEPS) {
       const uint32_t cur = c->tail_eid;
       if (is_head[cur] || uses[cur] != 1) break;
@@ -316,8 +337,15 @@ struct Lowering {
         for (const auto& e : g.nodes[nid].inputs)
           if (g.entry_id(e) == cur) { consumer = nid; break; }
       if (consumer == UINT32_MAX || absorbed[consumer]) break;  // e.g. a join taken by its other branch
+      bool crosses_writer = false;
+      for (const auto& w : input_writers)
+        for (const auto& r : reads)
+          crosses_writer |= r.first == w.second && r.second < w.first && w.first < consumer;
+      if (crosses_writer) break;
       cvmk_ep_step st;
       if (!node_as_step(consumer, cur, &st)) break;
+      for (const auto& e : g.nodes[consumer].inputs)
+        if (g.entry_id(e) != cur) reads.emplace_back(g.entry_id(e), consumer);
       c->ep.s[c->ep.n++] = st;
       absorbed[consumer] = 1;
       c->tail_nid = consumer;
@@ -1142,6 +1170,7 @@ struct Lowering {
 
   void run() {
     analyse();
+    find_input_writers();
     // graph input: raw API bytes -> clamp to the declared precision -> entry buffer
     int data_nid = -1;
     for (uint32_t nid = 0; nid < g.nodes.size(); ++nid)
@@ -1275,9 +1304,69 @@ Executor::~Executor() {
   if (stream_) cudaStreamDestroy(stream_);
 }
 
+StagePool::StagePool(int threads) {
+  for (int i = 0; i < threads; ++i) workers_.emplace_back([this] { Work(); });
+}
+
+StagePool::~StagePool() {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    stop_ = true;
+  }
+  cv_.notify_all();
+  for (auto& t : workers_) t.join();
+}
+
+void StagePool::Start(const char* src, char* dst, size_t bytes, size_t piece) {
+  std::lock_guard<std::mutex> lk(mu_);
+  src_ = src; dst_ = dst; bytes_ = bytes; piece_ = piece;
+  pieces_ = (bytes + piece - 1) / piece;
+  if (pieces_ > done_cap_) {
+    done_.reset(new std::atomic<int>[pieces_]);
+    done_cap_ = pieces_;
+  }
+  for (size_t k = 0; k < pieces_; ++k) done_[k].store(0, std::memory_order_relaxed);
+  next_.store(0, std::memory_order_release);
+  ++job_;
+  cv_.notify_all();
+}
+
+void StagePool::Work() {
+  uint64_t seen = 0;
+  for (;;) {
+    {
+      std::unique_lock<std::mutex> lk(mu_);
+      cv_.wait(lk, [&] { return stop_ || job_ != seen; });
+      if (stop_) return;
+      seen = job_;
+    }
+    for (;;) {
+      const size_t k = next_.fetch_add(1, std::memory_order_acq_rel);
+      if (k >= pieces_) break;
+      const size_t off = k * piece_;
+      memcpy(dst_ + off, src_ + off, std::min(piece_, bytes_ - off));
+      done_[k].store(1, std::memory_order_release);
+    }
+  }
+}
+
+void StagePool::WaitPiece(size_t k) {
+  // the caller helps out instead of idling: pieces are small, so this never waits long
+  while (!done_[k].load(std::memory_order_acquire)) {
+    const size_t j = next_.fetch_add(1, std::memory_order_acq_rel);
+    if (j < pieces_) {
+      const size_t off = j * piece_;
+      memcpy(dst_ + off, src_ + off, std::min(piece_, bytes_ - off));
+      done_[j].store(1, std::memory_order_release);
+    } else {
+      std::this_thread::yield();
+    }
+  }
+}
+
 // Queues the upload of one input.  Page-locked (or device) memory is read where it lies; pageable
-// memory goes through the pinned staging buffer in chunks, so that the host copy of one chunk
-// overlaps the transfer of the previous one.
+// memory goes through the pinned staging buffer in pieces that a few host threads copy in
+// parallel, each piece being sent to the device as soon as it is staged.
 void Executor::Upload(const void* input, cudaStream_t s) { UploadRange(input, 0, in_bytes_, s); }
 
 void Executor::UploadRange(const void* input, size_t begin, size_t bytes, cudaStream_t s) {
@@ -1291,10 +1380,28 @@ void Executor::UploadRange(const void* input, size_t begin, size_t bytes, cudaSt
     CUDA_OK(cudaMemcpyAsync((char*)in_dev_ + begin, (const char*)input + begin, bytes, cudaMemcpyDefault, s));
     return;
   }
-  const size_t chunk = (size_t)4 << 20;
-  for (size_t off = begin; off < begin + bytes; off += chunk) {
-    const size_t n = std::min(chunk, begin + bytes - off);
-    memcpy((char*)in_host_ + off, (const char*)input + off, n);
+  const size_t piece = (size_t)1 << 20;
+  if (bytes <= 2 * piece) {   // small inputs: not worth waking anyone
+    memcpy((char*)in_host_ + begin, (const char*)input + begin, bytes);
+    CUDA_OK(cudaMemcpyAsync((char*)in_dev_ + begin, (char*)in_host_ + begin, bytes, cudaMemcpyHostToDevice, s));
+    return;
+  }
+  if (!stage_pool_) {
+    unsigned hw = std::thread::hardware_concurrency();
+    int gpus = 1;
+    cudaGetDeviceCount(&gpus);
+    // three helpers beside the calling thread, fewer when the host has few cores per GPU
+    int helpers = hw ? std::max(1, std::min(3, (int)hw / std::max(1, gpus) - 1)) : 1;
+    stage_pool_.reset(new StagePool(helpers));
+  }
+  stage_pool_->Start((const char*)input + begin, (char*)in_host_ + begin, bytes, piece);
+  // the transfer is issued in groups of four pieces: fewer driver calls, still well pipelined
+  const size_t group = 4;
+  for (size_t k = 0; k < stage_pool_->pieces(); k += group) {
+    const size_t last = std::min(stage_pool_->pieces(), k + group);
+    for (size_t j = k; j < last; ++j) stage_pool_->WaitPiece(j);
+    const size_t off = begin + k * piece;
+    const size_t n = std::min(group * piece, begin + bytes - off);
     CUDA_OK(cudaMemcpyAsync((char*)in_dev_ + off, (char*)in_host_ + off, n, cudaMemcpyHostToDevice, s));
   }
 }

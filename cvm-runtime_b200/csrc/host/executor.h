@@ -15,9 +15,13 @@
 // There is no CPU fallback: every step is a CUDA kernel from this library.
 #pragma once
 #include <cuda_runtime.h>
+#include <atomic>
+#include <condition_variable>
 #include <functional>
 #include <memory>
+#include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 #include "cvmk_kernels.h"
 #include "graph.h"
@@ -46,6 +50,34 @@ struct HeadOut {
   void* dev = nullptr;       // canonical row-major copy on the device
   void* host = nullptr;      // pinned
   size_t bytes = 0;
+};
+
+// A few host threads that copy a pageable caller buffer into the page-locked staging buffer piece
+// by piece, so that the copy runs at several times one core's memcpy rate and the transfer of a
+// piece to the device starts as soon as that piece is staged.
+class StagePool {
+ public:
+  explicit StagePool(int threads);
+  ~StagePool();
+  // Starts copying [src, src + bytes) to dst in pieces of `piece` bytes; returns at once.
+  void Start(const char* src, char* dst, size_t bytes, size_t piece);
+  // Blocks until piece k (0-based) of the current job has been copied.
+  void WaitPiece(size_t k);
+  size_t pieces() const { return pieces_; }
+
+ private:
+  void Work();
+  std::vector<std::thread> workers_;
+  std::mutex mu_;
+  std::condition_variable cv_;
+  bool stop_ = false;
+  uint64_t job_ = 0;                 // generation counter: a new value wakes the workers
+  const char* src_ = nullptr;
+  char* dst_ = nullptr;
+  size_t bytes_ = 0, piece_ = 0, pieces_ = 0;
+  std::atomic<size_t> next_{0};
+  std::unique_ptr<std::atomic<int>[]> done_;
+  size_t done_cap_ = 0;
 };
 
 class Executor {
@@ -92,6 +124,7 @@ class Executor {
   // upload / stem overlap: per-chunk stem plans, the copy stream and one event per chunk
   cudaStream_t copy_stream_ = nullptr;
   std::vector<cudaEvent_t> chunk_events_;
+  std::unique_ptr<StagePool> stage_pool_;   // created by the first inference from pageable memory
 
   void* dalloc(size_t bytes);
   void Upload(const void* input, cudaStream_t s);

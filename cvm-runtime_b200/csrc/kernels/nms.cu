@@ -196,13 +196,13 @@ struct NmsParams {
   int npad;
   int key_cap;            // score keys that fit the dynamic shared memory behind the work area
   int fill_bound;         // rows from here on are -1 whatever the data says (top_k / max_output_size)
+  int dbg;                // development builds: bit 0 skips the IoU tests, bit 1 the pair gathering
 };
 
 constexpr int TB = 512;            // sweep block
 constexpr int TW = TB / 32;        // words per bit row
 
-constexpr int PAIRS_PER_WARP = 256; // same-class pairs a warp gathers before it runs their IoU tests
-constexpr int PAIR_CAP = PAIRS_PER_WARP * WARPS;
+constexpr int PAIR_CAP = 64 * TW + TB + 4;   // 64 bucket rows of TW words + (TB + 1) prefix sums
 struct SweepSmem {
   int32_t box[TB][5];              // id, x1, y1, x2, y2 of the block's sorted boxes
   int32_t stop[TB];
@@ -210,7 +210,7 @@ struct SweepSmem {
   uint32_t removed_bits[TW];
   int32_t kept_list[TB];
   int32_t kept_count;
-  uint32_t pairs[PAIR_CAP];        // per warp: (i << 16) | j
+  uint32_t pairs[PAIR_CAP];        // work area of the pair enumeration: bucket rows, prefix sums
 };
 struct SortSmem {
   int hist[256];
@@ -250,6 +250,20 @@ __device__ __forceinline__ bool iou_ge(const int32_t* a, const int32_t* b, int t
   // inter / uni >= thr  <=>  inter >= thr * uni   (uni > 0, thr > 0), in 128 bits
   const unsigned __int128 rhs = (unsigned __int128)(uint64_t)uni * (uint64_t)(uint32_t)thr;
   return (unsigned __int128)(uint64_t)inter >= rhs;
+}
+
+// The same test when every coordinate of both boxes lies in [-32768, 32767] and thr <= 2^20: areas
+// stay below 2^33 and both sides of the comparison below 2^54, so plain 64-bit arithmetic gives the
+// result of the general form above (whose overflow branch cannot be taken).
+__device__ __forceinline__ bool iou_ge_small(const int32_t* a, const int32_t* b, int thr) {
+  const int64_t sum_area = (int64_t)(a[2] - a[0]) * (a[3] - a[1]) + (int64_t)(b[2] - b[0]) * (b[3] - b[1]);
+  if (sum_area <= 0) return false;
+  const int32_t w = max(0, min(a[2], b[2]) - max(a[0], b[0]));
+  const int32_t h = max(0, min(a[3], b[3]) - max(a[1], b[1]));
+  const int64_t inter = (int64_t)h * w;
+  const int64_t uni = sum_area - inter;
+  if (uni <= 0) return false;
+  return inter * 100 >= (int64_t)thr * uni;
 }
 
 __global__ void __launch_bounds__(THREADS) nms_kernel(const __grid_constant__ NmsParams p) {
@@ -564,13 +578,18 @@ __global__ void __launch_bounds__(THREADS) nms_kernel(const __grid_constant__ Nm
   PHASE(4);
   for (int b0 = 0; b0 < keep; b0 += TB) {
     const int nb = min(TB, keep - b0);
+    bool small_here = true;
     for (int i = tid; i < nb; i += THREADS) {
       const int32_t* row = xb + (size_t)order[b0 + i] * 6;
       sm.sweep.box[i][0] = row[0];
       sm.sweep.box[i][1] = row[2]; sm.sweep.box[i][2] = row[3];
       sm.sweep.box[i][3] = row[4]; sm.sweep.box[i][4] = row[5];
       sm.sweep.stop[i] = stop[b0 + i];
+#pragma unroll
+      for (int e = 2; e < 6; ++e) small_here &= row[e] >= -32768 && row[e] <= 32767;
     }
+    // every box of the block has 16-bit coordinates: the cheap form of the IoU test applies
+    const bool small = __syncthreads_and(small_here ? 1 : 0) != 0 && p.thr <= (1 << 20);
     if (tid < TW) {
       uint32_t bits = 0;
       for (int k = 0; k < 32; ++k) {
@@ -585,52 +604,72 @@ __global__ void __launch_bounds__(THREADS) nms_kernel(const __grid_constant__ Nm
     // box[][5] fall into different banks) and a ballot assembles the word.
     //
     // With class-aware suppression only about one pair in (number of classes) needs an IoU test,
-    // and a warp that runs the test for one lane pays for all 32.  So every warp first gathers the
-    // same-class pairs of its rows into a list of its own (a cheap comparison per pair) and then
-    // runs the tests densely over the list, setting bits with shared-memory atomics; a full list is
-    // worked off and started again.  Forced suppression tests every pair in place.
+    // and a warp that runs the test for one lane pays for all 32.  So the same-class pairs are
+    // enumerated first, without looking at every pair: the boxes are dropped into 64 buckets by a
+    // hash of their class id, one 512-bit occupancy row per bucket; box i's candidates are the bits
+    // of its bucket's row between i and its stop position.  A prefix sum over the candidate counts
+    // numbers all candidate pairs of the block, and the threads then take pairs, not rows: find
+    // the row by bisection, the k-th candidate bit with __fns, check the class (a bucket can hold
+    // two classes), run the IoU test and set the bit.  Forced suppression, or a block with so
+    // many candidates that the dense walk is cheaper (one or two classes), tests every pair in place.
     {
       const int words = (nb + 31) >> 5;
-      const bool listed = !p.force;
-      if (b0 == 0) PHASE(14);
+      bool listed = !p.force;
       if (listed) {
+        uint32_t (*bucket)[TW] = reinterpret_cast<uint32_t (*)[TW]>(sm.sweep.pairs);          // [64][TW]
+        int* prefix = reinterpret_cast<int*>(sm.sweep.pairs + 64 * TW);                        // [nb + 1]
+        auto hash = [](int32_t id) { return ((uint32_t)id * 0x9E3779B1u) >> 26; };
         for (int e = tid; e < nb * TW; e += THREADS) (&sm.sweep.mask[0][0])[e] = 0;
+        for (int e = tid; e < 64 * TW; e += THREADS) (&bucket[0][0])[e] = 0;
         __syncthreads();
-        if (b0 == 0) PHASE(15);
-        uint32_t* mylist = sm.sweep.pairs + warp * PAIRS_PER_WARP;
-        int cnt = 0;
-        auto work_off = [&]() {
-          __syncwarp();
-          for (int e = lane; e < cnt; e += 32) {
-            const uint32_t pr = mylist[e];
-            const int i = (int)(pr >> 16), j = (int)(pr & 0xffffu);
-            if (iou_ge(&sm.sweep.box[i][1], &sm.sweep.box[j][1], p.thr)) atomicOr(&sm.sweep.mask[i][j >> 5], 1u << (j & 31));
-          }
-          __syncwarp();
-          cnt = 0;
+        for (int i = tid; i < nb; i += THREADS) atomicOr(&bucket[hash(sm.sweep.box[i][0])][i >> 5], 1u << (i & 31));
+        __syncthreads();
+        // candidate bits of row i in word w: same bucket, after i, before the row's stop position
+        auto candidates = [&](int i, int w, int last) -> uint32_t {
+          uint32_t bits = bucket[hash(sm.sweep.box[i][0])][w];
+          if (w == (i >> 5)) bits &= (i & 31) == 31 ? 0u : ~0u << ((i & 31) + 1);
+          else if (w < (i >> 5)) bits = 0;
+          if (w == (last >> 5)) bits &= (last & 31) == 0 ? 0u : ~0u >> (32 - (last & 31));
+          else if (w > (last >> 5)) bits = 0;
+          return bits;
         };
-        // class id of box 32 * w + lane, for every word, in registers
-        int32_t idw[TW];
-#pragma unroll
-        for (int w = 0; w < TW; ++w) idw[w] = (w * 32 + lane < nb) ? sm.sweep.box[w * 32 + lane][0] : 0;
-        for (int i = warp; i < nb; i += WARPS) {
-          const int32_t idi = sm.sweep.box[i][0];
-          const int st = sm.sweep.stop[i] - b0;
-          const int w_first = (i + 1) >> 5;
-#pragma unroll
-          for (int w = 0; w < TW; ++w) {
-            if (w < w_first || w >= words || w * 32 >= st) continue;   // the same for the whole warp
-            const int j = w * 32 + lane;
-            const bool match = idi == idw[w] && j > i && j < nb && j < st;
-            const uint32_t m = __ballot_sync(0xffffffffu, match);
-            if (m) {
-              if (match) mylist[cnt + __popc(m & ((1u << lane) - 1u))] = ((uint32_t)i << 16) | (uint32_t)j;
-              cnt += __popc(m);
-              if (cnt > PAIRS_PER_WARP - 32) work_off();
+        int mine = 0;
+        const int row_t = tid;       // THREADS >= TB: one row per thread
+        int last_t = 0;
+        if (row_t < nb) {
+          last_t = min(sm.sweep.stop[row_t] - b0, nb);     // candidates j < last
+          for (int w = row_t >> 5; w < words; ++w) mine += __popc(candidates(row_t, w, last_t));
+        }
+        int total_pairs;
+        const int before = block_exclusive_scan(mine, ws, &total_pairs);
+        if (row_t < nb) prefix[row_t] = before;
+        if (tid == 0) prefix[nb] = total_pairs;
+        __syncthreads();
+        if (total_pairs > 24 * 1024) {
+          listed = false;           // uniform; the dense walk below fills the whole mask itself
+        } else {
+          for (int e = tid; e < total_pairs && !(p.dbg & 1); e += THREADS) {
+            int lo = 0, hi = nb - 1;  // the last row whose prefix is <= e
+            while (lo < hi) {
+              const int mid = (lo + hi + 1) >> 1;
+              if (prefix[mid] <= e) lo = mid; else hi = mid - 1;
             }
+            const int i = lo;
+            int k = e - prefix[i];
+            const int last = min(sm.sweep.stop[i] - b0, nb);
+            int j = -1;
+            for (int w = i >> 5; w < words; ++w) {
+              const uint32_t bits = candidates(i, w, last);
+              const int c = __popc(bits);
+              if (k < c) { j = w * 32 + (int)__fns(bits, 0, k + 1); break; }
+              k -= c;
+            }
+            if (j < 0 || sm.sweep.box[j][0] != sm.sweep.box[i][0]) continue;
+            const bool hit = small ? iou_ge_small(&sm.sweep.box[i][1], &sm.sweep.box[j][1], p.thr)
+                                   : iou_ge(&sm.sweep.box[i][1], &sm.sweep.box[j][1], p.thr);
+            if (hit) atomicOr(&sm.sweep.mask[i][j >> 5], 1u << (j & 31));
           }
         }
-        work_off();
       }
       if (!listed) {
         __syncthreads();
@@ -644,7 +683,7 @@ __global__ void __launch_bounds__(THREADS) nms_kernel(const __grid_constant__ Nm
               const int j = w * 32 + lane;
               bool hit = false;
               if (j > i && j < nb && j < st && (p.force || idi == sm.sweep.box[j][0]))
-                hit = iou_ge(bi, &sm.sweep.box[j][1], p.thr);
+                hit = small ? iou_ge_small(bi, &sm.sweep.box[j][1], p.thr) : iou_ge(bi, &sm.sweep.box[j][1], p.thr);
               bits = __ballot_sync(0xffffffffu, hit);
             }
             if (lane == 0) sm.sweep.mask[i][w] = bits;
@@ -806,6 +845,10 @@ static int nms_launch(NmsParams& p, cudaStream_t stream, const char* what) {
   if (p.topk >= 0) bound = std::min(bound, p.topk);
   if (p.mos > 0) bound = std::min(bound, p.mos);
   p.fill_bound = bound;
+  p.dbg = 0;
+#ifdef CVMK_NMS_TIMING
+  if (getenv("NMS_DBG")) p.dbg = atoi(getenv("NMS_DBG"));
+#endif
   int fillers = 0;
   if (bound < p.N) {
     const long long tail_bytes = (long long)(p.N - bound) * 24;

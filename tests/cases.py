@@ -52,9 +52,30 @@ def conv_case(seed, n, c, h, w, oc, k, stride=1, pad=0, dil=1, groups=1, bias=Tr
     return js, pb, x
 
 
+def nms_writeback_case():
+    """non_max_suppression overwrites the rows of its INPUT outside the top_k (cpu/ops/nms.cc:93-97).
+    Here that input is read three times: by a cvm_clip before the operator (which must see the rows
+    as they were, although its only consumer -- an elemwise_add with the operator's output -- comes
+    after it, so a fused clip+add would run too late), by the operator, and by an elemwise_add after
+    it (which must see the overwritten rows)."""
+    b, n = 2, 120
+    g = wl.GraphBuilder(0)
+    d = g.var("data", (b, n, 6), 16)
+    vc, boxes = g.op("get_valid_counts", [d], [(b,), (b, n, 6)], {"score_threshold": 1 << 13})
+    c = g.op("cvm_clip", [boxes], (b, n, 6), {"precision": 10})
+    y = g.op("non_max_suppression", [boxes, vc], (b, n, 6), {
+        "iou_threshold": 45, "top_k": 12, "max_output_size": -1, "force_suppress": False, "id_index": 0,
+        "score_index": 1, "coord_start": 2, "return_indices": False, "invalid_to_bottom": True})
+    s1 = g.op("elemwise_add", [c, y], (b, n, 6), {})
+    s2 = g.op("elemwise_add", [s1, boxes], (b, n, 6), {})
+    js, pb = g.finish(s2)
+    return js, pb, wl.ssd_boxes(b, n, 3, classes=4, image=128)
+
+
 def model_cases():
     """name -> thunk; small enough for the CPU oracle to finish in seconds."""
     return {
+        "nms_input_writeback_order": nms_writeback_case,
         "conv_chain_s14": lambda: wl.conv_chain(batch=1, channels=32, size=14),
         "conv_chain_b3": lambda: wl.conv_chain(batch=3, channels=64, size=20),
         "resnet50_s64": lambda: wl.resnet50(batch=1, size=64),

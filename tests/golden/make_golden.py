@@ -4,6 +4,7 @@ reference tree; the fixtures it writes are committed and travel where the refere
 
     python tests/golden/make_golden.py              # everything
     python tests/golden/make_golden.py --fullsize   # only the digests of the full-size configurations
+    python tests/golden/make_golden.py --outputs    # only outputs.npz and load_status.npz
 """
 import hashlib
 import os
@@ -222,6 +223,8 @@ if __name__ == "__main__":
         fuzz_golden()
     elif len(sys.argv) > 1 and sys.argv[1] == "--fullsize":
         fullsize_golden()
+    elif len(sys.argv) > 1 and sys.argv[1] == "--outputs":
+        main()
     else:
         main()
         fuzz_golden()
