@@ -649,6 +649,7 @@ struct Lowering {
       d.N = N; d.H = H; d.W = W; d.C = C; d.OC = OC; d.KH = KH; d.KW = KW; d.OH = OH; d.OW = OW; d.groups = groups;
       d.stride_h = sh; d.stride_w = sw; d.pad_h = ph; d.pad_w = pw; d.dil_h = dh; d.dil_w = dw;
       d.depthwise = depthwise;
+      d.acc_bound = probe.acc_bound;
       d.ep = ch.ep;
       add_step(label + (depthwise ? "[dw]" : "[direct]"), [d](cudaStream_t s) { return cvmk_conv2d_direct(&d, s); });
     }

@@ -228,6 +228,129 @@ __global__ void __launch_bounds__(256) depthwise3x3_kernel(const __grid_constant
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Depthwise 3x3 (stride 1 or 2), int8 in / int8 out, tiled through shared memory.
+//
+// A CTA takes one image, a band of R output rows (all columns) and a block of CB = 32 / 64 / 128
+// channels.  The input rows of the band are copied into shared memory once with 16-byte
+// asynchronous copies (zeros where the filter reaches outside the image), so every input byte
+// crosses L2 -> SM once per band instead of three times, and all boundary handling is done there.
+// A thread then owns 4 channels (one 32-bit word per pixel) and walks strips of 4 output pixels:
+// the 36 weights sit in registers as words with one non-zero byte each, so that
+// dp4a(input word, weight word, acc) multiplies exactly one channel of the packed input word --
+// one instruction per product and no unpacking of the activations.  A warp covers CB/4
+// consecutive channel words of 32*4/CB rows; the row pitch is padded so that those rows fall into
+// different banks.  The requantisation is the packed form of the tensor-core kernels (multiply-add
+// into the upper half word, clamp on s16x2, byte permutes).
+// Reproduces groupwise_conv2d with groups = C (src/runtime/cpu/ops/ops.cc:333-366).
+struct Dw3Params {
+  const int8_t* x; const int8_t* w; const int32_t* bias; int8_t* y;
+  int N, H, W, C, OH, OW, ph, pw;
+  int cb_words;        // channel words per block (CB / 4): 8, 16 or 32
+  int rows_per_tile;   // R
+  int tiles_y, tiles_c;
+  int xw;              // staged pixels per input row
+  int pitch;           // words between staged rows
+  int strips;          // ceil(OW / 4)
+  int mul, add;        // requantisation: ((acc + bias + add) * mul) >> 16, mul = 2^(16 - shift)
+  uint32_t lo, hi;     // clamp, replicated into both halves of an s16x2 word
+  int relu;            // the clamp's lower bound is 0
+};
+
+template <int S>
+__global__ void __launch_bounds__(256) dw3x3_tile_kernel(const __grid_constant__ Dw3Params p) {
+  extern __shared__ __align__(16) uint32_t tile[];
+  constexpr int PX = 4;
+  constexpr int IN = (PX - 1) * S + 3;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int t = blockIdx.x;
+  const int tc = t % p.tiles_c; t /= p.tiles_c;
+  const int ty = t % p.tiles_y;
+  const int n = t / p.tiles_y;
+  const int oy0 = ty * p.rows_per_tile;
+  const int rows_here = min(p.rows_per_tile, p.OH - oy0);
+  const int cbw = p.cb_words;
+  const int c0 = tc * cbw * 4;
+  // ---- stage the input rows of the band
+  const int in_rows = (rows_here - 1) * S + 3;
+  const int iy0 = oy0 * S - p.ph;
+  const int vecs = cbw / 4;                     // 16-byte vectors per pixel
+  const int per_row = p.xw * vecs;
+  for (int idx = tid; idx < in_rows * per_row; idx += 256) {
+    const int r = idx / per_row, rem = idx - r * per_row;
+    const int xs = rem / vecs, v = rem - xs * vecs;
+    const int iy = iy0 + r, ix = xs - p.pw;
+    uint32_t* dst = tile + (size_t)r * p.pitch + xs * cbw + v * 4;
+    if (iy >= 0 && iy < p.H && ix >= 0 && ix < p.W) {
+      const int8_t* src = p.x + (((int64_t)n * p.H + iy) * p.W + ix) * p.C + c0 + v * 16;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+    } else {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  // ---- weights and bias of this thread's four channels (meanwhile)
+  const int cw = lane % cbw, rr = lane / cbw, rows_per_warp = 32 / cbw;
+  int wm[9][4];
+#pragma unroll
+  for (int tap = 0; tap < 9; ++tap) {
+    const int w = __ldg(reinterpret_cast<const int*>(p.w + (int64_t)tap * p.C + c0) + cw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) wm[tap][k] = w & (0xff << (8 * k));
+  }
+  int bq[4] = {0, 0, 0, 0};   // (bias + rounding addend) * mul
+  {
+    int4 b4 = make_int4(0, 0, 0, 0);
+    if (p.bias) b4 = __ldg(reinterpret_cast<const int4*>(p.bias + c0) + cw);
+    bq[0] = (b4.x + p.add) * p.mul; bq[1] = (b4.y + p.add) * p.mul;
+    bq[2] = (b4.z + p.add) * p.mul; bq[3] = (b4.w + p.add) * p.mul;
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncthreads();
+  // ---- compute: warp items = (group of rows_per_warp rows, strip of 4 pixels)
+  const int groups = (rows_here + rows_per_warp - 1) / rows_per_warp;
+  for (int item = warp; item < groups * p.strips; item += 8) {
+    const int g = item / p.strips, sidx = item - g * p.strips;
+    const int orow = g * rows_per_warp + rr;
+    if (orow >= rows_here) continue;
+    const int ox0 = sidx * PX;
+    const uint32_t* base = tile + (size_t)(orow * S) * p.pitch + (ox0 * S) * cbw + cw;
+    int acc[PX][4];
+#pragma unroll
+    for (int q = 0; q < PX; ++q)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[q][k] = 0;
+#pragma unroll
+    for (int fy = 0; fy < 3; ++fy) {
+      int xin[IN];
+#pragma unroll
+      for (int j = 0; j < IN; ++j) xin[j] = (int)base[(size_t)fy * p.pitch + j * cbw];
+#pragma unroll
+      for (int j = 0; j < IN; ++j) {
+#pragma unroll
+        for (int fx = 0; fx < 3; ++fx) {
+          if ((j - fx) % S != 0 || j - fx < 0 || (j - fx) / S >= PX) continue;  // resolved at compile time
+          const int q = (j - fx) / S;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[q][k] = __dp4a(xin[j], wm[fy * 3 + fx][k], acc[q][k]);
+        }
+      }
+    }
+    int8_t* yrow = p.y + (((int64_t)n * p.OH + oy0 + orow) * p.OW + ox0) * p.C + c0 + cw * 4;
+#pragma unroll
+    for (int q = 0; q < PX; ++q) {
+      if (ox0 + q >= p.OW) break;
+      const uint32_t v0 = (uint32_t)(acc[q][0] * p.mul + bq[0]), v1 = (uint32_t)(acc[q][1] * p.mul + bq[1]);
+      const uint32_t v2 = (uint32_t)(acc[q][2] * p.mul + bq[2]), v3 = (uint32_t)(acc[q][3] * p.mul + bq[3]);
+      uint32_t h0 = __byte_perm(v0, v1, 0x7632), h1 = __byte_perm(v2, v3, 0x7632);   // the upper halves
+      if (p.relu) { h0 = __vimin_s16x2_relu(h0, p.hi); h1 = __vimin_s16x2_relu(h1, p.hi); }
+      else { h0 = __vmaxs2(__vmins2(h0, p.hi), p.lo); h1 = __vmaxs2(__vmins2(h1, p.hi), p.lo); }
+      *reinterpret_cast<uint32_t*>(yrow + (int64_t)q * p.C) = __byte_perm(h0, h1, 0x6420);
+    }
+  }
+}
+
 // Patch gather: one thread builds 16 consecutive bytes of one row of A.  The (fy, fx, c) split
 // of every k is looked up in a shared-memory table built once per block.
 struct PackParams {
@@ -350,6 +473,64 @@ __global__ void __launch_bounds__(512) stem_pack_kernel(const __grid_constant__ 
   }
 }
 
+// Plans and launches dw3x3_tile_kernel when the layer and its chain qualify; returns -1 when they
+// do not (the caller then uses the register kernel).
+int try_dw3x3_tile(const cvmk_conv_direct_desc* d, const DevChain& chain, cudaStream_t s) {
+  if (d->y_dtype != CVMK_I8 || d->C % 32 != 0 || d->acc_bound <= 0 || d->OW < 1) return -1;
+  if (d->pad_h > 1 || d->pad_w > 1) return -1;
+  // chain = [bias] rs_clamp, with a sum that cannot overflow and fits 16 bits after the shift
+  int i0 = 0;
+  const int32_t* bias = nullptr;
+  if (chain.n > 0 && chain.s[0].op == K_ADD_C) { bias = reinterpret_cast<const int32_t*>(chain.s[0].ptr); i0 = 1; }
+  if (chain.n - i0 != 1 || chain.s[i0].op != K_RS_CLAMP) return -1;
+  const DevStep& rs = chain.s[i0];
+  const int64_t add = rs.c;
+  const int sh = rs.d;
+  const int64_t lo1 = ((int64_t)rs.a + add) >> sh, hi1 = ((int64_t)rs.b + add) >> sh;
+  if (sh > 16 || d->acc_bound + add >= (int64_t)INT32_MAX || ((d->acc_bound + add) >> sh) >= 32767 ||
+      lo1 < -32767 || hi1 > 32767 || lo1 > hi1)
+    return -1;
+  // The kernel clamps after the shift; the chain clamps the sum to [rs.a, rs.b] first.  Both give
+  // the same value because the shift is monotone (the argument of the tensor-core kernels).
+  Dw3Params p;
+  memset(&p, 0, sizeof(p));
+  p.x = reinterpret_cast<const int8_t*>(d->x); p.w = d->w; p.bias = bias; p.y = reinterpret_cast<int8_t*>(d->y);
+  p.N = d->N; p.H = d->H; p.W = d->W; p.C = d->C; p.OH = d->OH; p.OW = d->OW; p.ph = d->pad_h; p.pw = d->pad_w;
+  const int S = d->stride_h;
+  const int cb = d->C % 128 == 0 ? 128 : (d->C % 64 == 0 ? 64 : 32);
+  p.cb_words = cb / 4;
+  p.tiles_c = d->C / cb;
+  p.strips = (d->OW + 3) / 4;
+  p.xw = (p.strips * 4 - 1) * S + 3;
+  // rows of a warp must land in different banks: pitch = multiple of 32 words + cb_words / S
+  p.pitch = (p.xw * p.cb_words + 31) / 32 * 32 + p.cb_words / S;
+  const int rows_per_warp = 32 / p.cb_words;
+  int R = d->OH;
+  auto smem_of = [&](int r) { return ((r - 1) * S + 3) * p.pitch * 4; };
+  while (R > rows_per_warp && smem_of(R) > 44 * 1024) --R;
+  if (smem_of(R) > 44 * 1024) return -1;
+  // enough tiles to fill the GPU a few times over
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  while (R > 2 * rows_per_warp && (int64_t)d->N * ((d->OH + R - 1) / R) * p.tiles_c < 6LL * sms) R = (R + 1) / 2;
+  if (R > rows_per_warp) R = R / rows_per_warp * rows_per_warp;   // whole warp row groups
+  if (smem_of(R) > 48 * 1024) return -1;
+  p.rows_per_tile = R;
+  p.tiles_y = (d->OH + R - 1) / R;
+  p.mul = 1 << (16 - sh);
+  p.add = (int)add;
+  auto x2 = [](int64_t v) { return (uint32_t)((uint32_t)(uint16_t)(int16_t)v | ((uint32_t)(uint16_t)(int16_t)v << 16)); };
+  p.lo = x2(lo1); p.hi = x2(hi1);
+  p.relu = lo1 == 0;
+  const int64_t tiles = (int64_t)d->N * p.tiles_y * p.tiles_c;
+  if (tiles > INT32_MAX) return -1;
+  const int smem = smem_of(R);
+  if (S == 1) dw3x3_tile_kernel<1><<<(unsigned)tiles, 256, smem, s>>>(p);
+  else dw3x3_tile_kernel<2><<<(unsigned)tiles, 256, smem, s>>>(p);
+  return check_cuda(cudaGetLastError(), "dw3x3_tile_kernel launch");
+}
+
 int grid_sized(int64_t work, int threads) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -391,6 +572,8 @@ extern "C" int cvmk_conv2d_direct(const cvmk_conv_direct_desc* d, cvmk_stream_t 
     }
     if (d->KH == 3 && d->KW == 3 && d->dil_h == 1 && d->dil_w == 1 && d->stride_h == d->stride_w &&
         (d->stride_h == 1 || d->stride_h == 2)) {
+      const int rc_tile = try_dw3x3_tile(d, p.chain, s);
+      if (rc_tile >= 0) return rc_tile;
       const int64_t work3 = (int64_t)d->N * d->OH * (d->C / 4);
       if (d->stride_h == 1) depthwise3x3_kernel<1><<<grid_sized(work3, 256), 256, 0, s>>>(p);
       else depthwise3x3_kernel<2><<<grid_sized(work3, 256), 256, 0, s>>>(p);

@@ -224,6 +224,10 @@ typedef struct {
   int32_t N, H, W, C, OC, KH, KW, OH, OW, groups;
   int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int32_t depthwise;
+  int32_t reserved0;
+  /* Upper bound on |sum + bias| over every output element (0 = unknown), as in cvmk_conv_desc: lets
+   * the depthwise kernels requantise with packed 16-bit arithmetic. */
+  int64_t acc_bound;
   cvmk_epilogue ep;
 } cvmk_conv_direct_desc;
 CVMK_API int cvmk_conv2d_direct(const cvmk_conv_direct_desc* d, cvmk_stream_t stream);
