@@ -205,7 +205,9 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
   uint8_t* srow = smem + p.off_in;       // [srows][srow_bytes]
   uint8_t* out_panels = smem + p.off_out;  // [2][128][OC], swizzle of width OC
   int32_t* bias_s = reinterpret_cast<int32_t*>(smem + p.off_bias);
-  const int warp = threadIdx.x >> 5;
+  // warp index through a shuffle: provably uniform, so that the loops of the single-issuer roles
+  // (MMA, output stores) run on the uniform datapath with one elected lane issuing
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -316,7 +318,8 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
 #endif
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       const uint32_t idesc = umma_idesc_i8(p.OC);
       const uint64_t desc_b0 = umma_desc(smem_u32(wq), SLOT);
       const uint64_t desc_a0 = umma_desc(smem_u32(a_tiles), SLOT);
@@ -343,15 +346,19 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
             uint32_t al = (uint32_t)desc_a0 + (uint32_t)buf * (uint32_t)p.KH * (uint32_t)a_step;
             uint32_t bl = (uint32_t)desc_b0;
             const uint32_t a_hi = (uint32_t)(desc_a0 >> 32), b_hi = (uint32_t)(desc_b0 >> 32);
-            for (int ky = 0; ky < p.KH; ++ky, al += (uint32_t)a_step, bl += (uint32_t)b_step)
-              mma_i8_k<1>(d_tmem, al, a_hi, bl, b_hi, idesc, (uint32_t)ky);
-            mma_commit(&a_empty[buf]);
-            mma_commit(&acc_full[buf]);
+            if (leader) {
+              for (int ky = 0; ky < p.KH; ++ky, al += (uint32_t)a_step, bl += (uint32_t)b_step)
+                mma_i8_k<1>(d_tmem, al, a_hi, bl, b_hi, idesc, (uint32_t)ky);
+              mma_commit(&a_empty[buf]);
+              mma_commit(&acc_full[buf]);
+            }
             STADD(5, tw);
           }
         }
       }
-      STFLUSH(3); STFLUSH(4); STFLUSH(5);
+#ifdef CVMK_STEM_TIMING
+      if (leader) { STFLUSH(3); STFLUSH(4); STFLUSH(5); }
+#endif
     }
   } else if (warp < STORE_WARP) {
     // ------------------------------------------------------------------ epilogue
@@ -427,10 +434,11 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
 #ifdef CVMK_STEM_TIMING
     if (leader) { STFLUSH(6); STFLUSH(7); STFLUSH(8); STFLUSH(9); }
 #endif
-  } else if (lane == 0) {
+  } else {
     // ------------------------------------------------------------------ output stores
-    // One thread: waits until the four epilogue warps have written a panel, stores it with TMA,
-    // and hands the previous panel back once the engine has read it.
+    // One elected thread: waits until the four epilogue warps have written a panel, stores it with
+    // TMA, and hands the panel back once the engine has read it.
+    const bool leader = elect_one();
     uint32_t tile = 0;
     bool live = true;
     const int panel_bytes = BLOCK_M * p.OC;
@@ -441,14 +449,17 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_y, const __grid_consta
         for (int sg = 0; sg < p.segs; ++sg, ++tile) {
           const int buf = (int)(tile & 1u);
           if (!mbar_wait(&out_full[buf], (tile >> 1) & 1u, &abort_flag, 6)) { live = false; break; }
-          tma_store_3d(&tmap_y, out_panels + (size_t)buf * panel_bytes, 0, sg * p.seg_w, n * p.OH + oy0 + rr);
-          tma_store_commit();
-          tma_store_wait_read();  // the engine has read this panel: hand it back at once
-          mbar_arrive(&out_free[buf]);
+          if (leader) {
+            tma_store_3d(&tmap_y, out_panels + (size_t)buf * panel_bytes, 0, sg * p.seg_w, n * p.OH + oy0 + rr);
+            tma_store_commit();
+            tma_store_wait_read();  // the engine has read this panel: hand it back at once
+            mbar_arrive(&out_free[buf]);
+          }
+          __syncwarp();
         }
       }
     }
-    tma_store_wait_all();
+    // the writes themselves complete with the grid
   }
 
   // ------------------------------------------------------------------ teardown
