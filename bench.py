@@ -462,6 +462,7 @@ class Harness:
         res = {"workload": workload, "batch": batch, "launches": int(rt.step_count(net)),
                "units": units_per_step(workload, batch, wl), "graph_json": js,
                "device_bytes": int(rt.device_bytes(net)), "in_bytes": int(x.nbytes), "out_bytes": int(out.nbytes)}
+        res["activation_bytes"] = dict(zip(("buffers", "physical"), rt.activation_bytes(net)))
         rt.inference_bytes(net, x, out)
 
         # ---- end to end through the C-ABI: a page-locked caller buffer (uploaded in place) and an
@@ -624,7 +625,7 @@ def run_ours(args):
                     "input": "page-locked host buffer",
                     "pageable_input_value": total_units / head["e2e_pageable"][0]},
             "gpu_launches": head["launches"] * args.steps * head["repeats"],
-            "device_bytes": head["device_bytes"],
+            "device_bytes": head["device_bytes"], "activation_bytes": head["activation_bytes"],
             "clocks": head["clocks"], "roofline": roofline,
         }
 

@@ -310,6 +310,13 @@ int CVMXDeviceBytes(void* net, unsigned long long* n) {
   API_END();
 }
 
+int CVMXActivationBytes(void* net, unsigned long long* buffers, unsigned long long* physical) {
+  API_BEGIN();
+  CHECK(net != nullptr); CHECK(buffers != nullptr); CHECK(physical != nullptr);
+  static_cast<Model*>(net)->executor().activation_bytes(buffers, physical);
+  API_END();
+}
+
 int CVMXReplayDevice(void* net, int iters, float* total_ms) {
   API_BEGIN();
   CHECK(net != nullptr); CHECK(total_ms != nullptr);

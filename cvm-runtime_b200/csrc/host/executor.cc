@@ -1,5 +1,6 @@
 // Lowering of a Graph into kernel launches, and the per-inference replay.
 #include "executor.h"
+#include <cuda.h>
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -60,6 +61,113 @@ void* Executor::dalloc(size_t bytes) {
   return p;
 }
 
+// ---- CUDA virtual memory management, through the driver entry points -------------------------
+namespace {
+struct Vmm {
+  CUresult (*get_granularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+  CUresult (*reserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*address_free)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+  CUresult (*release)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*unmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*set_access)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+  bool ok = false;
+};
+const Vmm& vmm() {
+  static Vmm v = [] {
+    Vmm t;
+    auto get = [](const char* name) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) fn = nullptr;
+      return fn;
+    };
+    t.get_granularity = reinterpret_cast<decltype(t.get_granularity)>(get("cuMemGetAllocationGranularity"));
+    t.reserve = reinterpret_cast<decltype(t.reserve)>(get("cuMemAddressReserve"));
+    t.address_free = reinterpret_cast<decltype(t.address_free)>(get("cuMemAddressFree"));
+    t.create = reinterpret_cast<decltype(t.create)>(get("cuMemCreate"));
+    t.release = reinterpret_cast<decltype(t.release)>(get("cuMemRelease"));
+    t.map = reinterpret_cast<decltype(t.map)>(get("cuMemMap"));
+    t.unmap = reinterpret_cast<decltype(t.unmap)>(get("cuMemUnmap"));
+    t.set_access = reinterpret_cast<decltype(t.set_access)>(get("cuMemSetAccess"));
+    t.ok = t.get_granularity && t.reserve && t.address_free && t.create && t.release && t.map && t.unmap && t.set_access;
+    cudaGetLastError();
+    return t;
+  }();
+  return v;
+}
+CUmemAllocationProp device_prop(int device) {
+  CUmemAllocationProp prop;
+  memset(&prop, 0, sizeof(prop));
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = device;
+  return prop;
+}
+}  // namespace
+
+void* Executor::dalloc_activation(size_t bytes, uint32_t root) {
+  // small buffers are not worth a mapping of their own (the granularity is 2 MiB)
+  if (!vmm_ || bytes < (size_t)1 << 20) return dalloc(bytes);
+  ActBuf a;
+  a.bytes = std::max<size_t>(bytes, 256);
+  a.va_size = (a.bytes + vmm_gran_ - 1) / vmm_gran_ * vmm_gran_;
+  a.root = root;
+  CUdeviceptr va = 0;
+  const CUresult r = vmm().reserve(&va, a.va_size, vmm_gran_, 0, 0);
+  CHECK(r == CUDA_SUCCESS) << "cuMemAddressReserve(" << a.va_size << ") failed (" << (int)r << ")";
+  a.va = reinterpret_cast<void*>(va);
+  act_.push_back(a);
+  return a.va;
+}
+
+// Backs the activation buffers with physical memory in chunks of the allocation granularity (2 MiB):
+// walking the buffers in the order of their first write, a buffer takes any chunks that are free by
+// then (most recently freed first: they are the likeliest to be still in L2) and new ones for the
+// rest; its chunks are free again after its last read.  Chunks need not be contiguous -- the
+// virtual range of a buffer is -- so nothing is lost to fragmentation.
+void Executor::MapActivations() {
+  if (!vmm_ || act_.empty()) return;
+  const CUmemAllocationProp prop = device_prop(device_);
+  CUmemAccessDesc access;
+  memset(&access, 0, sizeof(access));
+  access.location = prop.location;
+  access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  std::vector<size_t> order(act_.size());
+  for (size_t i = 0; i < order.size(); ++i) order[i] = i;
+  std::stable_sort(order.begin(), order.end(), [&](size_t x, size_t y) { return act_[x].first < act_[y].first; });
+  for (size_t i : order) {
+    ActBuf& a = act_[i];
+    const size_t need = a.va_size / vmm_gran_;
+    std::vector<int> cand;
+    for (size_t c = 0; c < phys_.size(); ++c)
+      if (phys_[c].free_at <= a.first) cand.push_back((int)c);
+    std::stable_sort(cand.begin(), cand.end(), [&](int x, int y) { return phys_[x].free_at > phys_[y].free_at; });
+    std::vector<int> mine(cand.begin(), cand.begin() + std::min(cand.size(), need));
+    while (mine.size() < need) {
+      PhysBlock nb;
+      CUmemGenericAllocationHandle h = 0;
+      const CUresult r = vmm().create(&h, vmm_gran_, &prop, 0);
+      CHECK(r == CUDA_SUCCESS) << "cuMemCreate failed (" << (int)r << ") after " << device_bytes_ << " bytes";
+      nb.handle = (unsigned long long)h;
+      nb.size = vmm_gran_;
+      phys_.push_back(nb);
+      device_bytes_ += vmm_gran_;
+      mine.push_back((int)phys_.size() - 1);
+    }
+    const CUdeviceptr va = reinterpret_cast<CUdeviceptr>(a.va);
+    for (size_t k = 0; k < need; ++k) {
+      phys_[mine[k]].free_at = a.last + 1;
+      const CUresult r = vmm().map(va + k * vmm_gran_, vmm_gran_, 0, (CUmemGenericAllocationHandle)phys_[mine[k]].handle, 0);
+      CHECK(r == CUDA_SUCCESS) << "cuMemMap failed (" << (int)r << ")";
+    }
+    const CUresult r = vmm().set_access(va, a.va_size, &access, 1);
+    CHECK(r == CUDA_SUCCESS) << "cuMemSetAccess failed (" << (int)r << ")";
+    a.block = mine.empty() ? -1 : mine[0];
+  }
+}
+
 struct Lowering {
   Executor& ex;
   const Graph& g;
@@ -67,6 +175,10 @@ struct Lowering {
   std::vector<int> uses;
   std::vector<char> is_head, safe8, absorbed;
   uint32_t data_eid = 0;
+  uint32_t cur_root = UINT32_MAX;   // node being lowered: tags the activation buffers it allocates
+  std::vector<uint32_t> root_of;    // node -> root of the fused group it runs in
+  // activation memory: planned when a node is being lowered, persistent otherwise (heads, staging)
+  void* act_alloc(size_t bytes) { return cur_root == UINT32_MAX ? ex.dalloc(bytes) : ex.dalloc_activation(bytes, cur_root); }
   DevBuf raw_in;          // the input exactly as the C-ABI delivers it (row-major int8 / int32)
   int32_t data_range = 127;
 
@@ -138,7 +250,7 @@ struct Lowering {
     DevBuf& b = buf[eid];
     if (b.ptr) return b;
     auto it = g.params.find(eid);
-    b.ptr = ex.dalloc(b.bytes());
+    b.ptr = it != g.params.end() ? ex.dalloc(b.bytes()) : act_alloc(b.bytes());
     if (it != g.params.end()) {
       // parameter: convert on the host into the entry's dtype and layout, upload once
       const HostTensor& t = it->second;
@@ -218,7 +330,7 @@ struct Lowering {
     if (!b.nhwc) return b;
     DevBuf t = b;
     t.nhwc = false;
-    t.ptr = ex.dalloc(t.bytes());
+    t.ptr = act_alloc(t.bytes());
     emit_convert(b, t, label + ":to_rowmajor");
     return t;
   }
@@ -229,7 +341,7 @@ struct Lowering {
     DevBuf t = b;
     t.nhwc = false;
     t.dtype = CVMK_I32;
-    t.ptr = ex.dalloc(t.bytes());
+    t.ptr = act_alloc(t.bytes());
     emit_convert(b, t, label + ":to_i32");
     return t;
   }
@@ -239,7 +351,7 @@ struct Lowering {
     if (b.dtype == CVMK_I8) return b;
     DevBuf t = b;
     t.dtype = CVMK_I8;
-    t.ptr = ex.dalloc(t.bytes());
+    t.ptr = act_alloc(t.bytes());
     const DevBuf src = b;
     const int64_t n = shape_size(b.shape);
     add_step(label + ":narrow", [src, t, n](cudaStream_t s) {
@@ -546,7 +658,7 @@ struct Lowering {
     }
 
     if (via_pack) {
-      int8_t* amat = (int8_t*)ex.dalloc((size_t)packed.N * kp);
+      int8_t* amat = (int8_t*)act_alloc((size_t)packed.N * kp);
       cvmk_stem_pack_desc sp;
       memset(&sp, 0, sizeof(sp));
       sp.x = (const int8_t*)raw_in.ptr; sp.a = amat;
@@ -586,7 +698,7 @@ struct Lowering {
       DevBuf tmp = out;
       tmp.shape = Shape{(int64_t)N, (int64_t)OCp, (int64_t)OH, (int64_t)OW};
       tmp.nhwc = true;
-      tmp.ptr = ex.dalloc(tmp.bytes());
+      tmp.ptr = act_alloc(tmp.bytes());
       cvmk_conv_desc d = probe;
       d.OC = OCp;
       d.x = (const int8_t*)xin.ptr; d.w = wdev; d.y = tmp.ptr; d.y_dtype = tmp.dtype;
@@ -909,7 +1021,7 @@ struct Lowering {
     if (out_needs_convert) {
       DevBuf tmp = buf[eo];
       tmp.nhwc = false;
-      tmp.ptr = ex.dalloc(tmp.bytes());
+      tmp.ptr = act_alloc(tmp.bytes());
       d.y = tmp.ptr; d.y_dtype = tmp.dtype;
       add_step(label, [d](cudaStream_t s) { return cvmk_reduce(&d, s); });
       emit_convert(tmp, materialize(eo), label + ":to_nhwc");
@@ -1035,7 +1147,7 @@ struct Lowering {
     if (!b.nhwc) return b;
     DevBuf t = b;
     t.nhwc = false;
-    t.ptr = ex.dalloc(t.bytes());
+    t.ptr = act_alloc(t.bytes());
     return t;
   }
   void finish_rowmajor(const DevBuf& t, uint32_t eid, const std::string& label) {
@@ -1130,7 +1242,7 @@ struct Lowering {
     d.top_k = (int)n.attrs.i("top_k");
     d.force_suppress = n.attrs.b("force_suppress") ? 1 : 0;
     d.scratch_bytes = cvmk_nms_scratch_bytes(d.B, d.N);
-    d.scratch = ex.dalloc((size_t)d.scratch_bytes);
+    d.scratch = act_alloc((size_t)d.scratch_bytes);
     // The CPU operator writes -1 over the input rows outside the top_k (nms.cc:93-97).  That is
     // visible when the input entry is a head or is read again by a later node.
     const uint32_t in_eid = g.entry_id(n.inputs[0]);
@@ -1145,6 +1257,51 @@ struct Lowering {
       d.x_writeback = (int32_t*)own.ptr;
     }
     add_step(label, [d](cudaStream_t s) { return cvmk_non_max_suppression(&d, s); });
+  }
+
+  // Lifetimes of the activation buffers in schedule positions (one position per fused group, in
+  // the order the groups are launched), then their physical backing.  A buffer is live from the
+  // group that first writes it (the group of the producing node, which for a shortcut operand of
+  // a fused join can precede the group whose lowering allocated it) to the last group that reads
+  // it: the groups of all consumers of every graph entry stored in it (aliases of reshape-like
+  // nodes included), the end of the inference for a head.  Reads and writes inside one group all
+  // happen at that group's position.  Every kernel launched with programmatic dependent launch
+  // waits for the whole preceding kernel before it touches global memory, so a buffer whose last
+  // reader sits at position p can be overwritten from position p + 1 on.  The steps that are
+  // launched per batch chunk while the input uploads run chunk after chunk, so everything they
+  // touch stays live across that whole prefix.
+  std::vector<int> step_pos;   // step -> schedule position (-1: before the first group)
+  void plan_activations(const std::vector<std::pair<uint32_t, uint32_t>>& order) {
+    auto& act = ex.act_;
+    if (act.empty()) return;
+    const int end = (int)order.size() + 1;
+    std::vector<int> pos(g.nodes.size(), -1);
+    for (size_t i = 0; i < order.size(); ++i) pos[order[i].second] = (int)i;
+    auto group_pos = [&](uint32_t nid) { return root_of[nid] == UINT32_MAX ? -1 : pos[root_of[nid]]; };
+    for (auto& a : act) a.first = a.last = pos[a.root];
+    auto find = [&](const void* p) -> Executor::ActBuf* {
+      for (auto& a : act)
+        if ((const char*)p >= (const char*)a.va && (const char*)p < (const char*)a.va + a.va_size) return &a;
+      return nullptr;
+    };
+    std::vector<Executor::ActBuf*> of_entry(g.num_entries, nullptr);
+    for (uint32_t nid = 0; nid < g.nodes.size(); ++nid)
+      for (uint32_t eid = g.node_row_ptr[nid]; eid < g.node_row_ptr[nid + 1]; ++eid) {
+        if (!buf[eid].ptr) continue;
+        Executor::ActBuf* a = of_entry[eid] = find(buf[eid].ptr);
+        if (!a) continue;
+        a->first = std::min(a->first, g.nodes[nid].is_variable() ? -1 : group_pos(nid));
+        if (is_head[eid]) a->last = end;
+      }
+    for (uint32_t nid = 0; nid < g.nodes.size(); ++nid)
+      for (const auto& e : g.nodes[nid].inputs)
+        if (Executor::ActBuf* a = of_entry[g.entry_id(e)]) a->last = std::max(a->last, group_pos(nid));
+    if (ex.prefix_steps_ > 0) {
+      const int p = step_pos[ex.prefix_steps_ - 1];
+      for (auto& a : act)
+        if (a.first <= p) { a.first = -1; a.last = std::max(a.last, p); }
+    }
+    ex.MapActivations();
   }
 
   void lower_node(uint32_t nid) {
@@ -1199,6 +1356,7 @@ struct Lowering {
       // A dry pass decides the groups; the step lists of the groups are then ordered by tail.
       std::vector<std::vector<Step>> per_root(g.nodes.size());
       std::vector<uint32_t> tail(g.nodes.size(), 0);
+      root_of.assign(g.nodes.size(), UINT32_MAX);
       std::vector<Step> prologue = ex.steps_;
       ex.steps_.clear();
       for (uint32_t nid = 0; nid < g.nodes.size(); ++nid) {
@@ -1206,9 +1364,12 @@ struct Lowering {
         if (n.is_variable() || absorbed[nid]) continue;
         const size_t before = ex.steps_.size();
         uint32_t last = nid;
+        cur_root = nid;
+        root_of[nid] = nid;
         lower_node(nid);
+        cur_root = UINT32_MAX;
         for (uint32_t k = nid + 1; k < g.nodes.size(); ++k)
-          if (absorbed[k] == 1) { absorbed[k] = 2; last = std::max(last, k); }
+          if (absorbed[k] == 1) { absorbed[k] = 2; root_of[k] = nid; last = std::max(last, k); }
         per_root[nid].assign(ex.steps_.begin() + before, ex.steps_.end());
         ex.steps_.resize(before);
         tail[nid] = last;
@@ -1227,8 +1388,12 @@ struct Lowering {
         ep.s[0].b = data_range;
         emit_convert(raw_in, materialize(data_eid), "input:data", &ep);
       }
-      for (const auto& pr : order)
-        for (auto& s : per_root[pr.second]) ex.steps_.push_back(std::move(s));
+      step_pos.assign(ex.steps_.size(), -1);
+      for (size_t i = 0; i < order.size(); ++i)
+        for (auto& s : per_root[order[i].second]) {
+          ex.steps_.push_back(std::move(s));
+          step_pos.push_back((int)i);
+        }
     }
     // Upload / compute overlap: when the inference starts with the stem, the leading run of steps
     // that can be cut along the batch (about as much work as the upload takes) is launched per
@@ -1244,6 +1409,7 @@ struct Lowering {
         while (ex.prefix_steps_ < ex.steps_.size() && ex.prefix_steps_ < cap && ex.steps_[ex.prefix_steps_].chunk.size() == ex.steps_[0].chunk.size())
           ++ex.prefix_steps_;
     }
+    plan_activations(order);
     // heads: row-major staging + pinned host mirrors
     for (const auto& e : g.outputs) {
       const uint32_t eid = g.entry_id(e);
@@ -1272,6 +1438,14 @@ Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
   pinned_.push_back(status_host_);
   *status_host_ = 0;
   use_graph_ = dev_env("CVM_B200_NO_GRAPH") == nullptr;
+  if (vmm().ok && !dev_env("CVM_B200_NO_PLANNER")) {
+    const CUmemAllocationProp prop = device_prop(device_);
+    size_t gran = 0;
+    if (vmm().get_granularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM) == CUDA_SUCCESS && gran > 0) {
+      vmm_ = true;
+      vmm_gran_ = gran;
+    }
+  }
   Lowering low(*this, g);
   low.run();
   // One eager pass sets per-kernel attributes and surfaces launch errors before capture.
@@ -1301,6 +1475,11 @@ Executor::~Executor() {
   for (auto e : chunk_events_) cudaEventDestroy(e);
   if (copy_stream_) cudaStreamDestroy(copy_stream_);
   for (void* p : allocs_) cudaFree(p);
+  for (auto& a : act_) {
+    if (a.block >= 0) vmm().unmap(reinterpret_cast<CUdeviceptr>(a.va), a.va_size);
+    vmm().address_free(reinterpret_cast<CUdeviceptr>(a.va), a.va_size);
+  }
+  for (auto& b : phys_) vmm().release((CUmemGenericAllocationHandle)b.handle);
   for (void* p : pinned_) cudaFreeHost(p);
   if (stream_) cudaStreamDestroy(stream_);
 }

@@ -90,6 +90,12 @@ class Executor {
   const std::vector<HeadOut>& heads() const { return heads_; }
   size_t num_steps() const { return steps_.size(); }
   size_t device_bytes() const { return device_bytes_; }
+  void activation_bytes(unsigned long long* buffers, unsigned long long* physical) const {
+    *buffers = 0;
+    for (const auto& a : act_) *buffers += a.va_size;
+    *physical = 0;
+    for (const auto& b : phys_) *physical += b.size;
+  }
   // Per-step device times of one eager pass (label, milliseconds); used by the profiling table.
   std::vector<std::pair<std::string, float>> ProfileOnce(const void* input, size_t input_bytes);
   // Replays only the kernels (input already in device memory, no upload / download) `iters`
@@ -127,6 +133,27 @@ class Executor {
   std::unique_ptr<StagePool> stage_pool_;   // created by the first inference from pageable memory
 
   void* dalloc(size_t bytes);
+  // Activation memory.  Every activation buffer gets a virtual address range of its own when the
+  // graph is lowered (kernel descriptors and tensor maps are built on those addresses); once the
+  // schedule is known, buffers whose lifetimes do not overlap are backed by the SAME physical
+  // memory (CUDA virtual memory management: one physical allocation mapped at several addresses),
+  // which is what the reference's storage planner does with its shared pool
+  // (src/runtime/graph_runtime.cc:503-610).  Falls back to one cudaMalloc per buffer when the
+  // driver's virtual memory calls are not available.
+  struct ActBuf {
+    void* va = nullptr;
+    size_t bytes = 0, va_size = 0;
+    uint32_t root = UINT32_MAX;   // node whose lowering made the allocation
+    int first = 0, last = 0;      // schedule positions of the first write and the last read
+    int block = -1;               // physical block backing it
+  };
+  struct PhysBlock { unsigned long long handle = 0; size_t size = 0; int free_at = 0; };
+  void* dalloc_activation(size_t bytes, uint32_t root);
+  void MapActivations();
+  std::vector<ActBuf> act_;
+  std::vector<PhysBlock> phys_;
+  bool vmm_ = false;
+  size_t vmm_gran_ = 0;
   void Upload(const void* input, cudaStream_t s);
   void UploadRange(const void* input, size_t begin, size_t bytes, cudaStream_t s);
   void Enqueue(cudaStream_t s, size_t first = 0);

@@ -185,6 +185,13 @@ def device_bytes(net):
     return _get_ull("CVMXDeviceBytes", net)
 
 
+def activation_bytes(net):
+    """(sum of the planned activation buffers' sizes, device memory that backs them)."""
+    a, b = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+    check_call(lib().CVMXActivationBytes(net, ctypes.byref(a), ctypes.byref(b)), "CVMXActivationBytes")
+    return int(a.value), int(b.value)
+
+
 def replay_device(net, iters):
     """Device milliseconds for `iters` kernel-only replays (input of the last inference)."""
     ms = ctypes.c_float()

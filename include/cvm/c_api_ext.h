@@ -23,6 +23,10 @@ CVM_DLL const char* CVMXLastError(void);
 CVM_DLL int CVMXStepCount(void* net, unsigned long long* n);
 /* Device memory held by the model: weights, activations, staging. */
 CVM_DLL int CVMXDeviceBytes(void* net, unsigned long long* n);
+/* Activation memory under the lifetime planner: `buffers` = the sizes of all planned activation
+ * buffers added up (what one allocation per buffer would take), `physical` = the device memory
+ * that backs them once buffers with disjoint lifetimes share it.  Both 0 when the planner is off. */
+CVM_DLL int CVMXActivationBytes(void* net, unsigned long long* buffers, unsigned long long* physical);
 /* Replays the model's kernels `iters` times on the input of the last CVMAPIInference call (no
  * upload, no download) and returns the elapsed device time, measured with CUDA events on the
  * model's stream, in milliseconds. */
