@@ -615,13 +615,8 @@ struct Lowering {
       sd.acc_bound = probe.acc_bound;
       sd.ep = ch.ep;
       if (cvmk_conv2d_stem_supported(&sd)) {
-        // [KH][OC][32]: byte kx * C + c of row (ky, oc) = w[oc][c][ky][kx], the rest zero
-        std::vector<int8_t> ws((size_t)KH * OC * 32, 0);
-        for (int o = 0; o < OC; ++o)
-          for (int c = 0; c < C; ++c)
-            for (int ky = 0; ky < KH; ++ky)
-              for (int kx = 0; kx < KW; ++kx)
-                ws[((size_t)ky * OC + o) * 32 + kx * C + c] = (int8_t)wt.data[(((size_t)o * C + c) * KH + ky) * KW + kx];
+        std::vector<int8_t> ws((size_t)cvmk_conv2d_stem_weight_bytes(&sd), 0);
+        KERNEL_OK(cvmk_conv2d_stem_pack_weights(&sd, wt.data.data(), ws.data()));
         int8_t* wsdev = (int8_t*)ex.dalloc(ws.size());
         CUDA_OK(cudaMemcpy(wsdev, ws.data(), ws.size(), cudaMemcpyHostToDevice));
         sd.w = wsdev;

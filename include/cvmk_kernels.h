@@ -296,12 +296,14 @@ CVMK_API int cvmk_where(const cvmk_where_desc* d, cvmk_stream_t stream);
 /* ------------------------------------------------------------------------------------------------
  * conv2d of the network input itself when it has 1..4 channels (image stems), groups = 1
  * (cpu/ops/ops.cc:368-456 after the input clamp of graph_runtime.cc:379-386), on the tensor cores
- * without an intermediate patch matrix.
- *   x : the input as the C-ABI delivers it, NCHW int8 [N, C, H, W]; values are clamped to +-clamp
- *   w : int8 [KH][OC][32]: row ky of output channel oc holds w[oc][c][ky][kx] at byte kx * C + c,
- *       zero in the remaining bytes (KW * C <= 32)
+ * without an intermediate patch matrix.  Stride 1 or 2 (the same in both directions), filters up to
+ * 8 x 8, W a multiple of 16, no dilation.
+ *   x : the input as the C-ABI delivers it, NCHW int8 [N, C, H, W], 16-byte aligned; values are
+ *       clamped to +-clamp
+ *   w : the filter in the kernel's own operand order, cvmk_conv2d_stem_weight_bytes() bytes written
+ *       by cvmk_conv2d_stem_pack_weights() (a host function: OIHW int32 values in, bytes out)
  *   y : NHWC int8 [N, OH, OW, OC], OC in {32, 64, 128}; chain as for cvmk_conv2d_tc_*
- * No dilation.  prepare() encodes the output tensor map; the plan must be 64-byte aligned.
+ * prepare() encodes the tensor maps of x and y; the plan must be 64-byte aligned.
  * ---------------------------------------------------------------------------------------------- */
 typedef struct {
   const int8_t* x;
@@ -319,6 +321,7 @@ typedef struct {
 
 typedef struct __attribute__((aligned(64))) {
   unsigned char tmap_y[128];
+  unsigned char tmap_x[128];
   cvmk_stem_conv_desc d;
   int32_t grid;
   int32_t smem_bytes;
@@ -326,6 +329,8 @@ typedef struct __attribute__((aligned(64))) {
 } cvmk_stem_conv_plan;
 
 CVMK_API int cvmk_conv2d_stem_supported(const cvmk_stem_conv_desc* d);
+CVMK_API int64_t cvmk_conv2d_stem_weight_bytes(const cvmk_stem_conv_desc* d);
+CVMK_API int cvmk_conv2d_stem_pack_weights(const cvmk_stem_conv_desc* d, const int32_t* w_oihw, int8_t* packed);
 CVMK_API int cvmk_conv2d_stem_prepare(const cvmk_stem_conv_desc* d, cvmk_stem_conv_plan* plan);
 CVMK_API int cvmk_conv2d_stem_launch(const cvmk_stem_conv_plan* plan, cvmk_stream_t stream);
 
