@@ -624,29 +624,30 @@ struct Lowering {
         // the first images while the later ones are still being uploaded.
         const int chunks = (uses[ex_] == 1 && !is_head[ex_]) ? batch_chunks(N) : 1;
         const int per = N / chunks;
+        // plan 0 covers the whole batch (one launch when the input is already on the device);
+        // plans 1.. cover one chunk each
         std::vector<cvmk_stem_conv_plan*> plans;
-        for (int c = 0; c < chunks; ++c) {
+        for (int c = -1; c < (chunks > 1 ? chunks : 0); ++c) {
           cvmk_stem_conv_desc cd = sd;
-          cd.N = per;
-          cd.x = sd.x + (size_t)c * per * C * H * W;
-          cd.y = (int8_t*)sd.y + (size_t)c * per * OH * OW * OC;
+          if (c >= 0) {
+            cd.N = per;
+            cd.x = sd.x + (size_t)c * per * C * H * W;
+            cd.y = (int8_t*)sd.y + (size_t)c * per * OH * OW * OC;
+          }
           void* mem = nullptr;
           CHECK(posix_memalign(&mem, 64, sizeof(cvmk_stem_conv_plan)) == 0);
           ex.stem_plans_.emplace_back((cvmk_stem_conv_plan*)mem, plan_deleter);
           KERNEL_OK(cvmk_conv2d_stem_prepare(&cd, ex.stem_plans_.back().get()));
           plans.push_back(ex.stem_plans_.back().get());
         }
-        add_step(label + "[stem]", [plans](cudaStream_t s) {
-          for (auto* pl : plans) {
-            const int rc = cvmk_conv2d_stem_launch(pl, s);
-            if (rc != CVMK_OK) return rc;
-          }
-          return (int)CVMK_OK;
-        });
+        cvmk_stem_conv_plan* whole = plans[0];
+        add_step(label + "[stem]", [whole](cudaStream_t s) { return cvmk_conv2d_stem_launch(whole, s); });
         if (chunks > 1) {
           ex.chunk_bytes_ = (size_t)per * C * H * W;
-          for (auto* pl : plans)
+          for (size_t c = 1; c < plans.size(); ++c) {
+            cvmk_stem_conv_plan* pl = plans[c];
             ex.steps_.back().chunk.push_back([pl](cudaStream_t s) { return cvmk_conv2d_stem_launch(pl, s); });
+          }
         }
         return;
       }
