@@ -1031,7 +1031,13 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
     if (plan->tma_out && (budget - resident - 4 * group_bytes) / halo_stage >= 3) plan->io_bufs = 2;
   } else if (plan->tma_out && !dev_env("CVM_B200_SINGLE_STAGING")) {
     auto ring_depth = [&](int k) { return (budget - 4 * group_bytes) / ((BLOCK_M + bn) * k); };
-    if (ring_depth(bk) >= 3) plan->io_bufs = 2;
+    // Long reductions want the shared memory for operands in flight (three 128-byte K blocks
+    // cover the load latency, three 64-byte ones do not), short ones for the second staging buffer
+    // (their tiles are bound by the epilogue).
+    const bool deep_ring_first = bk == 128 && k_all >= 256 && ring_depth(128) < 3 &&
+                                 (budget - 2 * group_bytes) / ((BLOCK_M + bn) * 128) >= 3 && !dev_env("CVM_B200_DOUBLE_STAGING");
+    if (deep_ring_first) plan->io_bufs = 1;
+    else if (ring_depth(bk) >= 3) plan->io_bufs = 2;
     else if (bk == 128 && k_all <= 512 && ring_depth(64) >= 3) { plan->io_bufs = 2; bk = 64; }
   }
   plan->block_k = bk;
