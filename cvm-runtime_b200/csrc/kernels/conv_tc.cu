@@ -286,16 +286,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // Every filter tap multiplies a window of that halo: the descriptor starts (fy * halo_w + fx)
   // rows in and steps halo_w rows per 8-pixel group (the swizzle is a function of the shared-memory
   // address, so any 16-byte aligned start inside the swizzled halo reads consistently).
-  // a_mode 4 is the halo mode with the whole weight matrix resident in shared memory (one channel
-  // block, one N tile): the weights are loaded once per CTA in front of the ring and a stage is
-  // the halo alone.
+  // a_mode 4 is the halo mode with the whole weight matrix resident in shared memory (one or two
+  // channel blocks, one N tile): the weights are loaded once per CTA in front of the ring and a
+  // stage is the halo alone.
   const bool halo = p.a_mode >= 3;
   const bool w_resident = p.a_mode == 4;
   const int halo_w = p.patch_w + p.kw - 1;
   const int halo_bytes = halo_w * (p.patch_h + p.kh - 1) * p.block_k;
   const int halo_pad = (halo_bytes + 1023) & ~1023;
   const int taps = p.kh * p.kw;
-  const int resident_bytes = w_resident ? taps * b_bytes : 0;
+  const int resident_bytes = w_resident ? p.num_kb * taps * b_bytes : 0;   // [channel block][tap][block_n x block_k]
   uint8_t* const ring = smem + resident_bytes;
   const int stage_bytes = w_resident ? halo_pad : (halo ? halo_pad + taps * b_bytes : p.units * unit_bytes);
   const int num_kb = p.num_kb;  // ring stages consumed per tile
@@ -387,15 +387,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t wb = smem_u32(&bar_weights);
         if (leader) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wb), "r"((uint32_t)resident_bytes) : "memory");
         uint32_t dst = smem_u32(smem);
-        int kcol = 0;
-        for (int t = 0; t < taps; ++t) {
-          if (leader) asm volatile(
-              "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-              " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(wb),
-              "r"(kcol), "r"(0)
-              : "memory");
-          dst += (uint32_t)b_bytes;
-          kcol += p.c;
+        for (int cb = 0; cb < p.num_kb; ++cb) {
+          int kcol = cb * p.block_k;
+          for (int t = 0; t < taps; ++t) {
+            if (leader) asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(wb),
+                "r"(kcol), "r"(0)
+                : "memory");
+            dst += (uint32_t)b_bytes;
+            kcol += p.c;
+          }
         }
       }
       const TileOrigin to_first = tile_origin(p, (int)blockIdx.x);
@@ -565,7 +567,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (halo) {
             // 3 x 3 taps x two K slices of the 64-channel block, straight line
             TSTART(ti);
-            uint32_t bl = w_resident ? w_lo0 : st + halo_pad_q;
+            uint32_t bl = w_resident ? w_lo0 + (uint32_t)(kb * 9) * b_q : st + halo_pad_q;
 #pragma unroll
             for (int fy = 0; fy < 3; ++fy) {
               uint32_t al = st + (uint32_t)fy * halo_row_q;
@@ -1018,13 +1020,18 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   const int64_t k_all = (int64_t)d->KH * d->KW * d->C;
   const int budget = SMEM_DYNAMIC_MAX - 1024;
   plan->io_bufs = 1;
-  // Weights resident in shared memory: one 64-channel block and one N tile, i.e. every tile of the
-  // launch multiplies the same 9 * bn * 64 bytes.  A ring stage is then the 12 KB halo alone.
+  // Weights resident in shared memory: one N tile, i.e. every tile of the launch multiplies the
+  // same 9 * bn * C bytes (up to 144 KB for 128 x 128 channels).  A ring stage is then the 12 KB
+  // halo alone.
   const int halo_pad = ((10 * 18 * bk) + 1023) & ~1023;
   int resident = 0;
-  if (halo && d->C == 64 && d->OC <= bn && !dev_env("CVM_B200_NO_RESIDENT_WEIGHTS")) {
-    resident = d->KH * d->KW * bn * bk;
-    plan->a_im2col = 4;
+  if (halo && d->OC <= bn && !dev_env("CVM_B200_NO_RESIDENT_WEIGHTS")) {
+    // all channel blocks (one or two) stay, if three halo stages and one staging buffer per group still fit
+    const int all = (d->C / bk) * d->KH * d->KW * bn * bk;
+    if (budget - all - 2 * group_bytes >= 3 * halo_pad) {
+      resident = all;
+      plan->a_im2col = 4;
+    }
   }
   const int halo_stage = halo ? (resident ? halo_pad : halo_pad + d->KH * d->KW * bn * bk) : 0;
   if (halo) {
