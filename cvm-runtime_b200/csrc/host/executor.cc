@@ -1211,14 +1211,20 @@ struct Lowering {
   void lower_gvc(uint32_t nid) {
     const Node& n = g.nodes[nid];
     const std::string label = "get_valid_counts:" + n.name();
-    const DevBuf x = canon_i32_view(g.entry_id(n.inputs[0]), label);
+    const uint32_t in_eid = g.entry_id(n.inputs[0]);
+    // Rows that are the network input, read by nobody else: the operator reads the uploaded bytes
+    // and applies the input clamp itself, instead of a copy of the whole tensor doing it first.
+    const bool from_raw = in_eid == data_eid && raw_in.dtype == CVMK_I32 && uses[in_eid] == 1 && !is_head[in_eid] &&
+                          !buf[in_eid].ptr && !dev_env("CVM_B200_NO_GVC_FROM_INPUT");
+    const DevBuf x = from_raw ? raw_in : canon_i32_view(in_eid, label);
+    const int clamp = from_raw ? data_range : 0;
     const DevBuf vc = materialize(g.entry_id(nid, 0));
     const DevBuf y = materialize(g.entry_id(nid, 1));
     CHECK(vc.dtype == CVMK_I32 && y.dtype == CVMK_I32);
     const int B = (int)x.shape[0], N = (int)x.shape[1], K = (int)x.shape[2];
     const int thr = (int)n.attrs.i("score_threshold");
-    add_step(label, [x, y, vc, B, N, K, thr](cudaStream_t s) {
-      return cvmk_get_valid_counts((const int32_t*)x.ptr, (int32_t*)y.ptr, (int32_t*)vc.ptr, B, N, K, thr, s);
+    add_step(label, [x, y, vc, B, N, K, thr, clamp](cudaStream_t s) {
+      return cvmk_get_valid_counts_clamped((const int32_t*)x.ptr, (int32_t*)y.ptr, (int32_t*)vc.ptr, B, N, K, thr, clamp, s);
     });
   }
 

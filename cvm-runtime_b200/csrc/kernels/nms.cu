@@ -95,9 +95,16 @@ __device__ __forceinline__ void fill_minus_one(int32_t* y, size_t begin, size_t 
 // still uses many SMs: every CTA first counts the valid rows of the whole image (scores only,
 // served by L2) to learn where its chunk lands and where the -1 tail begins, then compacts its own
 // chunk and fills its share of the tail.  No CTA waits for another.
+// `clamp`: every element is first brought into [-clamp, clamp] (the runtime's clamp of the network
+// input to its declared precision, when these rows ARE the network input); INT32_MAX = values as
+// they are, except that INT32_MIN becomes -INT32_MAX, which is what that clamp does at 32 bits.
+__device__ __forceinline__ int clampv(int v, int clamp) { return max(min(v, clamp), -clamp); }
+__device__ __forceinline__ int2 clamp2(int2 v, int clamp) { return make_int2(clampv(v.x, clamp), clampv(v.y, clamp)); }
+
+template <bool CLAMP>
 __global__ void __launch_bounds__(THREADS, 1) gvc6_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ y,
                                                           int32_t* __restrict__ valid_count, int N, int thr,
-                                                          int chunk_rows) {
+                                                          int chunk_rows, int clamp) {
   __shared__ int ws[WARPS + 1];
   __shared__ int red[2][WARPS];
   const int b = blockIdx.y, c = blockIdx.x;
@@ -109,7 +116,9 @@ __global__ void __launch_bounds__(THREADS, 1) gvc6_kernel(const int32_t* __restr
   // valid rows before this chunk, and in the whole image
   int before = 0, total_valid = 0;
   for (int j = threadIdx.x; j < N; j += THREADS) {
-    const int ok = xb[(size_t)j * 3].y > thr ? 1 : 0;
+    int score = xb[(size_t)j * 3].y;
+    if (CLAMP) score = clampv(score, clamp);
+    const int ok = score > thr ? 1 : 0;
     total_valid += ok;
     before += (j < row0) ? ok : 0;
   }
@@ -134,6 +143,7 @@ __global__ void __launch_bounds__(THREADS, 1) gvc6_kernel(const int32_t* __restr
         r[q][0] = xb[(size_t)(j0 + q) * 3];
         r[q][1] = xb[(size_t)(j0 + q) * 3 + 1];
         r[q][2] = xb[(size_t)(j0 + q) * 3 + 2];
+        if (CLAMP) { r[q][0] = clamp2(r[q][0], clamp); r[q][1] = clamp2(r[q][1], clamp); r[q][2] = clamp2(r[q][2], clamp); }
         if (r[q][0].y > thr) ok |= 1 << q;
       }
     }
@@ -162,7 +172,7 @@ __global__ void __launch_bounds__(THREADS, 1) gvc6_kernel(const int32_t* __restr
 
 __global__ void __launch_bounds__(THREADS) gvc_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ y,
                                                       int32_t* __restrict__ valid_count, int N, int K,
-                                                      int thr) {
+                                                      int thr, int clamp) {
   __shared__ int ws[WARPS + 1];
   const int b = blockIdx.x;
   const int32_t* xb = x + (size_t)b * N * K;
@@ -170,13 +180,13 @@ __global__ void __launch_bounds__(THREADS) gvc_kernel(const int32_t* __restrict_
   int running = 0;
   for (int base = 0; base < N; base += THREADS) {
     const int j = base + threadIdx.x;
-    const bool ok = j < N && xb[(size_t)j * K + 1] > thr;
+    const bool ok = j < N && clampv(xb[(size_t)j * K + 1], clamp) > thr;
     int total;
     const int pos = running + block_exclusive_scan(ok ? 1 : 0, ws, &total);
     if (ok) {
       const int32_t* src = xb + (size_t)j * K;
       int32_t* dst = yb + (size_t)pos * K;
-      for (int k = 0; k < K; ++k) dst[k] = src[k];
+      for (int k = 0; k < K; ++k) dst[k] = clampv(src[k], clamp);
     }
     running += total;
   }
@@ -798,7 +808,13 @@ using namespace cvmk;
 extern "C" int cvmk_get_valid_counts(const int32_t* x, int32_t* y, int32_t* valid_count, int32_t B,
                                      int32_t N, int32_t K, int32_t score_threshold,
                                      cvmk_stream_t stream) {
-  if (!x || !y || !valid_count || B < 1 || N < 1 || K < 2) {
+  return cvmk_get_valid_counts_clamped(x, y, valid_count, B, N, K, score_threshold, 0, stream);
+}
+
+extern "C" int cvmk_get_valid_counts_clamped(const int32_t* x, int32_t* y, int32_t* valid_count, int32_t B,
+                                             int32_t N, int32_t K, int32_t score_threshold, int32_t clamp,
+                                             cvmk_stream_t stream) {
+  if (!x || !y || !valid_count || B < 1 || N < 1 || K < 2 || clamp < 0) {
     set_error("get_valid_counts: bad argument");
     return CVMK_ERR_ARG;
   }
@@ -813,10 +829,15 @@ extern "C" int cvmk_get_valid_counts(const int32_t* x, int32_t* y, int32_t* vali
     if (chunks < 1) chunks = 1;
     int chunk_rows = ((N + chunks - 1) / chunks + 3) & ~3;
     chunks = (N + chunk_rows - 1) / chunk_rows;
-    gvc6_kernel<<<dim3((unsigned)chunks, (unsigned)B), THREADS, 0, (cudaStream_t)stream>>>(x, y, valid_count, N,
-                                                                                            score_threshold, chunk_rows);
+    if (clamp > 0)
+      gvc6_kernel<true><<<dim3((unsigned)chunks, (unsigned)B), THREADS, 0, (cudaStream_t)stream>>>(
+          x, y, valid_count, N, score_threshold, chunk_rows, clamp);
+    else
+      gvc6_kernel<false><<<dim3((unsigned)chunks, (unsigned)B), THREADS, 0, (cudaStream_t)stream>>>(
+          x, y, valid_count, N, score_threshold, chunk_rows, INT32_MAX);
   } else
-    gvc_kernel<<<B, THREADS, 0, (cudaStream_t)stream>>>(x, y, valid_count, N, K, score_threshold);
+    gvc_kernel<<<B, THREADS, 0, (cudaStream_t)stream>>>(x, y, valid_count, N, K, score_threshold,
+                                                        clamp > 0 ? clamp : INT32_MAX);
   return check_cuda(cudaGetLastError(), "gvc_kernel launch");
 }
 

@@ -345,6 +345,12 @@ CVMK_API int cvmk_conv2d_stem_launch(const cvmk_stem_conv_plan* plan, cvmk_strea
 CVMK_API int cvmk_get_valid_counts(const int32_t* x, int32_t* y, int32_t* valid_count, int32_t B,
                                    int32_t N, int32_t K, int32_t score_threshold,
                                    cvmk_stream_t stream);
+/* The same with every element of x first clamped to [-clamp, clamp] (clamp > 0): for rows that are
+ * the network input itself, which the runtime clamps to the declared precision on entry
+ * (src/runtime/graph_runtime.cc:379-386); clamp = 0 reads x as it is. */
+CVMK_API int cvmk_get_valid_counts_clamped(const int32_t* x, int32_t* y, int32_t* valid_count, int32_t B,
+                                           int32_t N, int32_t K, int32_t score_threshold, int32_t clamp,
+                                           cvmk_stream_t stream);
 typedef struct {
   const int32_t* x;
   const int32_t* valid_count;
