@@ -719,12 +719,14 @@ struct Lowering {
       d.x = (const int8_t*)xin.ptr; d.w = wdev; d.y = out.ptr; d.y_dtype = out.dtype;
       d.status = ex.status_dev_;
       d.ep = ch.ep;
+      d.workspace_bytes = cvmk_conv2d_tc_workspace_bytes(&d);   // > 0: few rows over a long K, cut along K
+      if (d.workspace_bytes > 0) d.workspace = act_alloc((size_t)d.workspace_bytes);
       void* mem = nullptr;
       CHECK(posix_memalign(&mem, 64, sizeof(cvmk_conv_plan)) == 0);
       ex.plans_.emplace_back((cvmk_conv_plan*)mem, plan_deleter);
       cvmk_conv_plan* plan = ex.plans_.back().get();
       KERNEL_OK(cvmk_conv2d_tc_prepare(&d, plan));
-      add_step(label + "[tc]", [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
+      add_step(label + (plan->k_slices > 1 ? "[tc,k-slices]" : "[tc]"), [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
       // Quarter-batch plans (every operand is batch-major, so a chunk is a contiguous slice).
       const int chunks = batch_chunks(d.N);
       if (chunks > 1 && xin.nhwc && out.nhwc) {

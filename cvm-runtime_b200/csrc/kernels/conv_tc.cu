@@ -112,6 +112,8 @@ struct ConvParams {
   int bias_static;      // the bias vector is a parameter: it may be read before the previous kernel has finished
   const int8_t* w;      // the weight matrix [oc, kh * kw * c] and its size, for the L2 warm-up
   unsigned w_bytes;
+  int k_slices;         // > 1: `oc` counts k_slices x oc_real virtual columns; column block s reduces over
+  int oc_real;          //      K slice s (c bytes long) of the real columns and writes int32 partial sums
   DevChain chain;
 };
 
@@ -233,12 +235,19 @@ __device__ long long g_conv_trace[17 * 512];
 
 // Origin of a tile: first output channel, and either the first linear output row (modes 0, 1) or
 // the corner (w, h, n) of the spatial patch (mode 2).
-struct TileOrigin { int n0, m0, cw, ch, cn; };
+struct TileOrigin { int n0, m0, cw, ch, cn, nb, k0; };   // nb: first weight row, k0: first K byte (K slices)
 __device__ __forceinline__ TileOrigin tile_origin(const ConvParams& p, int tile) {
   TileOrigin t;
   const int mt = fdiv(tile, p.fd_n_tiles);
   t.n0 = (tile - mt * p.num_n_tiles) * p.block_n;
   t.m0 = mt * BLOCK_M;
+  t.nb = t.n0;
+  t.k0 = 0;
+  if (p.k_slices > 1) {
+    const int s = t.n0 / p.oc_real;
+    t.nb = t.n0 - s * p.oc_real;
+    t.k0 = s * p.c;
+  }
   t.cw = t.ch = t.cn = 0;
   if (p.a_mode >= 2) {
     const int r = fdiv(mt, p.fd_tiles_w);
@@ -493,12 +502,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               asm volatile(
                   "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                   " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(bar),
-                  "r"(cc), "r"(m0)
+                  "r"(cc + to.k0), "r"(m0)
                   : "memory");
             asm volatile(
                 "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                 " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa + (uint32_t)a_bytes), "l"(reinterpret_cast<uint64_t>(&tmap_b)),
-                "r"(bar), "r"(kcol), "r"(to.n0)
+                "r"(bar), "r"(kcol + to.k0), "r"(to.nb)
                 : "memory");
           }
           if (mine) sa += (uint32_t)unit_bytes;
@@ -951,6 +960,54 @@ extern "C" int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d) {
   return 1;
 }
 
+// K slices for a pointwise layer of at most one M tile: 1 = not cut.  The slice count divides
+// the number of K blocks, leaves at least four blocks per slice, and is the smallest that makes
+// the best use of the SMs (tiles / (waves x SMs)).
+static int pick_k_slices(const cvmk_conv_desc& d, int bk, int bn) {
+  if (!is_pointwise(d) || (int64_t)d.N * d.OH * d.OW > BLOCK_M || d.OC % bn != 0 || d.C % bk != 0) return 1;
+  if (dev_env("CVM_B200_NO_SPLIT_K")) return 1;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaGetLastError();
+  const int blocks = d.C / bk, nt = d.OC / bn;
+  if (blocks < 8 || 2 * nt >= sms) return 1;
+  int best = 1;
+  double best_eff = (double)nt / sms;
+  for (int s = 2; s * 4 <= blocks; ++s) {
+    if (blocks % s) continue;
+    const int tiles = nt * s;
+    if (tiles > 4 * sms) break;
+    const double eff = (double)tiles / (double)(((tiles + sms - 1) / sms) * sms);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+  }
+  return best;
+}
+
+extern "C" int64_t cvmk_conv2d_tc_workspace_bytes(const cvmk_conv_desc* d) {
+  if (!d || !cvmk_conv2d_tc_supported(d)) return 0;
+  const int s = pick_k_slices(*d, pick_block_k(d->C), pick_block_n(d->OC));
+  return s > 1 ? (int64_t)d->N * d->OH * d->OW * s * d->OC * 4 : 0;
+}
+
+// Adds the k_slices partial sums of every output element and applies the chain.
+__global__ void __launch_bounds__(256) splitk_finish_kernel(const int32_t* __restrict__ part, void* y, int y_dtype, int m,
+                                                            int oc, int slices, const __grid_constant__ DevChain chain) {
+  const int quads = oc / 4;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m * quads) return;
+  const int row = i / quads, c0 = (i - row * quads) * 4;
+  const int4* src = reinterpret_cast<const int4*>(part + ((size_t)row * slices) * oc + c0);
+  int32_t v[4] = {0, 0, 0, 0};
+  for (int s = 0; s < slices; ++s) {
+    const int4 t = __ldg(src + (size_t)s * (oc / 4));
+    v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
+  }
+  const size_t lin = (size_t)row * oc + c0;
+  apply_chain<4>(chain, v, lin, c0, 1, nullptr, -1, 0);
+  if (y_dtype == CVMK_I8) *reinterpret_cast<uint32_t*>(reinterpret_cast<int8_t*>(y) + lin) = pack4(v[0], v[1], v[2], v[3]);
+  else *reinterpret_cast<int4*>(reinterpret_cast<int32_t*>(y) + lin) = make_int4(v[0], v[1], v[2], v[3]);
+}
+
 extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* plan) {
   if (!d || !plan) { set_error("conv2d_tc_prepare: null argument"); return CVMK_ERR_ARG; }
   if (!cvmk_conv2d_tc_supported(d)) {
@@ -999,7 +1056,13 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
 
   // Output path: int8 tiles leave through shared memory and a TMA store; the first int8 tensor
   // operand of the chain (a residual join) comes in by TMA as well.
-  plan->tma_out = d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !dev_env("CVM_B200_NO_TMA_STORE");
+  // Reductions cut along K write int32 partial sums into the caller's scratch with plain stores.
+  {
+    const int ks = pick_k_slices(*d, bk, bn);
+    const int64_t need = (int64_t)d->N * d->OH * d->OW * ks * d->OC * 4;
+    plan->k_slices = (ks > 1 && d->workspace && d->workspace_bytes >= need && ((uintptr_t)d->workspace & 15) == 0) ? ks : 1;
+  }
+  plan->tma_out = plan->k_slices == 1 && d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !dev_env("CVM_B200_NO_TMA_STORE");
   plan->res_step = -1;
   if (plan->tma_out) {
     for (int i = 0; i < d->ep.n; ++i) {
@@ -1017,7 +1080,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   // is still deep enough; short reductions (little work per output tile) may give up half of their
   // K block for it.
   const int group_bytes = plan->panels * BLOCK_M * plan->panel_bytes;
-  const int64_t k_all = (int64_t)d->KH * d->KW * d->C;
+  const int64_t k_all = (int64_t)d->KH * d->KW * d->C / plan->k_slices;   // per tile
   const int budget = SMEM_DYNAMIC_MAX - 1024;
   plan->io_bufs = 1;
   // Weights resident in shared memory: one N tile, i.e. every tile of the launch multiplies the
@@ -1120,7 +1183,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  int64_t tiles = num_m_tiles * num_n_tiles;
+  int64_t tiles = num_m_tiles * num_n_tiles * plan->k_slices;
   plan->grid = (int)(tiles < sms ? tiles : sms);
   return CVMK_OK;
 }
@@ -1168,6 +1231,19 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.w = d.w;
   p.w_bytes = (unsigned)std::min<int64_t>((int64_t)d.OC * d.KH * d.KW * d.C, (int64_t)1 << 30);
   p.tma_out = plan->tma_out; p.res_step = plan->res_step;
+  const int ks = plan->k_slices > 1 ? plan->k_slices : 1;
+  if (ks > 1) {   // virtual columns (slice, real column); int32 partial sums, no chain in this kernel
+    p.k_slices = ks;
+    p.oc_real = d.OC;
+    p.oc = ks * d.OC;
+    p.c = d.C / ks;
+    p.y = d.workspace;
+    p.y_dtype = CVMK_I32;
+    p.num_n_tiles *= ks;
+    p.num_units = d.C / ks / plan->block_k;
+    p.num_kb = (p.num_units + p.units - 1) / p.units;
+    p.fd_n_tiles = make_fastdiv(p.num_n_tiles);
+  }
 #ifdef CVMK_CONV_TIMING
   p.dbg = getenv("CVM_DBG") ? atoi(getenv("CVM_DBG")) : 0;
   if (getenv("CVM_HINT")) {
@@ -1179,6 +1255,8 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.io_bufs = plan->io_bufs; p.ring_bytes = plan->ring_bytes;
   int rc = lower_chain(d.ep, &p.chain);
   if (rc != CVMK_OK) return rc;
+  DevChain finish_chain = p.chain;
+  if (ks > 1) p.chain.n = 0;
   // lower_chain() may merge steps: find the TMA-served operand again by its pointer.
   if (plan->res_step >= 0) {
     const void* want = d.ep.s[plan->res_step].ptr;
@@ -1267,7 +1345,15 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   static const bool pdl = dev_env("CVM_B200_NO_PDL") == nullptr;
   cfg.attrs = &attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return check_cuda(cudaLaunchKernelEx(&cfg, conv_tc_kernel, ta, tb, ty, tr, p), "conv_tc_kernel launch");
+  if (check_cuda(cudaLaunchKernelEx(&cfg, conv_tc_kernel, ta, tb, ty, tr, p), "conv_tc_kernel launch")) return CVMK_ERR_CUDA;
+  if (ks > 1) {
+    const int m = d.N * d.OH * d.OW;
+    const int work = m * (d.OC / 4);
+    splitk_finish_kernel<<<(work + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const int32_t*>(d.workspace), d.y, d.y_dtype, m, d.OC, ks, finish_chain);
+    return check_cuda(cudaGetLastError(), "splitk_finish_kernel launch");
+  }
+  return CVMK_OK;
 }
 
 #ifdef CVMK_CONV_TIMING

@@ -121,6 +121,13 @@ typedef struct {
    * (it stages the bias and warms L2 with the weights while it waits for its turn). */
   int32_t bias_static;
   int32_t reserved0;
+  /* Optional scratch for reductions cut along K (dense layers of a few rows over a long K, whose
+   * few output tiles would leave most SMs idle): cvmk_conv2d_tc_workspace_bytes() says how much the
+   * shape wants (0: it is not cut).  With at least that much here, K slices run as separate tiles
+   * that write int32 partial sums, and a second small kernel adds them and applies the chain.
+   * Sums of integers: the result is the same bit for bit. */
+  void* workspace;
+  int64_t workspace_bytes;
   cvmk_epilogue ep;
 } cvmk_conv_desc;
 
@@ -142,9 +149,12 @@ typedef struct __attribute__((aligned(64))) {
   int32_t io_bufs;    /* staging buffers per epilogue group: 1 or 2 */
   int32_t ring_bytes; /* bytes of the operand ring in shared memory */
   int32_t reserved[4];  /* [0..2] patch width / height / images (a_im2col = 2, 3), [3] (tap, channel block) units per ring stage */
+  int32_t k_slices;   /* > 1: the reduction is cut into this many slices (see cvmk_conv_desc.workspace) */
+  int32_t pad_[3];
 } cvmk_conv_plan;
 
 CVMK_API int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d);
+CVMK_API int64_t cvmk_conv2d_tc_workspace_bytes(const cvmk_conv_desc* d);
 CVMK_API int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* plan);
 CVMK_API int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t stream);
 
