@@ -726,7 +726,7 @@ struct Lowering {
       ex.plans_.emplace_back((cvmk_conv_plan*)mem, plan_deleter);
       cvmk_conv_plan* plan = ex.plans_.back().get();
       KERNEL_OK(cvmk_conv2d_tc_prepare(&d, plan));
-      add_step(label + (plan->k_slices > 1 ? "[tc,k-slices]" : "[tc]"), [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
+      add_step(label + (plan->k_slices > 1 ? ":k-slices[tc]" : "[tc]"), [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
       // Quarter-batch plans (every operand is batch-major, so a chunk is a contiguous slice).
       const int chunks = batch_chunks(d.N);
       if (chunks > 1 && xin.nhwc && out.nhwc) {
