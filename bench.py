@@ -735,12 +735,24 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="images per GPU (default 256; ssd_tail 64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the extra metrics / strong-scaling block")
+    ap.add_argument("--inferences", type=int, default=0,
+                    help="profiling aid: load the workload, run this many plain inferences through the C-ABI and exit "
+                         "(no timing, no JSON line); what a profiler capture of a few launches needs")
     args = ap.parse_args()
     if args.batch is None:
         args.batch = DEFAULT_BATCH.get(args.workload, 256)
     if args.impl == "reference":
         pkg = ge.load_package()
         run_reference(args, pkg.workloads, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
+        return
+    if args.inferences > 0:
+        pkg = ge.load_package()
+        js, pb, x = make_workload(pkg.workloads, args.workload, args.batch)
+        net = pkg.runtime.CVMAPILoadModel(js, pb, 0)
+        for _ in range(args.inferences):
+            pkg.runtime.inference_bytes(net, x)
+        pkg.runtime.CVMAPIFreeModel(net)
+        print("ran %d inference(s) of %s batch %d" % (args.inferences, args.workload, args.batch))
         return
     args.warmup = max(args.warmup, 3)
     run_ours(args)

@@ -236,16 +236,35 @@ __global__ void __launch_bounds__(256) depthwise3x3_kernel(const __grid_constant
 // channels.  The input rows of the band are copied into shared memory once with 16-byte
 // asynchronous copies (zeros where the filter reaches outside the image), so every input byte
 // crosses L2 -> SM once per band instead of three times, and all boundary handling is done there.
-// A thread then owns 4 channels (one 32-bit word per pixel) and walks strips of 4 output pixels:
-// the 36 weights sit in registers as words with one non-zero byte each, so that
-// dp4a(input word, weight word, acc) multiplies exactly one channel of the packed input word --
-// one instruction per product and no unpacking of the activations.  A warp covers CB/4
+// A thread then owns 4 channels (one 32-bit word per pixel) and walks strips of 4 output pixels.
+// The words of four neighbouring pixels are transposed in registers (eight byte permutes) into
+// four words that each hold ONE channel at four consecutive pixels; a funnel shift moves the
+// window of an output pixel to byte 0, and one dp4a against the word (w[fy][0], w[fy][1],
+// w[fy][2], 0) of that channel multiplies a whole filter row: three multiply instructions per
+// output element instead of nine, on a part whose integer multiply pipe runs at half rate and was
+// the limit of the form that multiplied tap by tap.  A warp covers CB/4
 // consecutive channel words of 32*4/CB rows; the row pitch is padded so that those rows fall into
 // different banks.  The requantisation is the packed form of the tensor-core kernels (multiply-add
 // into the upper half word, clamp on s16x2, byte permutes).
 // Reproduces groupwise_conv2d with groups = C (src/runtime/cpu/ops/ops.cc:333-366).
+// Division of a non-negative 31-bit number by a divisor fixed at launch: q = umulhi(n, mul) >> shr
+// (mul = ceil(2^(31 + ceil(log2 d)) / d)); d = 1 is flagged by mul = 0.
+struct DwDiv { uint32_t mul, shr; };
+__device__ __forceinline__ int dw_div(int n, const DwDiv& d) { return d.mul ? (int)(__umulhi((uint32_t)n, d.mul) >> d.shr) : n; }
+static DwDiv make_dw_div(int d) {
+  DwDiv f = {0, 0};
+  if (d <= 1) return f;
+  int lg = 0;
+  while ((1LL << lg) < d) ++lg;
+  f.mul = (uint32_t)((((uint64_t)1 << (31 + lg)) + (uint64_t)d - 1) / (uint64_t)d);
+  f.shr = (uint32_t)(lg - 1);
+  return f;
+}
+
 struct Dw3Params {
   const int8_t* x; const int8_t* w; const int32_t* bias; int8_t* y;
+  DwDiv div_per_row, div_strips;   // by xw * (cb_words / 4) and by strips
+  int vec_log2;                    // log2(cb_words / 4)
   int N, H, W, C, OH, OW, ph, pw;
   int cb_words;        // channel words per block (CB / 4): 8, 16 or 32
   int rows_per_tile;   // R
@@ -257,6 +276,16 @@ struct Dw3Params {
   uint32_t lo, hi;     // clamp, replicated into both halves of an s16x2 word
   int relu;            // the clamp's lower bound is 0
 };
+
+// 4 x 4 byte transpose: words a, b, c, d (4 bytes each) -> t[k] = (a.k, b.k, c.k, d.k)
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&t)[4]) {
+  const uint32_t ab01 = __byte_perm(a, b, 0x5140), cd01 = __byte_perm(c, d, 0x5140);   // (a0 b0 a1 b1), (c0 d0 c1 d1)
+  const uint32_t ab23 = __byte_perm(a, b, 0x7362), cd23 = __byte_perm(c, d, 0x7362);   // (a2 b2 a3 b3), (c2 d2 c3 d3)
+  t[0] = __byte_perm(ab01, cd01, 0x5410);
+  t[1] = __byte_perm(ab01, cd01, 0x7632);
+  t[2] = __byte_perm(ab23, cd23, 0x5410);
+  t[3] = __byte_perm(ab23, cd23, 0x7632);
+}
 
 template <int S>
 __global__ void __launch_bounds__(256) dw3x3_tile_kernel(const __grid_constant__ Dw3Params p) {
@@ -278,8 +307,8 @@ __global__ void __launch_bounds__(256) dw3x3_tile_kernel(const __grid_constant__
   const int vecs = cbw / 4;                     // 16-byte vectors per pixel
   const int per_row = p.xw * vecs;
   for (int idx = tid; idx < in_rows * per_row; idx += 256) {
-    const int r = idx / per_row, rem = idx - r * per_row;
-    const int xs = rem / vecs, v = rem - xs * vecs;
+    const int r = dw_div(idx, p.div_per_row), rem = idx - r * per_row;
+    const int xs = rem >> p.vec_log2, v = rem - (xs << p.vec_log2);
     const int iy = iy0 + r, ix = xs - p.pw;
     uint32_t* dst = tile + (size_t)r * p.pitch + xs * cbw + v * 4;
     if (iy >= 0 && iy < p.H && ix >= 0 && ix < p.W) {
@@ -292,12 +321,14 @@ __global__ void __launch_bounds__(256) dw3x3_tile_kernel(const __grid_constant__
   asm volatile("cp.async.commit_group;" ::: "memory");
   // ---- weights and bias of this thread's four channels (meanwhile)
   const int cw = lane % cbw, rr = lane / cbw, rows_per_warp = 32 / cbw;
-  int wm[9][4];
+  uint32_t wrow[3][4];   // wrow[fy][k] = (w[fy][0], w[fy][1], w[fy][2], 0) of channel k
 #pragma unroll
-  for (int tap = 0; tap < 9; ++tap) {
-    const int w = __ldg(reinterpret_cast<const int*>(p.w + (int64_t)tap * p.C + c0) + cw);
+  for (int fy = 0; fy < 3; ++fy) {
+    uint32_t w3[3];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) wm[tap][k] = w & (0xff << (8 * k));
+    for (int fx = 0; fx < 3; ++fx)
+      w3[fx] = (uint32_t)__ldg(reinterpret_cast<const int*>(p.w + (int64_t)(fy * 3 + fx) * p.C + c0) + cw);
+    transpose4x4(w3[0], w3[1], w3[2], 0u, wrow[fy]);
   }
   int bq[4] = {0, 0, 0, 0};   // (bias + rounding addend) * mul
   {
@@ -311,7 +342,7 @@ __global__ void __launch_bounds__(256) dw3x3_tile_kernel(const __grid_constant__
   // ---- compute: warp items = (group of rows_per_warp rows, strip of 4 pixels)
   const int groups = (rows_here + rows_per_warp - 1) / rows_per_warp;
   for (int item = warp; item < groups * p.strips; item += 8) {
-    const int g = item / p.strips, sidx = item - g * p.strips;
+    const int g = dw_div(item, p.div_strips), sidx = item - g * p.strips;
     const int orow = g * rows_per_warp + rr;
     if (orow >= rows_here) continue;
     const int ox0 = sidx * PX;
@@ -323,17 +354,25 @@ __global__ void __launch_bounds__(256) dw3x3_tile_kernel(const __grid_constant__
       for (int k = 0; k < 4; ++k) acc[q][k] = 0;
 #pragma unroll
     for (int fy = 0; fy < 3; ++fy) {
-      int xin[IN];
+      uint32_t xin[12];
 #pragma unroll
-      for (int j = 0; j < IN; ++j) xin[j] = (int)base[(size_t)fy * p.pitch + j * cbw];
+      for (int j = 0; j < 12; ++j) xin[j] = j < IN ? base[(size_t)fy * p.pitch + j * cbw] : 0u;
+      // t[g][k]: channel k at input pixels 4g .. 4g + 3 of the strip
+      uint32_t t[3][4];
+      transpose4x4(xin[0], xin[1], xin[2], xin[3], t[0]);
+      transpose4x4(xin[4], xin[5], xin[6], xin[7], t[1]);
+      if (S == 2) {
 #pragma unroll
-      for (int j = 0; j < IN; ++j) {
+        for (int k = 0; k < 4; ++k) t[2][k] = __byte_perm(xin[8], 0u, 0x4440 + k);   // pixel 8 alone
+      }
 #pragma unroll
-        for (int fx = 0; fx < 3; ++fx) {
-          if ((j - fx) % S != 0 || j - fx < 0 || (j - fx) / S >= PX) continue;  // resolved at compile time
-          const int q = (j - fx) / S;
+      for (int q = 0; q < PX; ++q) {
+        const int first = q * S;            // first input pixel of this output's window
+        const int g = first >> 2, sh = (first & 3) * 8;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) acc[q][k] = __dp4a(xin[j], wm[fy * 3 + fx][k], acc[q][k]);
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t win = sh ? __funnelshift_r(t[g][k], t[g + 1][k], sh) : t[g][k];
+          acc[q][k] = __dp4a((int)win, (int)wrow[fy][k], acc[q][k]);
         }
       }
     }
@@ -518,6 +557,9 @@ int try_dw3x3_tile(const cvmk_conv_direct_desc* d, const DevChain& chain, cudaSt
   if (smem_of(R) > 48 * 1024) return -1;
   p.rows_per_tile = R;
   p.tiles_y = (d->OH + R - 1) / R;
+  p.div_per_row = make_dw_div(p.xw * (p.cb_words / 4));
+  p.div_strips = make_dw_div(p.strips);
+  p.vec_log2 = p.cb_words == 8 ? 1 : (p.cb_words == 16 ? 2 : 3);
   p.mul = 1 << (16 - sh);
   p.add = (int)add;
   auto x2 = [](int64_t v) { return (uint32_t)((uint32_t)(uint16_t)(int16_t)v | ((uint32_t)(uint16_t)(int16_t)v << 16)); };
