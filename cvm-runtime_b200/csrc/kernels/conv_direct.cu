@@ -546,15 +546,16 @@ int try_dw3x3_tile(const cvmk_conv_direct_desc* d, const DevChain& chain, cudaSt
   const int rows_per_warp = 32 / p.cb_words;
   int R = d->OH;
   auto smem_of = [&](int r) { return ((r - 1) * S + 3) * p.pitch * 4; };
+  // up to 44 KB a CTA (four or five per SM); wide images whose shortest band needs more take up to 100 KB
   while (R > rows_per_warp && smem_of(R) > 44 * 1024) --R;
-  if (smem_of(R) > 44 * 1024) return -1;
+  if (smem_of(R) > 100 * 1024) return -1;
   // enough tiles to fill the GPU a few times over
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   while (R > 2 * rows_per_warp && (int64_t)d->N * ((d->OH + R - 1) / R) * p.tiles_c < 6LL * sms) R = (R + 1) / 2;
   if (R > rows_per_warp) R = R / rows_per_warp * rows_per_warp;   // whole warp row groups
-  if (smem_of(R) > 48 * 1024) return -1;
+  if (smem_of(R) > 100 * 1024) return -1;
   p.rows_per_tile = R;
   p.tiles_y = (d->OH + R - 1) / R;
   p.div_per_row = make_dw_div(p.xw * (p.cb_words / 4));
@@ -568,6 +569,16 @@ int try_dw3x3_tile(const cvmk_conv_direct_desc* d, const DevChain& chain, cudaSt
   const int64_t tiles = (int64_t)d->N * p.tiles_y * p.tiles_c;
   if (tiles > INT32_MAX) return -1;
   const int smem = smem_of(R);
+  if (smem > 48 * 1024) {
+    static bool attr_set_dev[64] = {false};
+    bool& attr_set = attr_set_dev[dev & 63];
+    if (!attr_set) {
+      if (check_cuda(cudaFuncSetAttribute(dw3x3_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024), "cudaFuncSetAttribute(dw3x3_tile_kernel)") ||
+          check_cuda(cudaFuncSetAttribute(dw3x3_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024), "cudaFuncSetAttribute(dw3x3_tile_kernel)"))
+        return CVMK_ERR_CUDA;
+      attr_set = true;
+    }
+  }
   if (S == 1) dw3x3_tile_kernel<1><<<(unsigned)tiles, 256, smem, s>>>(p);
   else dw3x3_tile_kernel<2><<<(unsigned)tiles, 256, smem, s>>>(p);
   return check_cuda(cudaGetLastError(), "dw3x3_tile_kernel launch");
