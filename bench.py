@@ -441,6 +441,26 @@ class Harness:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
+    def h2d_rate(self, nbytes, reps=12):
+        """GB/s of plain page-locked -> device copies of `nbytes`, every rank copying at the same
+        time (barrier before the timed copies, slowest rank counts): the rate the box gives the
+        uploads of an end-to-end step when all GPUs ask at once."""
+        torch = self.torch
+        src = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+        dst = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        for _ in range(2):
+            dst.copy_(src, non_blocking=True)
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            dst.copy_(src, non_blocking=True)
+        e1.record()
+        e1.synchronize()
+        ms = self.max_over_ranks(e0.elapsed_time(e1))
+        self.barrier()
+        return nbytes * reps / (ms * 1e-3) / 1e9
+
     def close(self):
         if self.dist:
             self.dist.destroy_process_group()
@@ -574,6 +594,7 @@ def run_ours(args):
     rt, wl = h.rt, h.wl
     rank, world = h.rank, h.world
     head = h.measure(args.workload, args.batch, args.steps, args.warmup, sample_clocks=True, flush=None)
+    h2d_gbs = h.h2d_rate(head["in_bytes"])
     peaks = measured_peaks()
     line = None
     if rank == 0:
@@ -623,7 +644,10 @@ def run_ours(args):
                     "h2d_bytes_per_step": head["in_bytes"], "d2h_bytes_per_step": head["out_bytes"] + 4,
                     "ms_per_step": 1e3 * e2e_med, "ms_per_step_best": 1e3 * e2e_best, "repeats": e2e_reps,
                     "input": "page-locked host buffer",
-                    "pageable_input_value": total_units / head["e2e_pageable"][0]},
+                    "pageable_input_value": total_units / head["e2e_pageable"][0],
+                    # what the uploads alone would allow: every rank copying its input at once
+                    "h2d_copy_gbs_per_gpu": h2d_gbs,
+                    "upload_bound_value": total_units / (head["in_bytes"] / (h2d_gbs * 1e9))},
             "gpu_launches": head["launches"] * args.steps * head["repeats"],
             "device_bytes": head["device_bytes"], "activation_bytes": head["activation_bytes"],
             "clocks": head["clocks"], "roofline": roofline,
