@@ -134,6 +134,18 @@ def op_cases():
     add("conv_stem_fused_4ch_nobias", lambda: conv_case(34, 2, 4, 20, 16, 64, 5, 2, 0, bias=False, shift=8))
     add("conv_stem_fused_1x1", lambda: conv_case(35, 2, 2, 9, 16, 32, 1, 1, 0, shift=3))
     add("conv_stem_fused_s3_rows", lambda: conv_case(36, 1, 3, 37, 32, 64, 7, 3, 2, shift=8, relu=True))
+    # more stems for the folded-stride kernel: odd heights, one and two channels, the widest filter,
+    # an input row wider than one TMA box (two boxes of 144 columns)
+    add("conv_stem_fused_3x3_s2_odd_h", lambda: conv_case(37, 3, 3, 37, 64, 32, 3, 2, 1, shift=7, relu=True))
+    add("conv_stem_fused_5x5_s1_2ch", lambda: conv_case(38, 2, 2, 19, 32, 64, 5, 1, 2, shift=8))
+    add("conv_stem_fused_8x8_s2_1ch", lambda: conv_case(39, 2, 1, 40, 48, 32, 8, 2, 3, shift=8, relu=True))
+    add("conv_stem_fused_7x7_s2_two_boxes", lambda: conv_case(40, 1, 3, 21, 288, 64, 7, 2, 3, shift=9, relu=True))
+    add("conv_stem_fused_4x4_s1_pad0", lambda: conv_case(41, 2, 4, 12, 16, 128, 4, 1, 0, shift=8))
+    # 3x3 over 128 -> 128 channels: both channel blocks of the weights resident in shared memory
+    add("conv_halo_resident_128", lambda: conv_case(42, 2, 128, 20, 24, 128, 3, 1, 1, shift=10, relu=True))
+    # depthwise 3x3 over an image wide enough that a band of rows needs more than 48 KB of shared memory
+    add("depthwise_3x3_wide_band", lambda: conv_case(43, 1, 32, 9, 256, 32, 3, 1, 1, groups=32, shift=6, relu=True))
+    add("depthwise_3x3_s2_wide_band", lambda: conv_case(44, 1, 64, 11, 192, 64, 3, 2, 1, groups=64, shift=6))
     # batch 8: the inference uploads the batch in four chunks and runs the stem per chunk
     add("conv_stem_fused_b8_chunked", lambda: conv_case(38, 8, 3, 20, 16, 32, 3, 2, 1, shift=7, relu=True))
     def stem_generic():
@@ -214,6 +226,24 @@ def op_cases():
         return f
     add("dense_tc", dense_case(11, 5, 64, 24))
     add("dense_odd", dense_case(12, 3, 50, 10, bias=False))
+
+    # dense layers of a few rows over a long reduction: cut along K into tiles of their own,
+    # partial sums added by a second kernel that also applies the chain
+    def dense_long_k(seed, m, k, units, second=None, relu=True):
+        def f():
+            g = wl.GraphBuilder(seed)
+            x = rnd(np.random.RandomState(seed), (m, k), 8)
+            d = g.var("data", x.shape, 8)
+            y = g.dense(d, units, shift=0, relu=relu)
+            if second:
+                y = g.dense(y, second)          # int32 head straight from the sums
+            js, pb = g.finish(y)
+            return js, pb, x
+        return f
+    add("dense_k_slices_int8", dense_long_k(13, 7, 4096, 512))
+    add("dense_k_slices_chain", dense_long_k(14, 33, 2048, 1024, second=256, relu=False))
+    add("dense_k_slices_head", lambda: (lambda g, x: (lambda d: g.finish(g.dense(d, 256)) + (x,))(g.var("data", x.shape, 8)))(
+        wl.GraphBuilder(15), rnd(np.random.RandomState(15), (4, 3072), 8)))
 
     def unary(func, attrs, prec=16, shape=(2, 3, 5, 7), seed=20, special=None):
         def f():
