@@ -2,6 +2,7 @@
 #include "executor.h"
 #include <cuda.h>
 #include <algorithm>
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -1300,8 +1301,8 @@ struct Lowering {
     for (uint32_t nid = 0; nid < g.nodes.size(); ++nid)
       for (const auto& e : g.nodes[nid].inputs)
         if (Executor::ActBuf* a = of_entry[g.entry_id(e)]) a->last = std::max(a->last, group_pos(nid));
-    if (ex.prefix_steps_ > 0) {
-      const int p = step_pos[ex.prefix_steps_ - 1];
+    if (ex.prefix_max_ > 0) {
+      const int p = step_pos[ex.prefix_max_ - 1];
       for (auto& a : act)
         if (a.first <= p) { a.first = -1; a.last = std::max(a.last, p); }
     }
@@ -1406,12 +1407,11 @@ struct Lowering {
       const std::string tag = "[stem]";
       const bool first = !ex.steps_.empty() && ex.steps_[0].chunk.size() > 1 && ex.steps_[0].label.size() >= tag.size() &&
                          ex.steps_[0].label.compare(ex.steps_[0].label.size() - tag.size(), tag.size(), tag) == 0;
-      size_t cap = 6;   // ResNet-50: stem, pooling and the first bottleneck block take about as long as the upload
-      if (const char* e = dev_env("CVM_B200_PREFIX_STEPS")) cap = (size_t)atoi(e);
-      ex.prefix_steps_ = 0;
+      const size_t cap = 24;   // the lengths actually used are chosen after the load-time measurements
+      ex.prefix_max_ = 0;
       if (first)
-        while (ex.prefix_steps_ < ex.steps_.size() && ex.prefix_steps_ < cap && ex.steps_[ex.prefix_steps_].chunk.size() == ex.steps_[0].chunk.size())
-          ++ex.prefix_steps_;
+        while (ex.prefix_max_ < ex.steps_.size() && ex.prefix_max_ < cap && ex.steps_[ex.prefix_max_].chunk.size() == ex.steps_[0].chunk.size())
+          ++ex.prefix_max_;
     }
     plan_activations(order);
     // heads: row-major staging + pinned host mirrors
@@ -1457,24 +1457,98 @@ Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
   Enqueue(stream_);
   CUDA_OK(cudaStreamSynchronize(stream_));
   if (use_graph_) {
-    if (prefix_steps_ > 0) {
+    ChoosePrefixes();
+    if (prefix_steps_ > 0 || prefix_steps_pageable_ > 0) {
       CUDA_OK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
       chunk_events_.resize(steps_[0].chunk.size());
       for (auto& e : chunk_events_) CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     }
-    cudaGraph_t graph = nullptr;
-    CUDA_OK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
-    Enqueue(stream_, prefix_steps_);  // the chunked prefix is launched outside the graph
-    CUDA_OK(cudaStreamEndCapture(stream_, &graph));
-    CUDA_OK(cudaGraphInstantiate(&graph_exec_, graph, 0));
-    CUDA_OK(cudaGraphDestroy(graph));
+    auto capture_from = [&](size_t first, cudaGraphExec_t* exec) {
+      cudaGraph_t graph = nullptr;
+      CUDA_OK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+      Enqueue(stream_, first);  // the chunked prefix is launched outside the graph
+      CUDA_OK(cudaStreamEndCapture(stream_, &graph));
+      CUDA_OK(cudaGraphInstantiate(exec, graph, 0));
+      CUDA_OK(cudaGraphDestroy(graph));
+    };
+    capture_from(prefix_steps_, &graph_exec_);
+    if (prefix_steps_pageable_ != prefix_steps_) capture_from(prefix_steps_pageable_, &graph_exec_pageable_);
   }
+}
+
+bool Executor::IsDirect(const void* input) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, input) == cudaSuccess)
+    return at.type == cudaMemoryTypeHost || at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+  cudaGetLastError();
+  return false;
+}
+
+// How many leading steps to run chunk by chunk: the fewest whose device time, measured here step
+// by step on the whole batch and scaled by 1.3 (a quarter of the batch runs less efficiently than
+// the whole), reaches the time the upload takes -- measured here too, once for a page-locked source
+// and once through the staging path a pageable source takes.
+void Executor::ChoosePrefixes() {
+  prefix_steps_ = prefix_steps_pageable_ = 0;
+  if (prefix_max_ == 0 || dev_env("CVM_B200_NO_UPLOAD_OVERLAP")) { prefix_max_ = 0; return; }
+  if (const char* e = dev_env("CVM_B200_PREFIX_STEPS")) {
+    prefix_steps_ = prefix_steps_pageable_ = std::min(prefix_max_, (size_t)atoi(e));
+    return;
+  }
+  std::vector<cudaEvent_t> ev(prefix_max_ + 1);
+  for (auto& e : ev) CUDA_OK(cudaEventCreate(&e));
+  std::vector<double> step_ms(prefix_max_, 0.0);
+  for (int rep = 0; rep < 2; ++rep) {   // the second pass is the warm one
+    CUDA_OK(cudaEventRecord(ev[0], stream_));
+    for (size_t k = 0; k < prefix_max_; ++k) {
+      KERNEL_OK(steps_[k].launch(stream_));
+      CUDA_OK(cudaEventRecord(ev[k + 1], stream_));
+    }
+    CUDA_OK(cudaStreamSynchronize(stream_));
+  }
+  for (size_t k = 0; k < prefix_max_; ++k) {
+    float ms = 0;
+    CUDA_OK(cudaEventElapsedTime(&ms, ev[k], ev[k + 1]));
+    step_ms[k] = ms;
+  }
+  auto upload_ms = [&](const void* src) {
+    double best = 1e30;
+    for (int rep = 0; rep < 2; ++rep) {
+      CUDA_OK(cudaEventRecord(ev[0], stream_));
+      Upload(src, stream_);
+      CUDA_OK(cudaEventRecord(ev[1], stream_));
+      const auto t0 = std::chrono::steady_clock::now();
+      CUDA_OK(cudaStreamSynchronize(stream_));
+      float ms = 0;
+      CUDA_OK(cudaEventElapsedTime(&ms, ev[0], ev[1]));
+      // a pageable source is staged by host threads while the stream waits: wall time counts
+      const double wall = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+      best = std::min(best, std::max((double)ms, wall));
+    }
+    return best;
+  };
+  const double t_pinned = upload_ms(in_host_);
+  std::vector<char> pageable(in_bytes_, 0);
+  const double t_pageable = upload_ms(pageable.data());
+  auto pick = [&](double t_upload) {
+    double sum = 0;
+    size_t n = 0;
+    while (n < prefix_max_ && 1.3 * sum < t_upload) sum += step_ms[n++];
+    return n;
+  };
+  prefix_steps_ = pick(t_pinned);
+  prefix_steps_pageable_ = std::max(prefix_steps_, pick(t_pageable));
+  if (dev_env("CVM_B200_VERBOSE"))
+    fprintf(stderr, "upload %.3f ms page-locked, %.3f ms pageable: %zu / %zu of %zu leading steps run per chunk\n", t_pinned,
+            t_pageable, prefix_steps_, prefix_steps_pageable_, prefix_max_);
+  for (auto& e : ev) cudaEventDestroy(e);
 }
 
 Executor::~Executor() {
   cudaSetDevice(device_);
   if (stream_) cudaStreamSynchronize(stream_);
   if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+  if (graph_exec_pageable_) cudaGraphExecDestroy(graph_exec_pageable_);
   if (kernels_exec_) cudaGraphExecDestroy(kernels_exec_);
   for (auto e : chunk_events_) cudaEventDestroy(e);
   if (copy_stream_) cudaStreamDestroy(copy_stream_);
@@ -1554,13 +1628,7 @@ void StagePool::WaitPiece(size_t k) {
 void Executor::Upload(const void* input, cudaStream_t s) { UploadRange(input, 0, in_bytes_, s); }
 
 void Executor::UploadRange(const void* input, size_t begin, size_t bytes, cudaStream_t s) {
-  cudaPointerAttributes at;
-  bool direct = false;
-  if (cudaPointerGetAttributes(&at, input) == cudaSuccess)
-    direct = at.type == cudaMemoryTypeHost || at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
-  else
-    cudaGetLastError();
-  if (direct) {
+  if (IsDirect(input)) {
     CUDA_OK(cudaMemcpyAsync((char*)in_dev_ + begin, (const char*)input + begin, bytes, cudaMemcpyDefault, s));
     return;
   }
@@ -1603,18 +1671,20 @@ void Executor::Enqueue(cudaStream_t s, size_t first) {
 void Executor::Run(const void* input, size_t input_bytes) {
   CHECK(input_bytes == in_bytes_) << "input size " << input_bytes << " vs. " << in_bytes_;
   CUDA_OK(cudaSetDevice(device_));
-  if (graph_exec_ && prefix_steps_ > 0) {
+  const bool pageable = graph_exec_pageable_ && !IsDirect(input);
+  const size_t prefix = pageable ? prefix_steps_pageable_ : prefix_steps_;
+  if (graph_exec_ && prefix > 0) {
     // chunk c of the batch is uploaded on the copy stream while the leading steps run on chunk c - 1
     for (size_t c = 0; c < steps_[0].chunk.size(); ++c) {
       UploadRange(input, c * chunk_bytes_, chunk_bytes_, copy_stream_);
       CUDA_OK(cudaEventRecord(chunk_events_[c], copy_stream_));
       CUDA_OK(cudaStreamWaitEvent(stream_, chunk_events_[c], 0));
-      for (size_t k = 0; k < prefix_steps_; ++k) {
+      for (size_t k = 0; k < prefix; ++k) {
         const int rc = steps_[k].chunk[c](stream_);
         CHECK(rc == CVMK_OK) << "step " << steps_[k].label << " (chunk) failed (" << rc << "): " << cvmk_last_error();
       }
     }
-    CUDA_OK(cudaGraphLaunch(graph_exec_, stream_));
+    CUDA_OK(cudaGraphLaunch(pageable ? graph_exec_pageable_ : graph_exec_, stream_));
   } else {
     Upload(input, stream_);
     if (graph_exec_) CUDA_OK(cudaGraphLaunch(graph_exec_, stream_));

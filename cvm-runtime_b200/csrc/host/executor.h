@@ -110,7 +110,17 @@ class Executor {
   int device_;
   cudaStream_t stream_ = nullptr;
   std::vector<Step> steps_;
-  size_t prefix_steps_ = 0;   // leading steps launched per batch chunk, outside the graph
+  // Leading steps launched per batch chunk, outside the graph, while later chunks upload: as many
+  // as take about as long as the upload, which differs for a page-locked caller buffer (read by the
+  // copy engine where it lies) and a pageable one (staged by host threads first).  Both lengths are
+  // chosen at load from step times and upload rates measured there; prefix_max_ bounds them (the
+  // memory planner keeps everything those steps touch live together).
+  size_t prefix_steps_ = 0;            // page-locked input
+  size_t prefix_steps_pageable_ = 0;   // pageable input
+  size_t prefix_max_ = 0;
+  cudaGraphExec_t graph_exec_pageable_ = nullptr;   // the steps from prefix_steps_pageable_ on
+  void ChoosePrefixes();
+  static bool IsDirect(const void* input);
   size_t chunk_bytes_ = 0;    // input bytes of one batch chunk
   std::vector<HeadOut> heads_;
   std::vector<void*> allocs_;
