@@ -59,6 +59,8 @@ struct StemConvParams {
   int in_rows;          // planar input rows per block (S * srows)
   int wbox, nwb;        // columns per TMA box and boxes per input row (a box is at most 256 wide)
   int box_stride;       // bytes from one box to the next in shared memory (a multiple of 128)
+  int lpad;             // columns of zero fill a box starts left of the image (0 or 16)
+  int fold_words;       // 1: rows are folded four staged pixels at a time on 32-bit words
   int planar_bytes, staged_bytes, w_bytes;
   int tmem_cols;
   int off_planar, off_staged, off_out, off_bias;  // byte offsets of the shared-memory regions after the weights
@@ -122,8 +124,9 @@ __device__ __forceinline__ uint4 fold_pixel(const StemConvParams& p, const uint8
       const int ix = X * S + b - p.pw;
       const bool inside = ix >= 0 && ix < p.W;
       const int ixc = inside ? ix : 0;
-      const int wb = p.nwb == 1 ? 0 : ixc / p.wbox;
-      const uint8_t* src = planar + (size_t)wb * p.box_stride + (size_t)row * p.wbox + (ixc - wb * p.wbox);
+      const int col = ixc + p.lpad;   // column inside the boxes
+      const int wb = p.nwb == 1 ? 0 : col / p.wbox;
+      const uint8_t* src = planar + (size_t)wb * p.box_stride + (size_t)row * p.wbox + (col - wb * p.wbox);
 #pragma unroll
       for (int c = 0; c < C; ++c) {
         int v = (int)(int8_t)src[(size_t)c * p.in_rows * p.wbox];
@@ -136,8 +139,60 @@ __device__ __forceinline__ uint4 fold_pixel(const StemConvParams& p, const uint8
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// The same on words, four staged pixels (X0 .. X0 + 3, X0 a multiple of 4) per call, for a single
+// box that carries zero columns left and right of the image (so that no column needs a test) and a
+// clamp to +-127 (only -128 moves).  Per sub-row and channel the 4 * S input bytes the pixels
+// take come out of two or three aligned words and a funnel shift; one byte permute moves each
+// byte into place.
+__device__ __forceinline__ uint32_t clamp127(uint32_t x) {
+  const uint32_t z = x ^ 0x80808080u;
+  const uint32_t m = ~(((z & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | z) & 0x80808080u;   // 0x80 in every byte that is -128
+  return x + (m >> 7);
+}
+template <int C, int S>
+__device__ __forceinline__ void fold_four(const StemConvParams& p, const uint8_t* planar, uint8_t* dst, int R, int X0) {
+  uint32_t o[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o[j][q] = 0u;
+  const int first = X0 * S - p.pw + p.lpad;          // first input column of the four pixels, inside the box
+  const uint32_t sh = (uint32_t)(first & 3) * 8u;
+#pragma unroll
+  for (int a = 0; a < S; ++a) {
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(planar + ((size_t)c * p.in_rows + (R * S + a)) * p.wbox + (first & ~3));
+      uint32_t s[S];   // the 4 * S bytes: pixel j, sub-column b at byte j * S + b
+      const uint32_t w0 = w[0], w1 = w[1];
+      s[0] = clamp127(__funnelshift_r(w0, w1, sh));
+      if (S == 2) s[S - 1] = clamp127(__funnelshift_r(w1, w[2], sh));
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int b = 0; b < S; ++b) {
+          const int from = j * S + b;                 // byte of s[]
+          const int to = (a * S + b) * C + c;         // byte of the staged pixel
+          const uint32_t sel = (0x3210u & ~(0xFu << (4 * (to & 3)))) | ((uint32_t)(4 + (from & 3)) << (4 * (to & 3)));
+          o[j][to >> 2] = __byte_perm(o[j][to >> 2], s[from >> 2], sel);
+        }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(dst + (size_t)(X0 + j) * PIX) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+}
+
 template <int C, int S>
 __device__ __forceinline__ void fold_block(const StemConvParams& p, const uint8_t* planar, uint8_t* staged, int t) {
+  if (p.fold_words) {
+    const int quads = p.xw >> 2;   // xw is a multiple of 4 on this path
+    for (int i = t; i < p.srows * quads; i += FOLDERS) {
+      const int R = i / quads, X0 = (i - R * quads) * 4;
+      fold_four<C, S>(p, planar, staged + (size_t)R * p.pitch, R, X0);
+    }
+    return;
+  }
   for (int R = 0; R < p.srows; ++R)
     for (int X = t; X < p.xw; X += FOLDERS)
       *reinterpret_cast<uint4*>(staged + (size_t)R * p.pitch + X * PIX) = fold_pixel<C, S>(p, planar, R, X);
@@ -185,7 +240,8 @@ __device__ __forceinline__ void stem_fast_row(const FastQ& fq, int mul, uint32_t
 // Development builds: cycles per role and phase, per CTA.  Slots: 0 folders wait for the planar
 // rows, 1 folders wait for a free staged buffer, 2 folding, 3 MMA waits for the accumulator, 4 MMA
 // waits for the staged rows, 5 MMA issue, 6 epilogue waits for the accumulator, 7 epilogue waits
-// for a panel, 8 epilogue compute, 10 whole folder loop, 11 tiles.
+// for a panel, 12 epilogue TMEM load + arithmetic + staging stores, 13 tcgen05 fence, 14 proxy fence,
+// 8 hand-over, 10 whole folder loop, 11 tiles.
 __device__ long long g_stem_timing[296 * 16];
 #define STSTART(var) long long var = clock64()
 #define STADD(slot, var) do { const long long now__ = clock64(); stacc[slot] += now__ - var; var = now__; } while (0)
@@ -254,10 +310,10 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     auto load_block = [&](int blk, int buf) {
       const int n = blk / p.blocks_per_image;
       const int oy0 = (blk - n * p.blocks_per_image) * p.rows_per_block;
-      mbar_expect_tx(&planar_full[buf], (uint32_t)(p.C * p.in_rows * p.W));
+      mbar_expect_tx(&planar_full[buf], (uint32_t)(p.C * p.in_rows * p.wbox * p.nwb));
       for (int wb = 0; wb < p.nwb; ++wb)
         tma_load_3d(planar + (size_t)buf * p.planar_bytes + (size_t)wb * p.box_stride, &tmap_x, &planar_full[buf],
-                    wb * p.wbox, oy0 * p.S - p.ph, n * p.C);
+                    wb * p.wbox - p.lpad, oy0 * p.S - p.ph, n * p.C);
     };
     if (issuer) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
@@ -387,6 +443,7 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
           if (p.fast_mode) {
             if (p.fast_variant & 1) stem_fast_row<1>(fq, p.f_mul, tbase, chunks, bias_s, panel, sw_key);
             else stem_fast_row<0>(fq, p.f_mul, tbase, chunks, bias_s, panel, sw_key);
+            STADD(12, tw);
           } else
           for (int ci = 0; ci < chunks; ++ci) {
             int32_t v[32];
@@ -410,7 +467,9 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             *reinterpret_cast<uint4*>(panel + (((j0 + 1) ^ sw_key) << 4)) = b;
           }
           tc_fence_before();
+          STADD(13, tw);
           fence_async_smem();
+          STADD(14, tw);
           __syncwarp();
           if (lane == 0) {
             mbar_arrive(&acc_empty[buf]);
@@ -422,7 +481,7 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       }
     }
 #ifdef CVMK_STEM_TIMING
-    if (leader) { STFLUSH(6); STFLUSH(7); STFLUSH(8); STFLUSH(9); }
+    if (leader) { STFLUSH(6); STFLUSH(7); STFLUSH(8); STFLUSH(9); STFLUSH(12); STFLUSH(13); STFLUSH(14); }
 #endif
   } else {
     // ------------------------------------------------------------------ output stores
@@ -473,7 +532,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 struct StemLayout {
-  int S, khp, kwp, nj, rows_per_block, segs, seg_w, srows, xw, pitch, in_rows, wbox, nwb, box_stride;
+  int S, khp, kwp, nj, rows_per_block, segs, seg_w, srows, xw, pitch, in_rows, wbox, nwb, box_stride, lpad, fold_words;
   int planar_bytes, staged_bytes, w_bytes, off_planar, off_staged, off_out, off_bias, smem_bytes;
 };
 
@@ -486,10 +545,24 @@ bool stem_layout(const cvmk_stem_conv_desc& d, StemLayout* L) {
   L->segs = (d.OW + BLOCK_M - 1) / BLOCK_M;
   L->seg_w = (d.OW + L->segs - 1) / L->segs;
   L->xw = L->segs * L->seg_w + 2 * L->nj;        // every tap of every real output pixel lies inside the row
-  L->pitch = L->xw * PIX;
   L->nwb = (d.W + 255) / 256;
   if (d.W % (16 * L->nwb) != 0) return false;
   L->wbox = d.W / L->nwb;
+  L->lpad = 0;
+  L->fold_words = 0;
+  // One box with 16 zero columns on either side of the image, when that fits a box and covers every
+  // column the staged pixels take (rounded up to whole words): the rows are then folded on words.
+  {
+    const int xw4 = (L->xw + 3) / 4 * 4;
+    const int last = (xw4 - 1) * S + (S - 1) - d.pad_w + 16;   // last column read, inside the box
+    if (d.W + 32 <= 256 && d.pad_w <= 16 && d.clamp == 127 && (last | 3) + 4 < d.W + 32 && !dev_env("CVM_B200_NO_FOLD_WORDS")) {
+      L->lpad = 16;
+      L->wbox = d.W + 32;
+      L->fold_words = 1;
+      L->xw = xw4;
+    }
+  }
+  L->pitch = L->xw * PIX;
   L->w_bytes = L->khp * L->nj * 2 * d.OC * PIX;
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -501,7 +574,7 @@ bool stem_layout(const cvmk_stem_conv_desc& d, StemLayout* L) {
     const int64_t blocks = (int64_t)d.N * ((d.OH + L->rows_per_block - 1) / L->rows_per_block);
     L->srows = L->rows_per_block + L->khp - 1;
     L->in_rows = L->srows * S;
-    L->box_stride = (d.C * L->in_rows * L->wbox + 127) / 128 * 128;
+    L->box_stride = (d.C * L->in_rows * L->wbox + 127) / 128 * 128;   // (one box, or nwb boxes of wbox = W / nwb columns)
     L->planar_bytes = L->nwb * L->box_stride;
     L->staged_bytes = (L->srows * L->pitch + 127) / 128 * 128;
     L->off_planar = (L->w_bytes + 1023) / 1024 * 1024;
@@ -635,6 +708,7 @@ extern "C" int cvmk_conv2d_stem_launch(const cvmk_stem_conv_plan* plan, cvmk_str
   p.num_blocks = d.N * p.blocks_per_image;
   p.segs = L.segs; p.seg_w = L.seg_w; p.srows = L.srows; p.xw = L.xw; p.pitch = L.pitch;
   p.in_rows = L.in_rows; p.wbox = L.wbox; p.nwb = L.nwb; p.box_stride = L.box_stride;
+  p.lpad = L.lpad; p.fold_words = L.fold_words;
   p.planar_bytes = L.planar_bytes; p.staged_bytes = L.staged_bytes; p.w_bytes = L.w_bytes;
   p.off_planar = L.off_planar; p.off_staged = L.off_staged; p.off_out = L.off_out; p.off_bias = L.off_bias;
   int cols = 2 * d.OC, pow2 = 32;
