@@ -128,6 +128,26 @@ void* Executor::dalloc_activation(size_t bytes, uint32_t root) {
 // then (most recently freed first: they are the likeliest to be still in L2) and new ones for the
 // rest; its chunks are free again after its last read.  Chunks need not be contiguous -- the
 // virtual range of a buffer is -- so nothing is lost to fragmentation.
+void Executor::PlanForPrefix(size_t prefix) {
+  if (!vmm_ || act_.empty()) return;
+  if (!phys_.empty()) {
+    for (auto& a : act_)
+      if (a.block >= 0) { vmm().unmap(reinterpret_cast<CUdeviceptr>(a.va), a.va_size); a.block = -1; }
+    for (auto& b : phys_) {
+      vmm().release((CUmemGenericAllocationHandle)b.handle);
+      device_bytes_ -= b.size;
+    }
+    phys_.clear();
+  }
+  const int p = prefix > 0 ? step_pos_[prefix - 1] : -2;
+  for (auto& a : act_) {
+    a.first = a.first0;
+    a.last = a.last0;
+    if (a.first <= p) { a.first = -1; a.last = std::max(a.last, p); }
+  }
+  MapActivations();
+}
+
 void Executor::MapActivations() {
   if (!vmm_ || act_.empty()) return;
   const CUmemAllocationProp prop = device_prop(device_);
@@ -1301,12 +1321,10 @@ struct Lowering {
     for (uint32_t nid = 0; nid < g.nodes.size(); ++nid)
       for (const auto& e : g.nodes[nid].inputs)
         if (Executor::ActBuf* a = of_entry[g.entry_id(e)]) a->last = std::max(a->last, group_pos(nid));
-    if (ex.prefix_max_ > 0) {
-      const int p = step_pos[ex.prefix_max_ - 1];
-      for (auto& a : act)
-        if (a.first <= p) { a.first = -1; a.last = std::max(a.last, p); }
-    }
-    ex.MapActivations();
+    for (auto& a : act) { a.first0 = a.first; a.last0 = a.last; }
+    ex.step_pos_ = step_pos;
+    // first with the longest prefix that may be chosen; the constructor plans again once it is known
+    ex.PlanForPrefix(ex.prefix_max_);
   }
 
   void lower_node(uint32_t nid) {
@@ -1407,7 +1425,10 @@ struct Lowering {
       const std::string tag = "[stem]";
       const bool first = !ex.steps_.empty() && ex.steps_[0].chunk.size() > 1 && ex.steps_[0].label.size() >= tag.size() &&
                          ex.steps_[0].label.compare(ex.steps_[0].label.size() - tag.size(), tag.size(), tag) == 0;
-      const size_t cap = 24;   // the lengths actually used are chosen after the load-time measurements
+      // The lengths actually used are chosen after the load-time measurements.  Everything the prefix
+      // touches is live for all of it (whole-batch buffers, filled chunk by chunk), so its length is
+      // also a memory decision: ten steps of ResNet-50 at batch 256 hold 1.3 GB, twenty 2.1 GB.
+      const size_t cap = 10;
       ex.prefix_max_ = 0;
       if (first)
         while (ex.prefix_max_ < ex.steps_.size() && ex.prefix_max_ < cap && ex.steps_[ex.prefix_max_].chunk.size() == ex.steps_[0].chunk.size())
@@ -1458,6 +1479,8 @@ Executor::Executor(const Graph& g, int device_id) : g_(g), device_(device_id) {
   CUDA_OK(cudaStreamSynchronize(stream_));
   if (use_graph_) {
     ChoosePrefixes();
+    CUDA_OK(cudaStreamSynchronize(stream_));
+    PlanForPrefix(std::max(prefix_steps_, prefix_steps_pageable_));   // memory for the prefix actually used
     if (prefix_steps_ > 0 || prefix_steps_pageable_ > 0) {
       CUDA_OK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
       chunk_events_.resize(steps_[0].chunk.size());

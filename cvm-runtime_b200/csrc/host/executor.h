@@ -155,11 +155,16 @@ class Executor {
     size_t bytes = 0, va_size = 0;
     uint32_t root = UINT32_MAX;   // node whose lowering made the allocation
     int first = 0, last = 0;      // schedule positions of the first write and the last read
+    int first0 = 0, last0 = 0;    // the same before the chunked prefix stretched them
     int block = -1;               // physical block backing it
   };
   struct PhysBlock { unsigned long long handle = 0; size_t size = 0; int free_at = 0; };
   void* dalloc_activation(size_t bytes, uint32_t root);
   void MapActivations();
+  // Lifetimes for a chunked prefix of `prefix` steps (everything those steps touch lives across
+  // all of them), then the physical backing; whatever was mapped before is released first.
+  void PlanForPrefix(size_t prefix);
+  std::vector<int> step_pos_;   // step -> schedule position
   std::vector<ActBuf> act_;
   std::vector<PhysBlock> phys_;
   bool vmm_ = false;

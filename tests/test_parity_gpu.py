@@ -365,3 +365,22 @@ def test_sharded_model_equals_single_handle(pkg, gpu_run, wl):
         assert np.array_equal(sm.infer(x), whole)
     finally:
         sm.free()
+
+
+def test_activation_memory_is_planned_by_lifetime(rt, wl, oracle):
+    """Buffers that are never live together share physical memory (the result is checked against
+    the oracle like every other case, here once more on the handle whose memory is inspected), and
+    what the handle reports is what it holds."""
+    js, pb, x = wl.mobilenet_v1(batch=16, size=160)
+    net = rt.CVMAPILoadModel(js, pb, 0)
+    try:
+        buffers, physical = rt.activation_bytes(net)
+        assert buffers > 0, "the planner did not run"
+        assert 0 < physical < buffers
+        assert physical % (2 << 20) == 0            # whole 2 MiB chunks
+        assert rt.device_bytes(net) >= physical
+        got = rt.inference_bytes(net, x)
+        assert np.array_equal(got, oracle.run_model(js, pb, x))
+        assert np.array_equal(got, rt.inference_bytes(net, x)), "second run on the shared memory differs"
+    finally:
+        rt.CVMAPIFreeModel(net)
