@@ -912,6 +912,7 @@ struct Lowering {
     if (axis < 0) axis += nd;
     const auto ys = phys_strides(y.shape, y.nhwc);
     int64_t offset = 0;
+    std::vector<cvmk_strided_desc> all;
     for (size_t m = 0; m < n.inputs.size(); ++m) {
       const DevBuf x = materialize(g.entry_id(n.inputs[m]));
       const auto order = phys_order(x.shape, y.nhwc);
@@ -928,8 +929,10 @@ struct Lowering {
       d.a = x.ptr; d.a_dtype = x.dtype; d.y = y.ptr; d.y_dtype = y.dtype;
       d.y_off = offset * ys[axis];
       offset += x.shape[axis];
-      add_step("concatenate:" + n.name(), [d](cudaStream_t s) { return cvmk_strided(&d, s); });
+      all.push_back(d);
     }
+    // all inputs in one launch when they move whole vectors, else one launch each
+    add_step("concatenate:" + n.name(), [all](cudaStream_t s) { return cvmk_strided_batch(all.data(), (int32_t)all.size(), s); });
   }
 
   // flatten / reshape / squeeze / expand_dims: the row-major element order is preserved.

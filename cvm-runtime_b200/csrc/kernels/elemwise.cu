@@ -82,10 +82,28 @@ __global__ void __launch_bounds__(256) elemwise_kernel(const void* __restrict__ 
   }
 }
 
+// Division of a non-negative 31-bit number by a divisor fixed at launch: q = umulhi(n, mul) >> shr
+// (mul = ceil(2^(31 + ceil(log2 d)) / d)); d = 1 is flagged by mul = 0.  The index split of the
+// strided kernels is one such division per dimension and element; the 64-bit hardware-emulated
+// divisions it replaces cost more than the copy itself.
+struct IdxDiv { uint32_t mul, shr; };
+__device__ __forceinline__ uint32_t idx_div(uint32_t n, const IdxDiv& d) { return d.mul ? __umulhi(n, d.mul) >> d.shr : n; }
+static IdxDiv make_idx_div(int64_t d) {
+  IdxDiv f = {0, 0};
+  if (d <= 1) return f;
+  int lg = 0;
+  while ((1LL << lg) < d) ++lg;
+  f.mul = (uint32_t)((((uint64_t)1 << (31 + lg)) + (uint64_t)d - 1) / (uint64_t)d);
+  f.shr = (uint32_t)(lg - 1);
+  return f;
+}
+
 struct StridedParams {
   int op, ndim;
   int64_t total;
   int64_t extent[6];
+  IdxDiv fd[6];
+  int idx32;          // total < 2^31: the index is split with 32-bit multiply-shifts
   int64_t as[6], bs[6], ys[6];
   const void* a; const void* b; void* y;
   int ad, bd, yd;
@@ -101,15 +119,31 @@ __device__ __forceinline__ int32_t load_elem(const void* p, int dt, int64_t off)
 __global__ void __launch_bounds__(256) strided_kernel(const __grid_constant__ StridedParams p) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
-    int64_t rem = i, ao = p.a_off, bo = p.b_off, yo = p.y_off;
+    int64_t ao = p.a_off, bo = p.b_off, yo = p.y_off;
+    if (p.idx32) {
+      uint32_t rem = (uint32_t)i;
 #pragma unroll
-    for (int k = 5; k >= 0; --k) {
-      if (k < p.ndim) {
-        const int64_t c = rem % p.extent[k];
-        rem /= p.extent[k];
-        ao += c * p.as[k];
-        bo += c * p.bs[k];
-        yo += c * p.ys[k];
+      for (int k = 5; k >= 0; --k) {
+        if (k < p.ndim) {
+          const uint32_t q = idx_div(rem, p.fd[k]);
+          const int64_t c = (int64_t)(rem - q * (uint32_t)p.extent[k]);
+          rem = q;
+          ao += c * p.as[k];
+          bo += c * p.bs[k];
+          yo += c * p.ys[k];
+        }
+      }
+    } else {
+      int64_t rem = i;
+#pragma unroll
+      for (int k = 5; k >= 0; --k) {
+        if (k < p.ndim) {
+          const int64_t c = rem % p.extent[k];
+          rem /= p.extent[k];
+          ao += c * p.as[k];
+          bo += c * p.bs[k];
+          yo += c * p.ys[k];
+        }
       }
     }
     int32_t v[1];
@@ -137,26 +171,51 @@ __global__ void __launch_bounds__(256) strided_kernel(const __grid_constant__ St
 // aligned: move 16-byte vectors.
 struct StridedVecParams {
   int ndim;
+  int idx32;
   int64_t total_vec;
   int64_t extent[6];   // innermost extent counted in vectors
+  IdxDiv fd[6];
   int64_t as[6], ys[6];  // strides in vectors (innermost = 1)
   const int4* a; int4* y;
 };
-__global__ void __launch_bounds__(256) strided_vec_kernel(const __grid_constant__ StridedVecParams p) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total_vec; i += stride) {
-    int64_t rem = i, ao = 0, yo = 0;
+__device__ __forceinline__ void strided_vec_body(const StridedVecParams& p, int64_t first, int64_t stride) {
+  for (int64_t i = first; i < p.total_vec; i += stride) {
+    int64_t ao = 0, yo = 0;
+    if (p.idx32) {
+      uint32_t rem = (uint32_t)i;
 #pragma unroll
-    for (int k = 5; k >= 0; --k) {
-      if (k < p.ndim) {
-        const int64_t c = rem % p.extent[k];
-        rem /= p.extent[k];
-        ao += c * p.as[k];
-        yo += c * p.ys[k];
+      for (int k = 5; k >= 0; --k) {
+        if (k < p.ndim) {
+          const uint32_t q = idx_div(rem, p.fd[k]);
+          const int64_t c = (int64_t)(rem - q * (uint32_t)p.extent[k]);
+          rem = q;
+          ao += c * p.as[k];
+          yo += c * p.ys[k];
+        }
+      }
+    } else {
+      int64_t rem = i;
+#pragma unroll
+      for (int k = 5; k >= 0; --k) {
+        if (k < p.ndim) {
+          const int64_t c = rem % p.extent[k];
+          rem /= p.extent[k];
+          ao += c * p.as[k];
+          yo += c * p.ys[k];
+        }
       }
     }
     p.y[yo] = __ldg(p.a + ao);
   }
+}
+__global__ void __launch_bounds__(256) strided_vec_kernel(const __grid_constant__ StridedVecParams p) {
+  strided_vec_body(p, (int64_t)blockIdx.x * blockDim.x + threadIdx.x, (int64_t)gridDim.x * blockDim.x);
+}
+// Several vector copies in one launch (the inputs of a concatenate): blockIdx.y picks the copy.
+constexpr int STRIDED_BATCH_MAX = 8;
+struct StridedVecBatch { StridedVecParams item[STRIDED_BATCH_MAX]; };
+__global__ void __launch_bounds__(256) strided_vec_batch_kernel(const __grid_constant__ StridedVecBatch b) {
+  strided_vec_body(b.item[blockIdx.y], (int64_t)blockIdx.x * blockDim.x + threadIdx.x, (int64_t)gridDim.x * blockDim.x);
 }
 
 struct ReduceParams {
@@ -395,18 +454,9 @@ extern "C" int cvmk_elemwise(const void* x, int x_dtype, void* y, int y_dtype, i
   return check_cuda(cudaGetLastError(), "elemwise_kernel launch");
 }
 
-extern "C" int cvmk_strided(const cvmk_strided_desc* d, cvmk_stream_t stream) {
-  if (!d || !d->a || !d->y || d->ndim < 1 || d->ndim > 6 || (d->op != CVMK_OP_COPY && !d->b)) {
-    set_error("strided: bad argument");
-    return CVMK_ERR_ARG;
-  }
-  int64_t total = 1;
-  for (int k = 0; k < d->ndim; ++k) {
-    if (d->extent[k] < 1) { set_error("strided: empty extent"); return CVMK_ERR_ARG; }
-    total *= d->extent[k];
-  }
-  cudaStream_t s = (cudaStream_t)stream;
-  const int threads = 256;
+// Fills `p` when `d` is a plain copy whose innermost run is contiguous and 16-byte aligned on both
+// sides (the vector kernels); false otherwise.
+static bool strided_as_vectors(const cvmk_strided_desc* d, int64_t total, StridedVecParams* p) {
   const int in = d->ndim - 1;
   const int es = d->a_dtype;
   const int vec = 16 / es;
@@ -414,26 +464,89 @@ extern "C" int cvmk_strided(const cvmk_strided_desc* d, cvmk_stream_t stream) {
               d->a_stride[in] == 1 && d->y_stride[in] == 1 && d->extent[in] % vec == 0 &&
               d->a_off % vec == 0 && d->y_off % vec == 0 && aligned16(d->a) && aligned16(d->y);
   for (int k = 0; fast && k < in; ++k) fast = d->a_stride[k] % vec == 0 && d->y_stride[k] % vec == 0;
-  if (fast) {
-    StridedVecParams p;
-    memset(&p, 0, sizeof(p));
-    p.ndim = d->ndim;
-    p.total_vec = total / vec;
-    for (int k = 0; k < d->ndim; ++k) {
-      p.extent[k] = k == in ? d->extent[k] / vec : d->extent[k];
-      p.as[k] = k == in ? 1 : d->a_stride[k] / vec;
-      p.ys[k] = k == in ? 1 : d->y_stride[k] / vec;
+  if (!fast) return false;
+  memset(p, 0, sizeof(*p));
+  p->ndim = d->ndim;
+  p->total_vec = total / vec;
+  p->idx32 = p->total_vec < ((int64_t)1 << 31);
+  for (int k = 0; k < d->ndim; ++k) {
+    p->extent[k] = k == in ? d->extent[k] / vec : d->extent[k];
+    p->fd[k] = make_idx_div(p->extent[k]);
+    p->as[k] = k == in ? 1 : d->a_stride[k] / vec;
+    p->ys[k] = k == in ? 1 : d->y_stride[k] / vec;
+  }
+  p->a = reinterpret_cast<const int4*>(reinterpret_cast<const char*>(d->a) + d->a_off * es);
+  p->y = reinterpret_cast<int4*>(reinterpret_cast<char*>(d->y) + d->y_off * es);
+  return true;
+}
+
+static bool strided_total(const cvmk_strided_desc* d, int64_t* total) {
+  if (!d || !d->a || !d->y || d->ndim < 1 || d->ndim > 6 || (d->op != CVMK_OP_COPY && !d->b)) {
+    set_error("strided: bad argument");
+    return false;
+  }
+  *total = 1;
+  for (int k = 0; k < d->ndim; ++k) {
+    if (d->extent[k] < 1) { set_error("strided: empty extent"); return false; }
+    *total *= d->extent[k];
+  }
+  return true;
+}
+
+// `n` copies: one launch when all of them are vector copies (groups of STRIDED_BATCH_MAX), else one
+// cvmk_strided() each.
+extern "C" int cvmk_strided_batch(const cvmk_strided_desc* d, int32_t n, cvmk_stream_t stream) {
+  if (!d || n < 1) { set_error("strided_batch: bad argument"); return CVMK_ERR_ARG; }
+  cudaStream_t s = (cudaStream_t)stream;
+  StridedVecBatch b;
+  bool all = true;
+  for (int32_t first = 0; first < n && all; first += STRIDED_BATCH_MAX) {
+    const int m = std::min<int32_t>(STRIDED_BATCH_MAX, n - first);
+    int64_t largest = 0;
+    for (int i = 0; i < m && all; ++i) {
+      int64_t total;
+      if (!strided_total(&d[first + i], &total)) return CVMK_ERR_ARG;
+      all = strided_as_vectors(&d[first + i], total, &b.item[i]);
+      largest = std::max(largest, b.item[i].total_vec);
     }
-    p.a = reinterpret_cast<const int4*>(reinterpret_cast<const char*>(d->a) + d->a_off * es);
-    p.y = reinterpret_cast<int4*>(reinterpret_cast<char*>(d->y) + d->y_off * es);
-    strided_vec_kernel<<<grid_for(p.total_vec, threads), threads, 0, s>>>(p);
-    return check_cuda(cudaGetLastError(), "strided_vec_kernel launch");
+    if (!all) {
+      if (first == 0) break;   // nothing launched yet: fall through to the one-by-one form
+      for (int32_t i = first; i < n; ++i) {
+        const int rc = cvmk_strided(&d[i], stream);
+        if (rc != CVMK_OK) return rc;
+      }
+      return CVMK_OK;
+    }
+    strided_vec_batch_kernel<<<dim3((unsigned)grid_for(largest, 256), (unsigned)m), 256, 0, s>>>(b);
+    if (check_cuda(cudaGetLastError(), "strided_vec_batch_kernel launch")) return CVMK_ERR_CUDA;
+  }
+  if (all) return CVMK_OK;
+  for (int32_t i = 0; i < n; ++i) {
+    const int rc = cvmk_strided(&d[i], stream);
+    if (rc != CVMK_OK) return rc;
+  }
+  return CVMK_OK;
+}
+
+extern "C" int cvmk_strided(const cvmk_strided_desc* d, cvmk_stream_t stream) {
+  int64_t total = 1;
+  if (!strided_total(d, &total)) return CVMK_ERR_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = 256;
+  {
+    StridedVecParams p;
+    if (strided_as_vectors(d, total, &p)) {
+      strided_vec_kernel<<<grid_for(p.total_vec, threads), threads, 0, s>>>(p);
+      return check_cuda(cudaGetLastError(), "strided_vec_kernel launch");
+    }
   }
   StridedParams p;
   memset(&p, 0, sizeof(p));
   p.op = d->op; p.ndim = d->ndim; p.total = total;
+  p.idx32 = total < ((int64_t)1 << 31);
   for (int k = 0; k < d->ndim; ++k) {
     p.extent[k] = d->extent[k];
+    p.fd[k] = make_idx_div(d->extent[k]);
     p.as[k] = d->a_stride[k]; p.bs[k] = d->b_stride[k]; p.ys[k] = d->y_stride[k];
   }
   p.a = d->a; p.b = d->b; p.y = d->y;

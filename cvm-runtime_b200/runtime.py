@@ -26,7 +26,7 @@ KERNEL_SYMBOLS = [
     "cvmk_conv2d_stem_supported", "cvmk_conv2d_stem_weight_bytes", "cvmk_conv2d_stem_pack_weights",
     "cvmk_conv2d_stem_prepare", "cvmk_conv2d_stem_launch",
     "cvmk_conv2d_tc_supported", "cvmk_conv2d_tc_workspace_bytes", "cvmk_conv2d_tc_prepare", "cvmk_conv2d_tc_launch", "cvmk_elemwise",
-    "cvmk_transpose_batched", "cvmk_strided", "cvmk_take", "cvmk_where", "cvmk_reduce", "cvmk_max_pool2d", "cvmk_conv2d_direct", "cvmk_get_valid_counts", "cvmk_get_valid_counts_clamped",
+    "cvmk_transpose_batched", "cvmk_strided", "cvmk_strided_batch", "cvmk_take", "cvmk_where", "cvmk_reduce", "cvmk_max_pool2d", "cvmk_conv2d_direct", "cvmk_get_valid_counts", "cvmk_get_valid_counts_clamped",
     "cvmk_nms_scratch_bytes", "cvmk_non_max_suppression", "cvmk_non_max_suppression_static",
     "cvmk_last_error",
 ]

@@ -188,6 +188,9 @@ typedef struct {
   cvmk_epilogue ep;
 } cvmk_strided_desc;
 CVMK_API int cvmk_strided(const cvmk_strided_desc* d, cvmk_stream_t stream);
+/* n strided copies at once (the inputs of a concatenate): one launch when every one of them moves
+ * whole 16-byte vectors, otherwise one cvmk_strided() each. */
+CVMK_API int cvmk_strided_batch(const cvmk_strided_desc* d, int32_t n, cvmk_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * sum / max reduce (cpu/ops/reduce.cc:34-140).  Output point c (up to 6 kept extents, strides into
