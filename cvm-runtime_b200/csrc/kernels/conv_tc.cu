@@ -81,6 +81,7 @@ struct ConvParams {
   int a_mode;           // activations: 0 plain 2-D tiles (1x1, dense), 1 im2col-mode TMA, 2 spatial patches,
                         // 3 spatial patches whose input halo is staged once per channel block,
                         // 4 the same with the whole weight matrix resident in shared memory
+  int b_resident;       // a_mode 0 with this CTA's N tile of the weights resident in shared memory
   int patch_w, patch_h, patch_n;  // a_mode 2, 3: an M tile is patch_w x patch_h output pixels of patch_n images
   int tiles_w, tiles_h;           // a_mode 2, 3: patches per image row / column
   int patch_w_log2, patch_h_log2; // patch sides are powers of two
@@ -288,7 +289,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (threadIdx.x == 0) TRACE(16, 0);
   const int a_bytes = BLOCK_M * p.block_k;
   const int b_bytes = p.block_n * p.block_k;
-  const int unit_bytes = a_bytes + b_bytes;          // one A tile and the B tile that goes with it
+  // b_resident: a 1x1 layer whose N tiles divide the grid, so that every tile of a CTA has the same
+  // first output channel: the K blocks of that N tile are loaded once and stay in front of the
+  // ring, which then carries activations only.
+  const bool b_resident = p.b_resident != 0;
+  const int unit_bytes = a_bytes + (b_resident ? 0 : b_bytes);   // one A tile and the B tile that goes with it
   const int num_units = p.num_units;
   // Halo mode (a_mode 3): a ring stage is one channel block: the (patch_w + kw - 1) x
   // (patch_h + kh - 1) input pixels the patch touches, loaded once, then the kh * kw weight tiles.
@@ -304,7 +309,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int halo_bytes = halo_w * (p.patch_h + p.kh - 1) * p.block_k;
   const int halo_pad = (halo_bytes + 1023) & ~1023;
   const int taps = p.kh * p.kw;
-  const int resident_bytes = w_resident ? p.num_kb * taps * b_bytes : 0;   // [channel block][tap][block_n x block_k]
+  const int resident_bytes = w_resident ? p.num_kb * taps * b_bytes             // [channel block][tap][block_n x block_k]
+                                        : (b_resident ? p.num_units * b_bytes : 0);   // [K block][block_n x block_k]
   uint8_t* const ring = smem + resident_bytes;
   const int stage_bytes = w_resident ? halo_pad : (halo ? halo_pad + taps * b_bytes : p.units * unit_bytes);
   const int num_kb = p.num_kb;  // ring stages consumed per tile
@@ -410,6 +416,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
       const TileOrigin to_first = tile_origin(p, (int)blockIdx.x);
+      if (b_resident && which == 0) {   // this CTA's N tile of the weights, once
+        const uint32_t wb = smem_u32(&bar_weights);
+        if (leader) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wb), "r"((uint32_t)resident_bytes) : "memory");
+        uint32_t dst = smem_u32(smem);
+        for (int u = 0; u < p.num_units; ++u, dst += (uint32_t)b_bytes)
+          if (leader) asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+              " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(wb),
+              "r"(u * p.block_k), "r"(to_first.n0)
+              : "memory");
+      }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       if (which == 0 && leader) TRACE(16, 1);
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
@@ -504,7 +521,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(bar),
                   "r"(cc + to.k0), "r"(m0)
                   : "memory");
-            asm volatile(
+            if (!b_resident) asm volatile(
                 "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                 " [%0], [%1, {%3, %4}], [%2];" ::"r"(sa + (uint32_t)a_bytes), "l"(reinterpret_cast<uint64_t>(&tmap_b)),
                 "r"(bar), "r"(kcol + to.k0), "r"(to.nb)
@@ -557,7 +574,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       TDECL;
       TSTART(tl);
       asm volatile("griddepcontrol.wait;" ::: "memory");
-      if (w_resident && blockIdx.x < num_tiles && !mbar_wait(&bar_weights, 0u, &abort_flag, 7)) live = false;
+      if ((w_resident || b_resident) && blockIdx.x < num_tiles && !mbar_wait(&bar_weights, 0u, &abort_flag, 7)) live = false;
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
         TSTART(tw);
         if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1, &abort_flag, 2)) { live = false; break; }
@@ -598,13 +615,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           const int in_stage = min(p.units, num_units - unit);
           uint32_t al = st;
+          // B next to A in the stage, or K block `unit` of the resident weights
+          uint32_t bl = b_resident ? w_lo0 + (uint32_t)unit * b_q : st + a_q;
+          const uint32_t b_step = b_resident ? b_q : unit_q;
           if (leader) {
             if (nk == 4) {
-              for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<4>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+              for (int u = 0; u < in_stage; ++u, al += unit_q, bl += b_step) mma_i8_k<4>(d_tmem, al, a_hi, bl, a_hi, idesc, (uint32_t)(unit + u));
             } else if (nk == 2) {
-              for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<2>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+              for (int u = 0; u < in_stage; ++u, al += unit_q, bl += b_step) mma_i8_k<2>(d_tmem, al, a_hi, bl, a_hi, idesc, (uint32_t)(unit + u));
             } else {
-              for (int u = 0; u < in_stage; ++u, al += unit_q) mma_i8_k<1>(d_tmem, al, a_hi, al + a_q, a_hi, idesc, (uint32_t)(unit + u));
+              for (int u = 0; u < in_stage; ++u, al += unit_q, bl += b_step) mma_i8_k<1>(d_tmem, al, a_hi, bl, a_hi, idesc, (uint32_t)(unit + u));
             }
             mma_commit(&bar_empty[stage]);
             TRACE(5, mseq);
@@ -1111,17 +1131,35 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
     else if (bk == 128 && k_all <= 512 && ring_depth(64) >= 3) { plan->io_bufs = 2; bk = 64; }
   }
   plan->block_k = bk;
+  // 1x1 layers: when the number of N tiles divides the grid, tile t + k * grid has the N tile of
+  // tile t, so a CTA multiplies one block of output channels all along and can keep its weights
+  // (K x block_n bytes) in shared memory; the ring then carries activations only, a third or a
+  // fifth of the bytes.  Taken when the weights leave room for a ring of at least four A blocks.
+  plan->b_resident = 0;
+  if (plan->a_im2col == 0 && plan->k_slices == 1 && !dev_env("CVM_B200_NO_RESIDENT_B")) {
+    int sms = 148, dev0 = 0;
+    if (cudaGetDevice(&dev0) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev0);
+    const int64_t m_tiles = ((int64_t)d->N * d->OH * d->OW + BLOCK_M - 1) / BLOCK_M;
+    const int nt = (d->OC + bn - 1) / bn;
+    const int64_t w_bytes = (int64_t)d->C * bn;
+    const int io1 = plan->tma_out ? 2 * plan->io_bufs * group_bytes : 0;
+    if (m_tiles * nt >= 2LL * sms && sms % nt == 0 && d->OC % bn == 0 &&
+        budget - io1 - w_bytes >= 4LL * BLOCK_M * bk) {
+      plan->b_resident = 1;
+      resident = (int)w_bytes;
+    }
+  }
   const int io_bytes = plan->tma_out ? 2 * plan->io_bufs * group_bytes : 0;
   // Every hand-over of a ring stage (TMA completion -> MMA thread -> commit -> producer) costs a
   // fixed latency of several hundred cycles whatever the stage holds, so small (tap, channel block)
   // units are grouped: up to four per stage, about 48 KB, while the ring stays three deep.
-  const int unit_bytes = (BLOCK_M + bn) * bk;
+  const int unit_bytes = (BLOCK_M + (plan->b_resident ? 0 : bn)) * bk;
   const int num_units = (int)(k_all / bk);
   int units = 48 * 1024 / unit_bytes;
   if (units > 4) units = 4;
   if (units > num_units) units = num_units;
   if (const char* e = dev_env("CVM_B200_UNITS")) units = atoi(e);
-  while (units > 1 && (budget - io_bytes) / (units * unit_bytes) < 3) --units;
+  while (units > 1 && (budget - io_bytes - resident) / (units * unit_bytes) < 3) --units;
   if (units < 1) units = 1;
   if (halo) units = d->KH * d->KW;
   plan->reserved[3] = units;
@@ -1204,6 +1242,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.dil_h = d.dil_h; p.dil_w = d.dil_w;
   p.block_k = plan->block_k; p.block_n = plan->block_n;
   p.stages = plan->stages; p.a_mode = plan->a_im2col;
+  p.b_resident = plan->b_resident;
   p.units = plan->reserved[3] > 0 ? plan->reserved[3] : 1;
   p.num_m_tiles = (p.m_total + BLOCK_M - 1) / BLOCK_M;
   if (p.a_mode >= 2) {

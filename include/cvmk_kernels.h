@@ -150,7 +150,8 @@ typedef struct __attribute__((aligned(64))) {
   int32_t ring_bytes; /* bytes of the operand ring in shared memory */
   int32_t reserved[4];  /* [0..2] patch width / height / images (a_im2col = 2, 3), [3] (tap, channel block) units per ring stage */
   int32_t k_slices;   /* > 1: the reduction is cut into this many slices (see cvmk_conv_desc.workspace) */
-  int32_t pad_[3];
+  int32_t b_resident; /* 1: 1x1 layer, every CTA keeps its N tile of the weights in shared memory */
+  int32_t pad_[2];
 } cvmk_conv_plan;
 
 CVMK_API int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d);
