@@ -783,6 +783,22 @@ struct Lowering {
       d.acc_bound = probe.acc_bound;
       d.ep = ch.ep;
       add_step(label + (depthwise ? "[dw]" : "[direct]"), [d](cudaStream_t s) { return cvmk_conv2d_direct(&d, s); });
+      // Quarter-batch forms (batch-major operands: a chunk is a contiguous slice), when no step of
+      // the chain indexes another tensor.
+      const int chunks = batch_chunks(d.N);
+      bool sliceable = chunks > 1 && xin.nhwc && out.nhwc;
+      for (int i = 0; i < d.ep.n; ++i)
+        sliceable &= !(d.ep.s[i].op == CVMK_EP_ADD_T || d.ep.s[i].op == CVMK_EP_SUB_T || d.ep.s[i].op == CVMK_EP_RSUB_T);
+      if (sliceable) {
+        const int per = d.N / chunks;
+        for (int c = 0; c < chunks; ++c) {
+          cvmk_conv_direct_desc cd = d;
+          cd.N = per;
+          cd.x = (const char*)d.x + (size_t)c * per * d.H * d.W * d.C * d.x_dtype;
+          cd.y = (char*)d.y + (size_t)c * per * d.OH * d.OW * d.OC * d.y_dtype;
+          ex.steps_.back().chunk.push_back([cd](cudaStream_t s) { return cvmk_conv2d_direct(&cd, s); });
+        }
+      }
     }
   }
 
