@@ -314,6 +314,7 @@ struct PoolParams {
   int N, H, W, C, OH, OW, KH, KW, sh, sw, ph, pw;
   int64_t total;  // output vectors
   int cvec;       // vectors per pixel
+  IdxDiv d_cvec, d_ow, d_oh;   // multiply-shift forms of the three divisions of the index split
 };
 // IDX32: the output has fewer than 2^31 vectors, so the index split runs on 32-bit divisions (the
 // 64-bit ones cost more instructions than the nine taps of a 3x3 window).
@@ -324,11 +325,11 @@ __global__ void __launch_bounds__(256) pool_vec_kernel(const __grid_constant__ P
     int cv, ox, oy, n;
     if (IDX32) {
       const uint32_t u = (uint32_t)i;
-      uint32_t pix = u / (uint32_t)p.cvec;
+      const uint32_t pix = idx_div(u, p.d_cvec);
       cv = (int)(u - pix * (uint32_t)p.cvec);
-      const uint32_t r1 = pix / (uint32_t)p.OW;
+      const uint32_t r1 = idx_div(pix, p.d_ow);
       ox = (int)(pix - r1 * (uint32_t)p.OW);
-      const uint32_t r2 = r1 / (uint32_t)p.OH;
+      const uint32_t r2 = idx_div(r1, p.d_oh);
       oy = (int)(r1 - r2 * (uint32_t)p.OH);
       n = (int)r2;
     } else {
@@ -359,15 +360,15 @@ __global__ void __launch_bounds__(256) pool_vec_kernel(const __grid_constant__ P
           if (!ok) v = make_int4(0x80808080, 0x80808080, 0x80808080, 0x80808080);
           const uint32_t w[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            me[q] = __vmaxs2(me[q], (w[q] << 8) & 0xFF00FF00u);
-            mo[q] = __vmaxs2(mo[q], w[q] & 0xFF00FF00u);
+          for (int q = 0; q < 4; ++q) {   // one byte permute each: (0, b0, 0, b2) and (0, b1, 0, b3)
+            me[q] = __vmaxs2(me[q], __byte_perm(w[q], 0u, 0x2404));
+            mo[q] = __vmaxs2(mo[q], __byte_perm(w[q], 0u, 0x3414));
           }
         }
       }
       uint32_t r[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) r[q] = ((me[q] >> 8) & 0x00FF00FFu) | (mo[q] & 0xFF00FF00u);
+      for (int q = 0; q < 4; ++q) r[q] = __byte_perm(me[q], mo[q], 0x7351);   // (me.b1, mo.b1, me.b3, mo.b3)
       m = make_int4((int)r[0], (int)r[1], (int)r[2], (int)r[3]);
     } else {
       m = make_int4(INT32_MIN, INT32_MIN, INT32_MIN, INT32_MIN);
@@ -622,6 +623,7 @@ extern "C" int cvmk_max_pool2d(const cvmk_pool_desc* d, cvmk_stream_t stream) {
   if (d->C % vec == 0 && aligned16(d->x) && aligned16(d->y)) {
     p.cvec = d->C / vec;
     p.total = (int64_t)d->N * d->OH * d->OW * p.cvec;
+    p.d_cvec = make_idx_div(p.cvec); p.d_ow = make_idx_div(d->OW); p.d_oh = make_idx_div(d->OH);
     const bool idx32 = p.total < ((int64_t)1 << 31);
     if (d->dtype == CVMK_I8) {
       if (idx32) pool_vec_kernel<CVMK_I8, true><<<grid_for(p.total, threads), threads, 0, s>>>(p);
