@@ -622,6 +622,18 @@ def run_ours(args):
                             1e3 * tc_ms / max(1, kernels["tc"]["launches_per_step"])),
                 "kernels": kernels,
             }
+            # The kernel runs layers of very different shape: some cannot be faster than their
+            # compulsory bytes over the HBM copy rate, others than their ops over the MMA rate.  The
+            # sum over layers of the larger of the two is the floor of this kernel on this network
+            # (bytes: input + output + weights + bias of a layer at one byte per activation; the
+            # int8 operand of a fused residual add is not counted, so the floor is on the low side).
+            floor_ms = 0.0
+            for x in layer_rates(head, want_kind=("tc",)):
+                rec = node_table(head["graph_json"])[x["name"]]
+                floor_ms += 1e3 * max(rec["ops"] / (peak_i8 * 1e12), rec["bytes"] / (peaks["hbm_gbs"] * 1e9))
+            roofline["layer_floor"] = {"ms_per_step": floor_ms, "frac": floor_ms / tc_ms if tc_ms else None,
+                                       "note": "sum over the kernel's launches of max(ops / measured int8 MMA rate, compulsory "
+                                               "bytes / measured HBM copy rate); frac = that floor / the launches' summed time"}
         elif "non_max_suppression" in kernels:
             nbytes = 2.0 * args.batch * wl.SSD_ANCHORS * 6 * 4
             ms = kernels["non_max_suppression"]["ms_per_step"]
