@@ -357,25 +357,33 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.w + begin), "r"(n) : "memory");
     }
   }
+  // The two producer warps need nothing of the set-up below but the barriers, which thread 0 (of
+  // producer warp 0) has just initialised: they meet at a barrier of their own and go on to their
+  // loads, whose latency then runs while the other ten warps allocate TMEM and stage the bias.
+  const bool is_producer = warp == 0 || warp == PRODUCER2_WARP;
+  if (is_producer) asm volatile("bar.sync 2, 64;" ::: "memory");
   auto stage_bias = [&]() {
     const int padded = min(MAX_BIAS, (p.oc + 31) & ~31);
-    for (int i = threadIdx.x; i < padded; i += NUM_THREADS) {
+    for (int i = (int)threadIdx.x - 32; i < padded; i += NUM_THREADS - 64) {   // warps 1..10
       const int32_t b = i < p.oc && p.bias ? __ldg(p.bias + i) : 0;
       // fast path: (bias + rounding addend) pre-multiplied by 2^(16 - shift), see fast_row()
       bias_s[i] = (p.fast_mode && !p.fast_wide) ? (int32_t)((uint32_t)(b + p.f_add) * (uint32_t)p.f_mul) : b;
     }
   };
-  if (bias_in_smem && p.bias_static) stage_bias();
-  if (bias_in_smem && !p.bias_static) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    stage_bias();
+  uint32_t tmem_base = 0;
+  if (!is_producer) {
+    if (bias_in_smem && p.bias_static) stage_bias();
+    if (bias_in_smem && !p.bias_static) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      stage_bias();
+    }
+    // Every role below finishes its own set-up arithmetic first and executes griddepcontrol.wait just
+    // before its loop, so that the set-up overlaps the tail of the previous kernel.
+    tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(NUM_THREADS - 64) : "memory");
+    tc_fence_after();
+    tmem_base = tmem_slot;
   }
-  // Every role below finishes its own set-up arithmetic first and executes griddepcontrol.wait just
-  // before its loop, so that the set-up overlaps the tail of the previous kernel.
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_slot;
   if (threadIdx.x == 0) TRACE(16, 2);
 
   if (warp == 0 || warp == PRODUCER2_WARP) {
