@@ -211,8 +211,54 @@ __device__ __forceinline__ void strided_vec_body(const StridedVecParams& p, int6
 __global__ void __launch_bounds__(256) strided_vec_kernel(const __grid_constant__ StridedVecParams p) {
   strided_vec_body(p, (int64_t)blockIdx.x * blockDim.x + threadIdx.x, (int64_t)gridDim.x * blockDim.x);
 }
-// Several vector copies in one launch (the inputs of a concatenate): blockIdx.y picks the copy.
+// Several element-wise copies in one launch, any strides and either element type on either side.
+struct StridedCopyItem {
+  int ndim, idx32;
+  int64_t total;
+  int64_t extent[6];
+  IdxDiv fd[6];
+  int64_t as[6], ys[6];
+  const void* a; void* y;
+  int ad, yd;
+  int64_t a_off, y_off;
+};
 constexpr int STRIDED_BATCH_MAX = 8;
+struct StridedCopyBatch { StridedCopyItem item[STRIDED_BATCH_MAX]; };
+__global__ void __launch_bounds__(256) strided_copy_batch_kernel(const __grid_constant__ StridedCopyBatch b) {
+  const StridedCopyItem& p = b.item[blockIdx.y];
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+    int64_t ao = p.a_off, yo = p.y_off;
+    if (p.idx32) {
+      uint32_t rem = (uint32_t)i;
+#pragma unroll
+      for (int k = 5; k >= 0; --k) {
+        if (k < p.ndim) {
+          const uint32_t q = idx_div(rem, p.fd[k]);
+          const int64_t c = (int64_t)(rem - q * (uint32_t)p.extent[k]);
+          rem = q;
+          ao += c * p.as[k];
+          yo += c * p.ys[k];
+        }
+      }
+    } else {
+      int64_t rem = i;
+#pragma unroll
+      for (int k = 5; k >= 0; --k) {
+        if (k < p.ndim) {
+          const int64_t c = rem % p.extent[k];
+          rem /= p.extent[k];
+          ao += c * p.as[k];
+          yo += c * p.ys[k];
+        }
+      }
+    }
+    const int32_t v = load_elem(p.a, p.ad, ao);
+    if (p.yd == CVMK_I8) reinterpret_cast<int8_t*>(p.y)[yo] = (int8_t)v;
+    else reinterpret_cast<int32_t*>(p.y)[yo] = v;
+  }
+}
+// Several vector copies in one launch (the inputs of a concatenate): blockIdx.y picks the copy.
 struct StridedVecBatch { StridedVecParams item[STRIDED_BATCH_MAX]; };
 __global__ void __launch_bounds__(256) strided_vec_batch_kernel(const __grid_constant__ StridedVecBatch b) {
   strided_vec_body(b.item[blockIdx.y], (int64_t)blockIdx.x * blockDim.x + threadIdx.x, (int64_t)gridDim.x * blockDim.x);
@@ -494,11 +540,49 @@ static bool strided_total(const cvmk_strided_desc* d, int64_t* total) {
   return true;
 }
 
-// `n` copies: one launch when all of them are vector copies (groups of STRIDED_BATCH_MAX), else one
-// cvmk_strided() each.
+// `n` copies: one launch per group of STRIDED_BATCH_MAX when all of them are vector copies, or all
+// plain copies without a chain; else one cvmk_strided() each.
 extern "C" int cvmk_strided_batch(const cvmk_strided_desc* d, int32_t n, cvmk_stream_t stream) {
   if (!d || n < 1) { set_error("strided_batch: bad argument"); return CVMK_ERR_ARG; }
   cudaStream_t s = (cudaStream_t)stream;
+  {
+    // element-wise form: every input a plain copy, but not all of them whole vectors
+    bool plain = n > 1, vectors = true;
+    for (int32_t i = 0; i < n && plain; ++i) {
+      int64_t total;
+      if (!strided_total(&d[i], &total)) return CVMK_ERR_ARG;
+      plain = d[i].op == CVMK_OP_COPY && d[i].ep.n == 0;
+      StridedVecParams tmp;
+      vectors = vectors && strided_as_vectors(&d[i], total, &tmp);
+    }
+    if (plain && !vectors) {
+      for (int32_t first = 0; first < n; first += STRIDED_BATCH_MAX) {
+        const int m = std::min<int32_t>(STRIDED_BATCH_MAX, n - first);
+        StridedCopyBatch b;
+        memset(&b, 0, sizeof(b));
+        int64_t largest = 0;
+        for (int i = 0; i < m; ++i) {
+          const cvmk_strided_desc& e = d[first + i];
+          StridedCopyItem& it = b.item[i];
+          it.ndim = e.ndim;
+          it.total = 1;
+          for (int k = 0; k < e.ndim; ++k) {
+            it.extent[k] = e.extent[k];
+            it.fd[k] = make_idx_div(e.extent[k]);
+            it.as[k] = e.a_stride[k];
+            it.ys[k] = e.y_stride[k];
+            it.total *= e.extent[k];
+          }
+          it.idx32 = it.total < ((int64_t)1 << 31);
+          it.a = e.a; it.y = e.y; it.ad = e.a_dtype; it.yd = e.y_dtype; it.a_off = e.a_off; it.y_off = e.y_off;
+          largest = std::max(largest, it.total);
+        }
+        strided_copy_batch_kernel<<<dim3((unsigned)grid_for(largest, 256), (unsigned)m), 256, 0, s>>>(b);
+        if (check_cuda(cudaGetLastError(), "strided_copy_batch_kernel launch")) return CVMK_ERR_CUDA;
+      }
+      return CVMK_OK;
+    }
+  }
   StridedVecBatch b;
   bool all = true;
   for (int32_t first = 0; first < n && all; first += STRIDED_BATCH_MAX) {
