@@ -360,7 +360,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // The two producer warps need nothing of the set-up below but the barriers, which thread 0 (of
   // producer warp 0) has just initialised: they meet at a barrier of their own and go on to their
   // loads, whose latency then runs while the other ten warps allocate TMEM and stage the bias.
+  // Warp 0 also ARRIVES (without waiting) at the barrier the other ten warps wait at, so that none
+  // of them touches an mbarrier or the abort flag before thread 0 has initialised them.
   const bool is_producer = warp == 0 || warp == PRODUCER2_WARP;
+  if (warp == 0) {
+    __threadfence_block();
+    asm volatile("bar.arrive 1, %0;" ::"n"(NUM_THREADS - 32) : "memory");
+  }
   if (is_producer) asm volatile("bar.sync 2, 64;" ::: "memory");
   auto stage_bias = [&]() {
     const int padded = min(MAX_BIAS, (p.oc + 31) & ~31);
@@ -380,7 +386,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // Every role below finishes its own set-up arithmetic first and executes griddepcontrol.wait just
     // before its loop, so that the set-up overlaps the tail of the previous kernel.
     tc_fence_before();
-    asm volatile("bar.sync 1, %0;" ::"n"(NUM_THREADS - 64) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(NUM_THREADS - 32) : "memory");   // ten warps wait, warp 0 has arrived
     tc_fence_after();
     tmem_base = tmem_slot;
   }

@@ -146,6 +146,16 @@ def op_cases():
     # depthwise 3x3 over an image wide enough that a band of rows needs more than 48 KB of shared memory
     add("depthwise_3x3_wide_band", lambda: conv_case(43, 1, 32, 9, 256, 32, 3, 1, 1, groups=32, shift=6, relu=True))
     add("depthwise_3x3_s2_wide_band", lambda: conv_case(44, 1, 64, 11, 192, 64, 3, 2, 1, groups=64, shift=6))
+    # depthwise 3x3 stride 1 over more shapes: ragged 28 x 28 images, a wide 32-channel image, four
+    # channel blocks without bias, no padding, 96 = 3 x 32 channels, 1024 channels; and an ordinary
+    # 32 -> 64 channel layer whose image is whole 8 x 16 pixel patches
+    add("depthwise_3x3_64ch_28x28", lambda: conv_case(45, 2, 64, 28, 28, 64, 3, 1, 1, groups=64, shift=6, relu=True))
+    add("depthwise_3x3_32ch_32x40", lambda: conv_case(46, 1, 32, 32, 40, 32, 3, 1, 1, groups=32, shift=6))
+    add("depthwise_3x3_256ch_nobias", lambda: conv_case(47, 3, 256, 14, 14, 256, 3, 1, 1, groups=256, bias=False, shift=5))
+    add("depthwise_3x3_pad0", lambda: conv_case(48, 1, 128, 18, 18, 128, 3, 1, 0, groups=128, shift=6))
+    add("depthwise_3x3_96ch", lambda: conv_case(49, 2, 96, 16, 16, 96, 3, 1, 1, groups=96, shift=6, relu=True))
+    add("depthwise_3x3_1024ch", lambda: conv_case(50, 1, 1024, 16, 16, 1024, 3, 1, 1, groups=1024, shift=6, relu=True))
+    add("conv_tc_3x3_32ch_patches", lambda: conv_case(51, 2, 32, 16, 24, 64, 3, 1, 1, shift=9, relu=True))
     # batch 8: the inference uploads the batch in four chunks and runs the stem per chunk
     add("conv_stem_fused_b8_chunked", lambda: conv_case(38, 8, 3, 20, 16, 32, 3, 2, 1, shift=7, relu=True))
     def stem_generic():
