@@ -22,7 +22,13 @@ int fail(int code, const char* what, cudaError_t e = cudaSuccess) {
   return code;
 }
 
-__global__ void __launch_bounds__(128) mma_rate_kernel(int n, int reps, int* status) {
+// row_bytes: row length of the A tile (128, 64 or 32: its swizzle); a_offset: bytes from the tile's
+// (1024-byte aligned) start to the first row the instruction reads; group_stride: bytes from one
+// 8-row group of A to the next.  (128, 0, 1024) is a dense K-major tile; a window of a staged input
+// halo, as the 3 x 3 halo mode of the convolution kernel reads it, starts some rows in and steps
+// one halo row (10 pixels) per group.
+__global__ void __launch_bounds__(128) mma_rate_kernel(int n, int reps, int* status, int row_bytes, int a_offset,
+                                                       int group_stride) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar;
   __shared__ uint32_t slot;
@@ -42,9 +48,12 @@ __global__ void __launch_bounds__(128) mma_rate_kernel(int n, int reps, int* sta
   const uint32_t tmem = slot;
   if (threadIdx.x == 0) {
     const uint32_t idesc = umma_idesc_i8(n);
-    const uint64_t da = umma_desc(smem_u32(smem), 128), db = umma_desc(smem_u32(smem + BLOCK_M * 128), 128);
+    uint64_t da = umma_desc(smem_u32(smem) + (uint32_t)a_offset, row_bytes);
+    da = (da & ~((uint64_t)0x3FFF << 32)) | ((uint64_t)((uint32_t)group_stride >> 4) << 32);
+    const uint64_t db = umma_desc(smem_u32(smem + BLOCK_M * 128), row_bytes);
+    const int kmask = row_bytes / 32 - 1;
     for (int i = 0; i < reps; ++i) {
-      const uint64_t koff = (uint64_t)(2 * (i & 3));
+      const uint64_t koff = (uint64_t)(2 * (i & kmask));
       mma_i8(tmem, da + koff, db + koff, idesc, 1u);
     }
     mma_commit(&bar);
@@ -86,7 +95,15 @@ extern "C" const char* cvmk_measure_last_error(void) { return g_measure_err; }
 
 // tops: 2 * multiply-accumulates per second / 1e12 over all SMs.  n: 32..256 (multiple of 16).
 extern "C" int cvmk_measure_i8_mma_rate(int n, int reps, double* tops) {
+  return cvmk_measure_i8_mma_rate_window(n, reps, 128, 0, 8, tops);
+}
+
+extern "C" int cvmk_measure_i8_mma_rate_window(int n, int reps, int row_bytes, int a_offset_rows, int group_stride_rows,
+                                               double* tops) {
   if (!tops || n < 32 || n > 256 || n % 16 || reps < 1) return fail(CVMK_ERR_ARG, "measure_i8_mma_rate: bad argument");
+  if ((row_bytes != 128 && row_bytes != 64 && row_bytes != 32) || a_offset_rows < 0 || a_offset_rows > 32 ||
+      group_stride_rows < 8 || group_stride_rows > 16)
+    return fail(CVMK_ERR_ARG, "measure_i8_mma_rate_window: row_bytes 32/64/128, offset 0..32 rows, group stride 8..16 rows");
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -100,9 +117,11 @@ extern "C" int cvmk_measure_i8_mma_rate(int n, int reps, double* tops) {
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0);
   cudaEventCreate(&e1);
-  mma_rate_kernel<<<sms, 128, smem>>>(n, reps / 10 + 1, status);  // warm-up
+  // (the window stays inside the (128 + 256) x 128 bytes the kernel fills: 32 + 15 * 16 + 8 rows at most)
+  const int a_off = a_offset_rows * row_bytes, gstride = group_stride_rows * row_bytes;
+  mma_rate_kernel<<<sms, 128, smem>>>(n, reps / 10 + 1, status, row_bytes, a_off, gstride);  // warm-up
   cudaEventRecord(e0);
-  mma_rate_kernel<<<sms, 128, smem>>>(n, reps, status);
+  mma_rate_kernel<<<sms, 128, smem>>>(n, reps, status, row_bytes, a_off, gstride);
   cudaEventRecord(e1);
   cudaError_t err = cudaEventSynchronize(e1);
   float ms = 0;

@@ -11,7 +11,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libcvm_runtime.so")
 MEASURE_LIB_PATH = os.path.join(HERE, "libcvm_measure.so")
-MEASURE_SYMBOLS = ["cvmk_measure_i8_mma_rate", "cvmk_measure_wait_timeout", "cvmk_measure_last_error"]
+MEASURE_SYMBOLS = ["cvmk_measure_i8_mma_rate", "cvmk_measure_i8_mma_rate_window", "cvmk_measure_wait_timeout",
+                   "cvmk_measure_last_error"]
 
 SUCCEED, ERROR_LOGIC, ERROR_RUNTIME = 0, 1, 2
 
@@ -207,6 +208,18 @@ def measure_i8_mma_rate(n=256, reps=20000):
     rc = measure_lib().cvmk_measure_i8_mma_rate(ctypes.c_int(n), ctypes.c_int(reps), ctypes.byref(tops))
     if rc != 0:
         raise RuntimeError("cvmk_measure_i8_mma_rate failed (%d): %s" % (rc, measure_lib().cvmk_measure_last_error().decode()))
+    return tops.value
+
+
+def measure_i8_mma_rate_window(n, reps, row_bytes, a_offset_rows, group_stride_rows):
+    """The rate with the A operand read as a window of a staged halo: rows of `row_bytes`, starting
+    `a_offset_rows` rows into the tile, 8-row groups `group_stride_rows` rows apart (TOP/s)."""
+    tops = ctypes.c_double()
+    rc = measure_lib().cvmk_measure_i8_mma_rate_window(ctypes.c_int(n), ctypes.c_int(reps), ctypes.c_int(row_bytes),
+                                                       ctypes.c_int(a_offset_rows), ctypes.c_int(group_stride_rows),
+                                                       ctypes.byref(tops))
+    if rc != 0:
+        raise RuntimeError("cvmk_measure_i8_mma_rate_window failed (%d): %s" % (rc, measure_lib().cvmk_measure_last_error().decode()))
     return tops.value
 
 

@@ -18,6 +18,13 @@ extern "C" {
  * the tensor roofline. */
 CVMK_API int cvmk_measure_i8_mma_rate(int n, int reps, double* tops);
 
+/* The same with the A operand read the way the 3 x 3 halo mode of the convolution kernel reads it:
+ * rows of `row_bytes` bytes (32, 64 or 128, with the matching swizzle), the first row
+ * `a_offset_rows` rows after the tile's 1024-byte aligned start, 8-row groups `group_stride_rows`
+ * rows apart (8 = a dense tile).  Shows what a window that straddles swizzle atoms costs. */
+CVMK_API int cvmk_measure_i8_mma_rate_window(int n, int reps, int row_bytes, int a_offset_rows, int group_stride_rows,
+                                             double* tops);
+
 /* Lets a bounded device-side wait run out on purpose: one thread waits, with the wait the
  * tensor-core kernels use, on an mbarrier that nothing arrives at, for `limit` polls of about 2 us
  * (1..65536).  The wait gives up, the kernel returns normally and *status_word receives what a
