@@ -576,8 +576,23 @@ struct Lowering {
       probe.acc_bound = (int64_t)icg * KH * KW * 128 * 128 + bias_max;
       probe.bias_static = (!use_bias || g.params.count(g.entry_id(n.inputs[2])) > 0) ? 1 : 0;
     }
-    const bool tc = groups == 1 && cvmk_conv2d_tc_supported(&probe) && !dev_env("CVM_B200_NO_TC");
     const bool depthwise = !dense && groups == C && OC == C && C % 16 == 0 && safe8[ex_];
+    // Depthwise 3x3 stride-1 layers over a multiple of 128 channels run on the tensor cores as
+    // groups of 32 channels with block-diagonal weights when the kernel's 8 x 16 pixel tiles fit
+    // the image: the CUDA-core form is bound by instruction issue at a fraction of the memory
+    // rate (measured 15-25 % slower on such layers; faster for 32 and 64 channels, which stay there).
+    const int dw_cg = 32;
+    bool dw_tc = false;
+    if (depthwise && C % 128 == 0 && KH == 3 && KW == 3 && sh == 1 && sw == 1 && dh == 1 && dw == 1 &&
+        out.dtype == CVMK_I8 && !dev_env("CVM_B200_NO_DW_TC") && !dev_env("CVM_B200_NO_TC")) {
+      const int64_t linear = ((int64_t)N * OH * OW + 127) / 128;
+      const int64_t tiles = (int64_t)((OW + 7) / 8) * ((OH + 15) / 16) * N;
+      probe.groups = C / dw_cg;
+      dw_tc = tiles * 20 <= linear * 27 && cvmk_conv2d_tc_supported(&probe);
+      if (!dw_tc) probe.groups = 0;
+    }
+    const bool tc = (dw_tc || groups == 1) && cvmk_conv2d_tc_supported(&probe) && !dev_env("CVM_B200_NO_TC");
+    const int wcg = dw_tc ? dw_cg : icg;   // input channels per weight row as the kernels take them
     // Few-channel convolutions (image stems): gather patches into a [M, Kp] matrix, then run the
     // tensor-core kernel on it as a 1x1 convolution.
     const int kflat = KH * KW * icg, kp = kflat > 64 ? (kflat + 63) / 64 * 64 : (kflat + 31) / 32 * 32;
@@ -605,8 +620,12 @@ struct Lowering {
       tc_pad = cvmk_conv2d_tc_supported(&pp) && plain_chain && bias_param && safe8[ex_] && out.shape.size() == 4;
     }
     // weights: OIHW int32 -> int8, [OC, KH, KW, C/groups] (depthwise: [KH, KW, C])
-    std::vector<int8_t> w8((size_t)(tc_pad ? OCp : OC) * KH * KW * icg);
-    if (depthwise && !tc) {
+    std::vector<int8_t> w8((size_t)(tc_pad ? OCp : OC) * KH * KW * wcg, 0);
+    if (dw_tc) {   // [OC, KH, KW, 32]: row o holds its filter in column o % 32 of every tap
+      for (int o = 0; o < OC; ++o)
+        for (int k = 0; k < KH * KW; ++k)
+          w8[((size_t)o * KH * KW + k) * wcg + (o % wcg)] = (int8_t)wt.data[(size_t)o * KH * KW + k];
+    } else if (depthwise && !tc) {
       for (int c = 0; c < C; ++c)
         for (int k = 0; k < KH * KW; ++k) w8[(size_t)k * C + c] = (int8_t)wt.data[(size_t)c * KH * KW + k];
     } else {
@@ -747,7 +766,8 @@ struct Lowering {
       ex.plans_.emplace_back((cvmk_conv_plan*)mem, plan_deleter);
       cvmk_conv_plan* plan = ex.plans_.back().get();
       KERNEL_OK(cvmk_conv2d_tc_prepare(&d, plan));
-      add_step(label + (plan->k_slices > 1 ? ":k-slices[tc]" : "[tc]"), [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
+      add_step(label + (dw_tc ? "[dw]" : (plan->k_slices > 1 ? ":k-slices[tc]" : "[tc]")),
+               [plan](cudaStream_t s) { return cvmk_conv2d_tc_launch(plan, s); });
       // Quarter-batch plans (every operand is batch-major, so a chunk is a contiguous slice).
       const int chunks = batch_chunks(d.N);
       if (chunks > 1 && xin.nhwc && out.nhwc) {

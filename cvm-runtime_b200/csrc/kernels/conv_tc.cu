@@ -82,6 +82,9 @@ struct ConvParams {
                         // 3 spatial patches whose input halo is staged once per channel block,
                         // 4 the same with the whole weight matrix resident in shared memory
   int b_resident;       // a_mode 0 with this CTA's N tile of the weights resident in shared memory
+  int grouped;          // grouped convolution (a_mode 4): `c` is the channels of ONE group, an N tile is block_n / c
+                        // groups and block_k = block_n; group j of N tile n0 reads input channels n0 + j * c .. and
+                        // fills accumulator columns j * c ..; the grid is a multiple of the N tiles
   int patch_w, patch_h, patch_n;  // a_mode 2, 3: an M tile is patch_w x patch_h output pixels of patch_n images
   int tiles_w, tiles_h;           // a_mode 2, 3: patches per image row / column
   int patch_w_log2, patch_h_log2; // patch sides are powers of two
@@ -288,7 +291,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 0) TRACE(16, 0);
   const int a_bytes = BLOCK_M * p.block_k;
-  const int b_bytes = p.block_n * p.block_k;
+  // (grouped: an N tile is gpt = block_n / c groups of c channels whose activations lie side by side
+  //  in one halo of block_k = block_n bytes per pixel; a weight tile is the c x c block of one group)
+  const int gpt = p.grouped ? p.block_n / p.c : 1;
+  const int b_bytes = p.grouped ? p.c * p.c : p.block_n * p.block_k;
   // b_resident: a 1x1 layer whose N tiles divide the grid, so that every tile of a CTA has the same
   // first output channel: the K blocks of that N tile are loaded once and stay in front of the
   // ring, which then carries activations only.
@@ -309,7 +315,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int halo_bytes = halo_w * (p.patch_h + p.kh - 1) * p.block_k;
   const int halo_pad = (halo_bytes + 1023) & ~1023;
   const int taps = p.kh * p.kw;
-  const int resident_bytes = w_resident ? p.num_kb * taps * b_bytes             // [channel block][tap][block_n x block_k]
+  const int resident_bytes = w_resident ? (p.grouped ? gpt : p.num_kb) * taps * b_bytes   // [channel block | group][tap][tile]
                                         : (b_resident ? p.num_units * b_bytes : 0);   // [K block][block_n x block_k]
   uint8_t* const ring = smem + resident_bytes;
   const int stage_bytes = w_resident ? halo_pad : (halo ? halo_pad + taps * b_bytes : p.units * unit_bytes);
@@ -412,24 +418,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // that is constant for a tile is computed once per tile.
       const uint32_t smem_base = smem_u32(ring);
       const uint32_t full0 = smem_u32(&bar_full[0]);
-      if (w_resident && which == 0) {  // the weight matrix, once (every tile of this CTA has n0 = 0)
+      const TileOrigin to_first = tile_origin(p, (int)blockIdx.x);
+      if (w_resident && which == 0) {  // the weight rows of this CTA's N tile, once (every tile of a CTA has the same n0)
         const uint32_t wb = smem_u32(&bar_weights);
         if (leader) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wb), "r"((uint32_t)resident_bytes) : "memory");
         uint32_t dst = smem_u32(smem);
-        for (int cb = 0; cb < p.num_kb; ++cb) {
-          int kcol = cb * p.block_k;
+        for (int cb = 0; cb < (p.grouped ? gpt : p.num_kb); ++cb) {
+          int kcol = p.grouped ? 0 : cb * p.block_k;
+          const int wrow = p.grouped ? to_first.n0 + cb * p.c : to_first.n0;
           for (int t = 0; t < taps; ++t) {
             if (leader) asm volatile(
                 "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                 " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(wb),
-                "r"(kcol), "r"(0)
+                "r"(kcol), "r"(wrow)
                 : "memory");
             dst += (uint32_t)b_bytes;
             kcol += p.c;
           }
         }
       }
-      const TileOrigin to_first = tile_origin(p, (int)blockIdx.x);
       if (b_resident && which == 0) {   // this CTA's N tile of the weights, once
         const uint32_t wb = smem_u32(&bar_weights);
         if (leader) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wb), "r"((uint32_t)resident_bytes) : "memory");
@@ -470,14 +477,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (leader) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
                          "r"((uint32_t)(halo_bytes + (w_resident ? 0 : taps * b_bytes))) : "memory");
             const int cc = cb * p.block_k;
+            const int ca = p.grouped ? cc + to.n0 : cc;   // a group reads its own input channels
             if (leader) asm volatile(
                 "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                 " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&tmap_a)),
-                "r"(bar), "r"(cc), "r"(to.cw - p.pad_w), "r"(to.ch - p.pad_h), "r"(to.cn)
+                "r"(bar), "r"(ca), "r"(to.cw - p.pad_w), "r"(to.ch - p.pad_h), "r"(to.cn)
                 : "memory");
             uint32_t sb = sa + (uint32_t)halo_pad;
             int kcol = cc;
-            for (int t = 0; t < (w_resident ? 0 : taps); ++t) {
+            for (int t = 0; t < (w_resident ? 0 : taps); ++t) {   // (grouped convolutions always keep their weights)
               if (leader) asm volatile(
                   "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
                   " [%0], [%1, {%3, %4}], [%2];" ::"r"(sb), "l"(reinterpret_cast<uint64_t>(&tmap_b)),
@@ -566,9 +574,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------------ MMA issuer
     {
       const bool leader = elect_one();
-      const uint32_t idesc = umma_idesc_i8(p.block_n);
+      const uint32_t idesc = umma_idesc_i8(p.grouped ? p.c : p.block_n);
       const uint64_t desc_a0 = umma_desc(smem_u32(ring), p.block_k);
-      const uint32_t w_lo0 = (uint32_t)umma_desc(smem_u32(smem), p.block_k);  // resident weights (a_mode 4)
+      const uint64_t desc_w0 = umma_desc(smem_u32(smem), p.grouped ? p.c : p.block_k);  // resident weights (a_mode 4)
+      const uint32_t w_lo0 = (uint32_t)desc_w0, w_hi = (uint32_t)(desc_w0 >> 32);
       // halo windows: 8-pixel groups are one halo row (halo_w pixels) apart
       const uint64_t desc_halo0 = (desc_a0 & ~((uint64_t)0x3FFF << 32)) |
                                   ((uint64_t)(((uint32_t)(halo_w * p.block_k)) >> 4) << 32);
@@ -579,6 +588,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t stage_q = (uint32_t)stage_bytes >> 4, unit_q = (uint32_t)unit_bytes >> 4;
       const uint32_t a_q = (uint32_t)a_bytes >> 4, b_q = (uint32_t)b_bytes >> 4;
       const uint32_t halo_pad_q = (uint32_t)halo_pad >> 4, halo_row_q = (uint32_t)(halo_w * p.block_k) >> 4;
+      const uint32_t pix_q = (uint32_t)p.block_k >> 4;   // grouped: one pixel of the halo row
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -605,17 +615,36 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tc_fence_after();
           const uint32_t st = a_lo0 + stage_q * (uint32_t)stage;
           if (halo) {
-            // 3 x 3 taps x two K slices of the 64-channel block, straight line
             TSTART(ti);
-            uint32_t bl = w_resident ? w_lo0 + (uint32_t)(kb * 9) * b_q : st + halo_pad_q;
+            if (p.grouped) {
+              // every group of the N tile: its own columns of the halo rows, its own 9 weight tiles,
+              // its own accumulator columns (the first tap overwrites them)
+              uint32_t bl = w_lo0;
+              uint32_t d_blk = d_tmem, a_g = st;
+              for (int g = 0; g < gpt; ++g, d_blk += 32u, a_g += 2u) {   // 32 columns, 32 bytes of the halo rows
 #pragma unroll
-            for (int fy = 0; fy < 3; ++fy) {
-              uint32_t al = st + (uint32_t)fy * halo_row_q;
+                for (int fy = 0; fy < 3; ++fy) {
+                  uint32_t al = a_g + (uint32_t)fy * halo_row_q;
 #pragma unroll
-              for (int fx = 0; fx < 3; ++fx) {
-                if (leader) mma_i8_k<2>(d_tmem, al, halo_hi, bl, a_hi, idesc, (uint32_t)(kb | fy | fx));
-                al += 4u;   // one pixel of 64 channels
-                bl += b_q;
+                  for (int fx = 0; fx < 3; ++fx) {
+                    if (leader) mma_i8_k<1>(d_blk, al, halo_hi, bl, w_hi, idesc, (uint32_t)(fy | fx));
+                    al += pix_q;
+                    bl += b_q;
+                  }
+                }
+              }
+            } else {
+              // 3 x 3 taps x two K slices of the 64-channel block, straight line
+              uint32_t bl = w_resident ? w_lo0 + (uint32_t)(kb * 9) * b_q : st + halo_pad_q;
+#pragma unroll
+              for (int fy = 0; fy < 3; ++fy) {
+                uint32_t al = st + (uint32_t)fy * halo_row_q;
+#pragma unroll
+                for (int fx = 0; fx < 3; ++fx) {
+                  if (leader) mma_i8_k<2>(d_tmem, al, halo_hi, bl, a_hi, idesc, (uint32_t)(kb | fy | fx));
+                  al += 4u;   // one pixel of 64 channels
+                  bl += b_q;
+                }
               }
             }
             TADD(13, ti);
@@ -978,6 +1007,24 @@ bool pick_patch(const cvmk_conv_desc& d, int* pw, int* ph, int* pn) {
   return best > 0 && best * 4 <= linear * 5;
 }
 
+// Halo tiles are 8 x 16 output pixels of one image: taken when that needs at most 35 % more tiles
+// than cutting the output rows linearly.
+bool halo_tiles_fit(const cvmk_conv_desc& d) {
+  const int64_t linear = ((int64_t)d.N * d.OH * d.OW + BLOCK_M - 1) / BLOCK_M;
+  const int64_t tiles = (int64_t)((d.OW + 7) / 8) * ((d.OH + 15) / 16) * d.N;
+  return tiles * 20 <= linear * 27;
+}
+
+// Grouped convolutions run in halo mode only, one group per N tile.
+bool grouped_supported(const cvmk_conv_desc& d) {
+  if (d.C % d.groups != 0 || d.OC % d.groups != 0) return false;
+  const int cg = d.C / d.groups;
+  if (cg != d.OC / d.groups || cg != 32) return false;
+  if (d.KH != 3 || d.KW != 3 || d.stride_h != 1 || d.stride_w != 1 || d.dil_h != 1 || d.dil_w != 1) return false;
+  if (d.OH != d.H + 2 * d.pad_h - 2 || d.OW != d.W + 2 * d.pad_w - 2) return false;
+  return halo_tiles_fit(d);
+}
+
 }  // namespace
 }  // namespace cvmk
 
@@ -986,6 +1033,7 @@ using namespace cvmk;
 extern "C" int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d) {
   if (!d) return 0;
   if (d->C % 32 != 0 || d->OC % 8 != 0) return 0;
+  if (d->groups > 1 && !grouped_supported(*d)) return 0;
   if (d->pad_h > 127 || d->pad_w > 127) return 0;
   if ((d->KH - 1) * d->dil_h > 255 || (d->KW - 1) * d->dil_w > 255) return 0;
   if ((d->KH - 1) * d->dil_h - d->pad_h > 128 || (d->KW - 1) * d->dil_w - d->pad_w > 128) return 0;
@@ -998,7 +1046,7 @@ extern "C" int cvmk_conv2d_tc_supported(const cvmk_conv_desc* d) {
 // the number of K blocks, leaves at least four blocks per slice, and is the smallest that makes
 // the best use of the SMs (tiles / (waves x SMs)).
 static int pick_k_slices(const cvmk_conv_desc& d, int bk, int bn) {
-  if (!is_pointwise(d) || (int64_t)d.N * d.OH * d.OW > BLOCK_M || d.OC % bn != 0 || d.C % bk != 0) return 1;
+  if (!is_pointwise(d) || d.groups > 1 || (int64_t)d.N * d.OH * d.OW > BLOCK_M || d.OC % bn != 0 || d.C % bk != 0) return 1;
   if (dev_env("CVM_B200_NO_SPLIT_K")) return 1;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -1058,28 +1106,43 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
 
   memset(plan, 0, sizeof(*plan));
   plan->d = *d;
-  int bk = pick_block_k(d->C);
-  if (const char* e = dev_env("CVM_B200_BK")) {  // experiments: a smaller K block (must divide C)
+  const bool grouped = d->groups > 1;
+  const int cg = grouped ? d->C / d->groups : d->C;   // channels one output channel reduces over
+  if (grouped && d->y_dtype != CVMK_I8) {
+    set_error("conv2d_tc_prepare: grouped convolutions write int8");
+    return CVMK_ERR_UNSUPPORTED;
+  }
+  int bk = grouped ? cg : pick_block_k(d->C);   // (grouped: set to the N tile below)
+  if (const char* e = grouped ? nullptr : dev_env("CVM_B200_BK")) {  // experiments: a smaller K block (must divide C)
     const int v = atoi(e);
     if ((v == 32 || v == 64 || v == 128) && d->C % v == 0 && v <= bk) bk = v;
   }
-  const int bn = pick_block_n(d->OC);
+  // grouped: an N tile is as many whole groups as make the epilogue's work per tile worth its
+  // fixed cost and still leave room for the groups' weights beside the ring (128 channels)
+  int bn = pick_block_n(d->OC);
+  if (grouped) {
+    bn = cg;
+    while (bn < 128 && d->OC % (2 * bn) == 0) bn *= 2;
+    bk = bn;   // one halo holds the channels of all groups of the N tile
+  }
   plan->block_n = bn;
   int patch_w = 0, patch_h = 0, patch_n = 0;
   plan->a_im2col = is_pointwise(*d) ? 0 : 1;
-  if (plan->a_im2col && d->stride_h == 1 && d->stride_w == 1 && !dev_env("CVM_B200_NO_PATCH") &&
-      pick_patch(*d, &patch_w, &patch_h, &patch_n))
+  if (plan->a_im2col && d->stride_h == 1 && d->stride_w == 1 && (grouped || !dev_env("CVM_B200_NO_PATCH")) &&
+      (grouped || pick_patch(*d, &patch_w, &patch_h, &patch_n)))
     plan->a_im2col = 2;
   // Halo mode: 3x3 (or any small) stride-1 undilated filters over at most 128 channels and output
   // channels.  The M tile is an 8 x 16 pixel patch of one image; its 10 x 18 input halo is loaded
   // once per 64-channel block and every filter tap multiplies a window of it, so the activations
   // cross L2 -> shared memory about 1.4 times instead of kh * kw times.
   bool halo = false;
-  if (plan->a_im2col == 2 && d->dil_h == 1 && d->dil_w == 1 && d->KH == 3 && d->KW == 3 && d->C % 64 == 0 &&
+  if (grouped) {   // (shape and tile fit were checked by cvmk_conv2d_tc_supported)
+    halo = true;
+    plan->a_im2col = 3;
+    patch_w = 8; patch_h = 16; patch_n = 1;
+  } else if (plan->a_im2col == 2 && d->dil_h == 1 && d->dil_w == 1 && d->KH == 3 && d->KW == 3 && d->C % 64 == 0 &&
       d->C <= 128 && bn <= 128 && d->y_dtype == CVMK_I8 && d->OC % 32 == 0 && !dev_env("CVM_B200_NO_HALO")) {
-    const int64_t linear = ((int64_t)d->N * d->OH * d->OW + BLOCK_M - 1) / BLOCK_M;
-    const int64_t tiles = (int64_t)((d->OW + 7) / 8) * ((d->OH + 15) / 16) * d->N;
-    if (tiles * 20 <= linear * 27) {
+    if (halo_tiles_fit(*d)) {
       halo = true;
       plan->a_im2col = 3;
       patch_w = 8; patch_h = 16; patch_n = 1;
@@ -1114,7 +1177,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   // is still deep enough; short reductions (little work per output tile) may give up half of their
   // K block for it.
   const int group_bytes = plan->panels * BLOCK_M * plan->panel_bytes;
-  const int64_t k_all = (int64_t)d->KH * d->KW * d->C / plan->k_slices;   // per tile
+  const int64_t k_all = (int64_t)d->KH * d->KW * cg / plan->k_slices;   // per tile
   const int budget = SMEM_DYNAMIC_MAX - 1024;
   plan->io_bufs = 1;
   // Weights resident in shared memory: one N tile, i.e. every tile of the launch multiplies the
@@ -1122,13 +1185,25 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   // halo alone.
   const int halo_pad = ((10 * 18 * bk) + 1023) & ~1023;
   int resident = 0;
-  if (halo && d->OC <= bn && !dev_env("CVM_B200_NO_RESIDENT_WEIGHTS")) {
+  int sms_all = 148;
+  {
+    int dev0 = 0;
+    if (cudaGetDevice(&dev0) == cudaSuccess) cudaDeviceGetAttribute(&sms_all, cudaDevAttrMultiProcessorCount, dev0);
+    cudaGetLastError();
+  }
+  // (grouped: the grid is cut to a multiple of the N tiles below, so that every tile of a CTA
+  //  covers the same groups and their 9 weight tiles each can stay as well)
+  if (halo && (d->OC <= bn || (grouped && d->OC / bn <= sms_all)) && !dev_env("CVM_B200_NO_RESIDENT_WEIGHTS")) {
     // all channel blocks (one or two) stay, if three halo stages and one staging buffer per group still fit
-    const int all = (d->C / bk) * d->KH * d->KW * bn * bk;
+    const int all = grouped ? d->KH * d->KW * bn * cg : (cg / bk) * d->KH * d->KW * bn * bk;
     if (budget - all - 2 * group_bytes >= 3 * halo_pad) {
       resident = all;
       plan->a_im2col = 4;
     }
+  }
+  if (grouped && plan->a_im2col != 4) {
+    set_error("conv2d_tc_prepare: the weights of a grouped convolution's N tile must fit shared memory");
+    return CVMK_ERR_UNSUPPORTED;
   }
   const int halo_stage = halo ? (resident ? halo_pad : halo_pad + d->KH * d->KW * bn * bk) : 0;
   if (halo) {
@@ -1186,7 +1261,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   plan->smem_bytes = plan->ring_bytes + io_bytes + 1024;
 
   const int64_t m_total = (int64_t)d->N * d->OH * d->OW;
-  const int64_t k_total = (int64_t)d->KH * d->KW * d->C;
+  const int64_t k_total = (int64_t)d->KH * d->KW * cg;
   CUtensorMap* ta = reinterpret_cast<CUtensorMap*>(plan->tmap_a);
   CUtensorMap* tb = reinterpret_cast<CUtensorMap*>(plan->tmap_b);
   CUresult r;
@@ -1210,7 +1285,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
     r = encode_rows(enc_tiled, ta, d->x, m_total, d->C, bk, BLOCK_M, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
   }
   if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: activation tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
-  r = encode_rows(enc_tiled, tb, d->w, d->OC, k_total, bk, bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+  r = encode_rows(enc_tiled, tb, d->w, d->OC, k_total, grouped ? cg : bk, grouped ? cg : bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (r != CUDA_SUCCESS) { set_error("conv2d_tc_prepare: weight tensor map rejected (CUresult %d)", (int)r); return CVMK_ERR_CUDA; }
   if (plan->tma_out) {
     auto encode_out = [&](unsigned char* map, const void* base, CUtensorMapL2promotion promo) {
@@ -1237,6 +1312,7 @@ extern "C" int cvmk_conv2d_tc_prepare(const cvmk_conv_desc* d, cvmk_conv_plan* p
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int64_t tiles = num_m_tiles * num_n_tiles * plan->k_slices;
   plan->grid = (int)(tiles < sms ? tiles : sms);
+  if (grouped && plan->a_im2col == 4) plan->grid = (int)(plan->grid / num_n_tiles * num_n_tiles);   // tile t + k * grid: same group as t
   return CVMK_OK;
 }
 
@@ -1268,8 +1344,9 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
     p.num_m_tiles = p.tiles_w * p.tiles_h * ((d.N + p.patch_n - 1) / p.patch_n);
   }
   p.num_n_tiles = (d.OC + plan->block_n - 1) / plan->block_n;
-  p.num_units = d.KH * d.KW * (d.C / plan->block_k);
-  p.num_kb = p.a_mode >= 3 ? d.C / plan->block_k : (p.num_units + p.units - 1) / p.units;
+  if (d.groups > 1) { p.grouped = 1; p.c = d.C / d.groups; }
+  p.num_units = p.grouped ? d.KH * d.KW : d.KH * d.KW * (p.c / plan->block_k);
+  p.num_kb = p.a_mode >= 3 ? (p.grouped ? 1 : p.c / plan->block_k) : (p.num_units + p.units - 1) / p.units;
   p.fd_n_tiles = make_fastdiv(p.num_n_tiles);
   p.fd_tiles_w = make_fastdiv(p.tiles_w);
   p.fd_tiles_h = make_fastdiv(p.tiles_h);
@@ -1282,7 +1359,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.status = d.status;
   p.bias_static = d.bias_static;
   p.w = d.w;
-  p.w_bytes = (unsigned)std::min<int64_t>((int64_t)d.OC * d.KH * d.KW * d.C, (int64_t)1 << 30);
+  p.w_bytes = (unsigned)std::min<int64_t>((int64_t)d.OC * d.KH * d.KW * p.c, (int64_t)1 << 30);
   p.tma_out = plan->tma_out; p.res_step = plan->res_step;
   const int ks = plan->k_slices > 1 ? plan->k_slices : 1;
   if (ks > 1) {   // virtual columns (slice, real column); int32 partial sums, no chain in this kernel

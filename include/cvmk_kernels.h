@@ -120,7 +120,15 @@ typedef struct {
    * like w.  The kernel may then read both before the previous kernel of the stream has finished
    * (it stages the bias and warms L2 with the weights while it waits for its turn). */
   int32_t bias_static;
-  int32_t reserved0;
+  /* 0 or 1: an ordinary convolution.  > 1: a grouped convolution whose groups are C / groups = OC /
+   * groups = 32 channels wide, 3 x 3, stride 1, no dilation, int8 output; w is then
+   * [OC, KH, KW, 32].  A depthwise layer runs this way with block-diagonal weights (channel c of a
+   * group multiplies only row c of that group): an N tile is up to four groups side by side, one
+   * input halo serves all of them and each group is nine M128 N32 K32 instructions into its own
+   * accumulator columns.  Only the diagonal of every 32 x 32 block is used, and it is still faster
+   * than the CUDA-core form for 128 channels and more, which is bound by instruction issue.
+   * cvmk_conv2d_tc_supported() says whether the 8 x 16 pixel tiles fit the image. */
+  int32_t groups;
   /* Optional scratch for reductions cut along K (dense layers of a few rows over a long K, whose
    * few output tiles would leave most SMs idle): cvmk_conv2d_tc_workspace_bytes() says how much the
    * shape wants (0: it is not cut).  With at least that much here, K slices run as separate tiles

@@ -155,6 +155,9 @@ def op_cases():
     add("depthwise_3x3_pad0", lambda: conv_case(48, 1, 128, 18, 18, 128, 3, 1, 0, groups=128, shift=6))
     add("depthwise_3x3_96ch", lambda: conv_case(49, 2, 96, 16, 16, 96, 3, 1, 1, groups=96, shift=6, relu=True))
     add("depthwise_3x3_1024ch", lambda: conv_case(50, 1, 1024, 16, 16, 1024, 3, 1, 1, groups=1024, shift=6, relu=True))
+    # (128 channels and more run on the tensor cores as groups of 32 channels: ragged patches, three N tiles)
+    add("depthwise_3x3_128ch_28x28", lambda: conv_case(52, 2, 128, 28, 28, 128, 3, 1, 1, groups=128, shift=6, relu=True))
+    add("depthwise_3x3_384ch", lambda: conv_case(53, 1, 384, 16, 24, 384, 3, 1, 1, groups=384, shift=6))
     add("conv_tc_3x3_32ch_patches", lambda: conv_case(51, 2, 32, 16, 24, 64, 3, 1, 1, shift=9, relu=True))
     # batch 8: the inference uploads the batch in four chunks and runs the stem per chunk
     add("conv_stem_fused_b8_chunked", lambda: conv_case(38, 8, 3, 20, 16, 32, 3, 2, 1, shift=7, relu=True))
