@@ -92,6 +92,8 @@ struct ConvParams {
   int num_units, num_kb;          // (tap, channel block) pairs per tile; ring stages consumed per tile
   FastDiv fd_n_tiles, fd_tiles_w, fd_tiles_h, fd_ohow, fd_ow;
   int tmem_cols;
+  int acc_bufs;         // accumulators in TMEM: 2, or 4 when block_n <= 128 (the MMA warp may then run three tiles ahead
+                        // of the epilogue groups, each of which drains its tiles into accumulators g and g + 2 in turn)
   int* status;
   const int32_t* bias;  // per-channel add applied first (nullptr: none)
   int first_step;       // chain steps before this one are already covered by `bias`
@@ -270,8 +272,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[MAX_STAGES];
   __shared__ uint64_t bar_empty[MAX_STAGES];
-  __shared__ uint64_t bar_acc_full[2];
-  __shared__ uint64_t bar_acc_empty[2];
+  __shared__ uint64_t bar_acc_full[4];
+  __shared__ uint64_t bar_acc_empty[4];
   __shared__ uint64_t bar_res[2][2];     // [group][buffer]: staging buffer free / operand tile landed in it
   __shared__ uint64_t bar_staged[2][2];  // [group][buffer]: the group has written its tile into the buffer
   __shared__ uint64_t bar_weights;       // a_mode 4: the resident weight matrix has landed
@@ -328,9 +330,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(&bar_full[s], 1);
       mbar_init(&bar_empty[s], 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < 4; ++a) {
       mbar_init(&bar_acc_full[a], 1);
       mbar_init(&bar_acc_empty[a], NUM_EPI_WARPS / 2);
+    }
+    for (int a = 0; a < 2; ++a) {
       for (int b = 0; b < 2; ++b) {
         mbar_init(&bar_res[a][b], 1);
         mbar_init(&bar_staged[a][b], NUM_EPI_WARPS / 2);
@@ -678,8 +682,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (!live) break;
         if (leader) mma_commit(&bar_acc_full[acc]);
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1;
+        if (++acc == p.acc_bufs) { acc = 0; acc_phase ^= 1; }
       }
       TADD(3, tl);
 #ifdef CVMK_CONV_TIMING
@@ -703,7 +706,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const bool leader = lane == 0 && (ew & 3) == 0;
     uint8_t* group_base = smem + p.ring_bytes + (size_t)group * p.io_bufs * buf_bytes;
     const bool vec_ok = (p.y_dtype == CVMK_I8) ? (p.oc % 16 == 0) : (p.oc % 4 == 0);
-    const int acc = group;
+    const bool four_acc = p.acc_bufs == 4;
     const int stride_tiles = 2 * gridDim.x;
     const int first_tile = blockIdx.x + group * gridDim.x;
     // patch mode: this thread's pixel inside the patch
@@ -730,7 +733,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t use = (uint32_t)(p.io_bufs == 2 ? (k >> 1) : k);  // how often this buffer was used before
       uint8_t* io_base = group_base + (size_t)buf * buf_bytes;
       TSTART(tw);
-      bool ok = mbar_wait(&bar_acc_full[acc], (uint32_t)(k & 1), &abort_flag, 4);
+      // this group's k-th tile: accumulator g, or g and g + 2 in turn
+      const int acc = four_acc ? group + 2 * (k & 1) : group;
+      bool ok = mbar_wait(&bar_acc_full[acc], (uint32_t)((four_acc ? k >> 1 : k) & 1), &abort_flag, 4);
       TADD(4 + 4 * group, tw);
       if (leader) TRACE(7 + 3 * group, k);
       tc_fence_after();
@@ -1352,7 +1357,8 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.fd_tiles_h = make_fastdiv(p.tiles_h);
   p.fd_ohow = make_fastdiv(d.OH * d.OW);
   p.fd_ow = make_fastdiv(d.OW);
-  int cols = 2 * plan->block_n;
+  p.acc_bufs = (plan->block_n <= 128 && !dev_env("CVM_B200_TWO_ACCUMULATORS")) ? 4 : 2;
+  int cols = p.acc_bufs * plan->block_n;
   int pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
   p.tmem_cols = pow2;
