@@ -88,7 +88,9 @@ typedef struct {
 } cvmk_epilogue;
 
 /* ------------------------------------------------------------------------------------------------
- * conv2d, groups = 1, and dense, on the tcgen05 int8 tensor cores.
+ * conv2d, groups = 1, and dense, on the tcgen05 int8 tensor cores; grouped 3 x 3 convolutions with
+ * 32 channels per group as well (`groups` below; depthwise layers, i.e. the groups > 1 branch
+ * cpu/ops/ops.cc:417-425 with depthwise_conv2d :248-277, are given to it with block-diagonal weights).
  * Reproduces cvm.runtime.cpu.conv2d (src/runtime/cpu/ops/ops.cc:368-456: im2col_cpu :204-246 +
  * matrix_mul :148-200) and cvm.runtime.cpu.dense (:34-75) followed by the fused chain.
  *
