@@ -598,6 +598,29 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int acc = 0;
       uint32_t acc_phase = 0;
       bool live = true;
+      // tcgen05.commit keeps this thread until the instructions queued before it have left the
+      // queue, so after a commit the tensor pipe stands idle until the next instruction has been
+      // issued -- through the loop overhead and the barrier checks of the next tile, if the commits
+      // sit at the end of a tile.  So the commits a tile owes (its accumulator is complete, its ring
+      // stage is free) are issued a few instructions INTO the next stage's instructions, where
+      // nothing but the rest of that straight-line block follows them; they then also cover those
+      // few instructions, which delays the signal by their run time.  Done in the halo modes, whose
+      // stages are nine or more instructions and whose rings are deep.  Whenever the thread would
+      // have to block on a barrier it pays its debts first (flush), so that an epilogue group or a
+      // producer never waits for a commit that waits for them.
+      int owed_stage = -1, owed_acc = -1;
+      auto flush = [&]() {
+        if (leader) {
+          if (owed_acc >= 0) mma_commit(&bar_acc_full[owed_acc]);
+          if (owed_stage >= 0) mma_commit(&bar_empty[owed_stage]);
+        }
+        owed_acc = owed_stage = -1;
+      };
+      auto ensure = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+        if (mbar_test(bar, parity)) return true;
+        flush();
+        return mbar_wait(bar, parity, &abort_flag, code);
+      };
       int mseq = 0, tseq = 0; (void)mseq; (void)tseq;
       TDECL;
       TSTART(tl);
@@ -605,7 +628,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if ((w_resident || b_resident) && blockIdx.x < num_tiles && !mbar_wait(&bar_weights, 0u, &abort_flag, 7)) live = false;
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
         TSTART(tw);
-        if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1, &abort_flag, 2)) { live = false; break; }
+        if (!ensure(&bar_acc_empty[acc], acc_phase ^ 1, 2)) { live = false; break; }
         TADD(1, tw);
         if (leader) TRACE(6, tseq);
         ++tseq;
@@ -613,7 +636,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.block_n);
         int unit = 0;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&bar_full[stage], phase, &abort_flag, 3)) { live = false; break; }
+          if (!ensure(&bar_full[stage], phase, 3)) { live = false; break; }
           TADD(2, tw);
           if (leader) TRACE(4, mseq);
           tc_fence_after();
@@ -635,6 +658,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     al += pix_q;
                     bl += b_q;
                   }
+                  if (fy == 0 && g == 0) flush();
                 }
               }
             } else {
@@ -649,10 +673,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   al += 4u;   // one pixel of 64 channels
                   bl += b_q;
                 }
+                if (fy == 0) flush();
               }
             }
             TADD(13, ti);
-            if (leader) mma_commit(&bar_empty[stage]);
+            owed_stage = stage;
             if (leader) TRACE(5, mseq);
             ++mseq;
             TADD(14, ti);
@@ -665,6 +690,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // B next to A in the stage, or K block `unit` of the resident weights
           uint32_t bl = b_resident ? w_lo0 + (uint32_t)unit * b_q : st + a_q;
           const uint32_t b_step = b_resident ? b_q : unit_q;
+          // (a stage of these modes is one to four instructions groups: its commit follows at once --
+          //  deferring it would only take a stage out of a ring that is three deep)
           if (leader) {
             if (nk == 4) {
               for (int u = 0; u < in_stage; ++u, al += unit_q, bl += b_step) mma_i8_k<4>(d_tmem, al, a_hi, bl, a_hi, idesc, (uint32_t)(unit + u));
@@ -681,9 +708,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (!live) break;
-        if (leader) mma_commit(&bar_acc_full[acc]);
+        owed_acc = acc;
+        if (!halo) flush();
         if (++acc == p.acc_bufs) { acc = 0; acc_phase ^= 1; }
       }
+      if (live) flush();
       TADD(3, tl);
 #ifdef CVMK_CONV_TIMING
       if (leader) { TFLUSH(1); TFLUSH(2); TFLUSH(3); TFLUSH(13); TFLUSH(14); }

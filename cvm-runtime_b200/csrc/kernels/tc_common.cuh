@@ -59,6 +59,20 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_
       : "memory");
   return ok != 0;
 }
+// Non-blocking: true if the phase with `parity` has completed.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait (about a second in all).  Returns false when it gave up, or when another role of
 // this CTA already did.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
