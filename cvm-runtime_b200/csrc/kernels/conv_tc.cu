@@ -196,22 +196,36 @@ __device__ __forceinline__ void fast_chunk(const ConvParams& p, const FastQ& fq,
   *q1 = b;
 }
 
+// `acc_free`: the barrier that hands the accumulator back to the MMA warp.  The warp arrives at it
+// as soon as its last columns are in registers (the loads have completed: tcgen05.wait::ld), not
+// after the arithmetic on them: the MMA warp's way back to a full accumulator (it notices, issues,
+// the instructions run, this group notices) then overlaps the last quarter of this tile's work
+// instead of following it.  Used when the tile is so wide that TMEM holds only two accumulators
+// (nullptr otherwise: with four, the MMA warp is tiles ahead anyway).
 template <int RELU1, int KIND, int WIDE>
 __device__ __forceinline__ void fast_row(const ConvParams& p, uint32_t tbase, int chunks, const int32_t* bias_row,
-                                         uint8_t* io_base, int panel_size, int row_in_tile, int pw) {
+                                         uint8_t* io_base, int panel_size, int row_in_tile, int pw, uint64_t* acc_free) {
   const FastQ fq = {p.f_lo1, p.f_hi1, p.f_lo2, p.f_hi2};
   const uint32_t row_off = (uint32_t)row_in_tile * (uint32_t)pw;
   const uint32_t sw = (row_off >> 7) & (((uint32_t)pw - 1u) >> 4);  // swizzle key of this row, as in panel_offset()
+  auto release = [&]() {
+    if (acc_free == nullptr) return;
+    tc_fence_before();
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(acc_free);
+  };
   int ci = 0;
   for (; ci + 2 <= chunks; ci += 2) {  // two chunks per TMEM round trip
     int32_t v0[32], v1[32];
     tmem_ld64(tbase + (uint32_t)(ci * 32), v0, v1);
+    if (ci + 2 >= chunks) release();
     fast_chunk<RELU1, KIND, WIDE>(p, fq, v0, ci, bias_row, io_base, panel_size, row_off, sw);
     fast_chunk<RELU1, KIND, WIDE>(p, fq, v1, ci + 1, bias_row, io_base, panel_size, row_off, sw);
   }
   if (ci < chunks) {
     int32_t v[32];
     tmem_ld32(tbase + (uint32_t)(ci * 32), v);
+    release();
     fast_chunk<RELU1, KIND, WIDE>(p, fq, v, ci, bias_row, io_base, panel_size, row_off, sw);
   }
 }
@@ -778,23 +792,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (p.fast_mode) {
           const int chunks = min(p.block_n, p.oc - n0) >> 5;  // OC is a multiple of 32 on this path
           const int32_t* brow = bias_s + n0;
+          uint64_t* early_free = four_acc ? nullptr : &bar_acc_empty[acc];
           switch (p.fast_variant + 8 * p.fast_wide) {
-            case 0: fast_row<0, 0, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 1: fast_row<1, 0, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 2: fast_row<0, 1, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 3: fast_row<1, 1, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 4: fast_row<0, 2, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 5: fast_row<1, 2, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 6: fast_row<0, 3, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 7: fast_row<1, 3, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 8: fast_row<0, 0, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 9: fast_row<1, 0, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 10: fast_row<0, 1, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 11: fast_row<1, 1, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 12: fast_row<0, 2, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 13: fast_row<1, 2, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            case 14: fast_row<0, 3, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
-            default: fast_row<1, 3, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw); break;
+            case 0: fast_row<0, 0, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 1: fast_row<1, 0, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 2: fast_row<0, 1, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 3: fast_row<1, 1, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 4: fast_row<0, 2, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 5: fast_row<1, 2, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 6: fast_row<0, 3, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 7: fast_row<1, 3, 0>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 8: fast_row<0, 0, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 9: fast_row<1, 0, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 10: fast_row<0, 1, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 11: fast_row<1, 1, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 12: fast_row<0, 2, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 13: fast_row<1, 2, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            case 14: fast_row<0, 3, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
+            default: fast_row<1, 3, 1>(p, tbase, chunks, brow, io_base, panel_size, row_in_tile, pw, early_free); break;
           }
         } else {
         int32_t v[32];
@@ -865,7 +880,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (p.tma_out) fence_async_smem();  // make the staged bytes visible to the TMA engine
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&bar_acc_empty[acc]);
+        if (!p.fast_mode || four_acc) mbar_arrive(&bar_acc_empty[acc]);   // (else fast_row has handed it back already)
         if (p.tma_out) mbar_arrive(&bar_staged[group][buf]);
       }
       TADD(6 + 4 * group, tw);
