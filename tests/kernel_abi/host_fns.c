@@ -5,6 +5,7 @@
  * here and the packed bytes written to the file named on the command line.
  *
  *   host_fns workspace N H W C OC KH KW        -> "@supported=.. @workspace=.."
+ *   host_fns grouped N H W C groups K stride   -> "@supported=.." (OC = C, padding K / 2)
  *   host_fns stem N H W C OC KH KW stride pad out.bin
  *                                              -> "@supported=.. @weight_bytes=.. @pack=.."
  * The stem filter is w[oc][c][ky][kx] = ((oc * 131 + c * 31 + ky * 7 + kx) mod 255) - 127.
@@ -28,6 +29,20 @@ int main(int argc, char** argv) {
     d.pad_h = d.KH / 2; d.pad_w = d.KW / 2;
     d.OH = d.H; d.OW = d.W;
     printf("@supported=%d @workspace=%lld\n", cvmk_conv2d_tc_supported(&d), (long long)cvmk_conv2d_tc_workspace_bytes(&d));
+    return 0;
+  }
+  if (argc >= 9 && strcmp(argv[1], "grouped") == 0) {
+    cvmk_conv_desc d;
+    memset(&d, 0, sizeof(d));
+    d.y_dtype = CVMK_I8;
+    d.N = arg(argv, 2); d.H = arg(argv, 3); d.W = arg(argv, 4); d.C = d.OC = arg(argv, 5);
+    d.groups = arg(argv, 6);
+    d.KH = d.KW = arg(argv, 7);
+    d.stride_h = d.stride_w = arg(argv, 8); d.dil_h = d.dil_w = 1;
+    d.pad_h = d.pad_w = d.KH / 2;
+    d.OH = (d.H + 2 * d.pad_h - d.KH) / d.stride_h + 1;
+    d.OW = (d.W + 2 * d.pad_w - d.KW) / d.stride_w + 1;
+    printf("@supported=%d\n", cvmk_conv2d_tc_supported(&d));
     return 0;
   }
   if (argc >= 12 && strcmp(argv[1], "stem") == 0) {

@@ -108,3 +108,14 @@ def test_stem_refuses_what_it_cannot_run(host_fns, tmp_path, shape):
     f = host_fns("stem", *shape, tmp_path / "none.bin")
     assert f["supported"] == "0" and int(f["weight_bytes"]) < 0 and f["pack"] == "-1"
     assert not (tmp_path / "none.bin").exists()
+
+
+@pytest.mark.parametrize("shape,ok", [((256, 56, 56, 128, 4, 3, 1), "1"),    # MobileNet: 128 channels as 4 groups of 32
+                                      ((256, 14, 14, 512, 16, 3, 1), "1"),
+                                      ((1, 16, 16, 1024, 32, 3, 1), "1"),
+                                      ((256, 56, 56, 128, 2, 3, 1), "0"),    # groups of 64 channels
+                                      ((256, 56, 56, 128, 4, 3, 2), "0"),    # stride 2
+                                      ((256, 56, 56, 128, 4, 5, 1), "0"),    # 5 x 5
+                                      ((256, 7, 7, 1024, 32, 3, 1), "0")])   # a 7 x 7 image wastes most of an 8 x 16 tile
+def test_grouped_convolutions_the_tensor_core_kernel_takes(host_fns, shape, ok):
+    assert host_fns("grouped", *shape)["supported"] == ok
