@@ -159,6 +159,13 @@ def op_cases():
     add("depthwise_3x3_128ch_28x28", lambda: conv_case(52, 2, 128, 28, 28, 128, 3, 1, 1, groups=128, shift=6, relu=True))
     add("depthwise_3x3_384ch", lambda: conv_case(53, 1, 384, 16, 24, 384, 3, 1, 1, groups=384, shift=6))
     add("conv_tc_3x3_32ch_patches", lambda: conv_case(51, 2, 32, 16, 24, 64, 3, 1, 1, shift=9, relu=True))
+    # narrow 1x1 layers, which the executor runs with 4 or 2 neighbouring pixels folded into the
+    # channels (block-diagonal weights): 32 -> 64 (fold 4), 64 -> 64 with int32 output and a pixel
+    # count that only 2 divides, 25 pixels (no fold), 64 -> 128 without bias (fold 2)
+    add("conv_1x1_fold4", lambda: conv_case(54, 2, 32, 12, 10, 64, 1, 1, 0, shift=7, relu=True))
+    add("conv_1x1_fold2_int32", lambda: conv_case(55, 1, 64, 9, 6, 64, 1, 1, 0, shift=0))
+    add("conv_1x1_odd_pixels", lambda: conv_case(56, 1, 32, 5, 5, 32, 1, 1, 0, shift=6))
+    add("conv_1x1_fold2_nobias", lambda: conv_case(57, 2, 64, 8, 8, 128, 1, 1, 0, bias=False, shift=7))
     # batch 8: the inference uploads the batch in four chunks and runs the stem per chunk
     add("conv_stem_fused_b8_chunked", lambda: conv_case(38, 8, 3, 20, 16, 32, 3, 2, 1, shift=7, relu=True))
     def stem_generic():
