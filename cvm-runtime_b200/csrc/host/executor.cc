@@ -591,6 +591,26 @@ struct Lowering {
       dw_tc = tiles * 20 <= linear * 27 && cvmk_conv2d_tc_supported(&probe);
       if (!dw_tc) probe.groups = 0;
     }
+    // 32 and 64 channels: 4 or 2 neighbouring pixels of a row are 128 contiguous bytes, so the layer
+    // is given to the same kernel as a 128-channel one over a quarter / half of the width, whose
+    // filter moves in steps of one real pixel (cvmk_conv_desc.group_fold).
+    int dw_fold = 1;
+    if (depthwise && !dw_tc && (C == 32 || C == 64) && KH == 3 && KW == 3 && sh == 1 && sw == 1 && dh == 1 && dw == 1 &&
+        pw == 1 && OW == W && W % (128 / C) == 0 && out.dtype == CVMK_I8 &&
+        (!use_bias || g.params.count(g.entry_id(n.inputs[2])) > 0) && !dev_env("CVM_B200_NO_DW_TC") &&
+        !dev_env("CVM_B200_NO_DW_FOLD") && !dev_env("CVM_B200_NO_TC")) {
+      const int F = 128 / C;
+      const int64_t linear = ((int64_t)N * OH * (OW / F) + 127) / 128;
+      const int64_t tiles = (int64_t)((OW / F + 7) / 8) * ((OH + 15) / 16) * N;
+      cvmk_conv_desc fp = probe;
+      fp.W = W / F; fp.OW = OW / F; fp.C = fp.OC = 128;
+      fp.groups = 4; fp.group_fold = F;
+      if (tiles * 20 <= linear * 27 && cvmk_conv2d_tc_supported(&fp)) {
+        probe = fp;
+        dw_tc = true;
+        dw_fold = F;
+      }
+    }
     const bool tc = (dw_tc || groups == 1) && cvmk_conv2d_tc_supported(&probe) && !dev_env("CVM_B200_NO_TC");
     const int wcg = dw_tc ? dw_cg : icg;   // input channels per weight row as the kernels take them
     // Few-channel convolutions (image stems): gather patches into a [M, Kp] matrix, then run the
@@ -620,11 +640,13 @@ struct Lowering {
       tc_pad = cvmk_conv2d_tc_supported(&pp) && plain_chain && bias_param && safe8[ex_] && out.shape.size() == 4;
     }
     // weights: OIHW int32 -> int8, [OC, KH, KW, C/groups] (depthwise: [KH, KW, C])
-    std::vector<int8_t> w8((size_t)(tc_pad ? OCp : OC) * KH * KW * wcg, 0);
+    std::vector<int8_t> w8((size_t)(tc_pad ? OCp : OC) * dw_fold * KH * KW * wcg, 0);
     if (dw_tc) {   // [OC, KH, KW, 32]: row o holds its filter in column o % 32 of every tap
-      for (int o = 0; o < OC; ++o)
+      for (int o = 0; o < OC * dw_fold; ++o) {   // (folded: the C filters once per sub-pixel)
+        const int c = o % OC;
         for (int k = 0; k < KH * KW; ++k)
-          w8[((size_t)o * KH * KW + k) * wcg + (o % wcg)] = (int8_t)wt.data[(size_t)o * KH * KW + k];
+          w8[((size_t)o * KH * KW + k) * wcg + (c % wcg)] = (int8_t)wt.data[(size_t)c * KH * KW + k];
+      }
     } else if (depthwise && !tc) {
       for (int c = 0; c < C; ++c)
         for (int k = 0; k < KH * KW; ++k) w8[(size_t)k * C + c] = (int8_t)wt.data[(size_t)c * KH * KW + k];
@@ -765,6 +787,15 @@ struct Lowering {
       // block-diagonal weights [f * OC, f * C] -> [M / f, f * OC], byte for byte the same output:
       // f times the multiplies (zeros), 1 / f of the tiles.  32 -> 64 channels at 112 x 112, batch
       // 256: 0.116 -> 0.058 ms with f = 4; 64 -> 64 at 56 x 56: 0.032 -> 0.022 ms with f = 2.
+      if (dw_fold > 1 && use_bias) {   // the bias once per sub-pixel
+        const auto& bv = g.params.find(g.entry_id(n.inputs[2]))->second.data;
+        std::vector<int32_t> bf(128, 0);
+        for (int j = 0; j < dw_fold; ++j)
+          for (int o = 0; o < OC; ++o) bf[(size_t)j * OC + o] = bv[o];
+        int32_t* bfdev = (int32_t*)ex.dalloc(bf.size() * 4);
+        CUDA_OK(cudaMemcpy(bfdev, bf.data(), bf.size() * 4, cudaMemcpyHostToDevice));
+        d.ep.s[0].ptr = bfdev;
+      }
       int fold = 1;
       const int bchunks = batch_chunks(N);
       if (!dense && !dw_tc && groups == 1 && KH == 1 && KW == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 &&

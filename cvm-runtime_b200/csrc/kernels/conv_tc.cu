@@ -85,6 +85,8 @@ struct ConvParams {
   int grouped;          // grouped convolution (a_mode 4): `c` is the channels of ONE group, an N tile is block_n / c
                         // groups and block_k = block_n; group j of N tile n0 reads input channels n0 + j * c .. and
                         // fills accumulator columns j * c ..; the grid is a multiple of the N tiles
+  int group_fold;       // grouped: 1, or F = 2 / 4: a pixel is F sub-pixels of block_n / F channels and the filter
+                        // moves in sub-pixel steps (see cvmk_conv_desc.group_fold)
   int patch_w, patch_h, patch_n;  // a_mode 2, 3: an M tile is patch_w x patch_h output pixels of patch_n images
   int tiles_w, tiles_h;           // a_mode 2, 3: patches per image row / column
   int patch_w_log2, patch_h_log2; // patch sides are powers of two
@@ -607,6 +609,28 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t a_q = (uint32_t)a_bytes >> 4, b_q = (uint32_t)b_bytes >> 4;
       const uint32_t halo_pad_q = (uint32_t)halo_pad >> 4, halo_row_q = (uint32_t)(halo_w * p.block_k) >> 4;
       const uint32_t pix_q = (uint32_t)p.block_k >> 4;   // grouped: one pixel of the halo row
+      // grouped: where filter column t of group g starts inside a halo row (16-byte units).  Without
+      // folding that is halo pixel t, the group's own 32 channels.  With F sub-pixels per pixel the
+      // group of sub-pixel a reads sub-pixel a + t - 1: the same halo pixel (1) for most, the last
+      // sub-pixel of pixel 0 / the first of pixel 2 at the ends.
+      uint32_t g_off[4][3];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int fold = p.group_fold > 1 ? p.group_fold : 1;
+        const int cs = p.block_n / fold;          // channels per sub-pixel
+        const int gps = cs >> 5;                  // 32-channel groups per sub-pixel
+        const int a = p.group_fold > 1 ? g / gps : 0, h = p.group_fold > 1 ? g - a * gps : g;
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+          int px = t, b = 0;
+          if (p.group_fold > 1) {
+            const int bp = a + t - 1;
+            px = bp < 0 ? 0 : (bp >= fold ? 2 : 1);
+            b = bp - (px - 1) * fold;
+          }
+          g_off[g][t] = (uint32_t)px * pix_q + (uint32_t)((b * cs + h * 32) >> 4);
+        }
+      }
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -661,18 +685,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               // every group of the N tile: its own columns of the halo rows, its own 9 weight tiles,
               // its own accumulator columns (the first tap overwrites them)
               uint32_t bl = w_lo0;
-              uint32_t d_blk = d_tmem, a_g = st;
-              for (int g = 0; g < gpt; ++g, d_blk += 32u, a_g += 2u) {   // 32 columns, 32 bytes of the halo rows
+              uint32_t d_blk = d_tmem;
 #pragma unroll
-                for (int fy = 0; fy < 3; ++fy) {
-                  uint32_t al = a_g + (uint32_t)fy * halo_row_q;
+              for (int g = 0; g < 4; ++g) {   // 32 accumulator columns each
+                if (g < gpt) {
 #pragma unroll
-                  for (int fx = 0; fx < 3; ++fx) {
-                    if (leader) mma_i8_k<1>(d_blk, al, halo_hi, bl, w_hi, idesc, (uint32_t)(fy | fx));
-                    al += pix_q;
-                    bl += b_q;
+                  for (int fy = 0; fy < 3; ++fy) {
+                    const uint32_t al = st + (uint32_t)fy * halo_row_q;
+#pragma unroll
+                    for (int fx = 0; fx < 3; ++fx) {
+                      if (leader) mma_i8_k<1>(d_blk, al + g_off[g][fx], halo_hi, bl, w_hi, idesc, (uint32_t)(fy | fx));
+                      bl += b_q;
+                    }
+                    if (fy == 0 && g == 0) flush();
                   }
-                  if (fy == 0 && g == 0) flush();
+                  d_blk += 32u;
                 }
               }
             } else {
@@ -1070,6 +1097,11 @@ bool grouped_supported(const cvmk_conv_desc& d) {
   const int cg = d.C / d.groups;
   if (cg != d.OC / d.groups || cg != 32) return false;
   if (d.KH != 3 || d.KW != 3 || d.stride_h != 1 || d.stride_w != 1 || d.dil_h != 1 || d.dil_w != 1) return false;
+  if (d.group_fold > 1) {   // folded pixels: one N tile holds all sub-pixels; the real padding is one sub-pixel
+    if ((d.group_fold != 2 && d.group_fold != 4) || d.C != 128 || d.pad_w != 1) return false;
+    if (d.OH != d.H + 2 * d.pad_h - 2 || d.OW != d.W) return false;
+    return halo_tiles_fit(d);
+  }
   if (d.OH != d.H + 2 * d.pad_h - 2 || d.OW != d.W + 2 * d.pad_w - 2) return false;
   return halo_tiles_fit(d);
 }
@@ -1393,7 +1425,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
     p.num_m_tiles = p.tiles_w * p.tiles_h * ((d.N + p.patch_n - 1) / p.patch_n);
   }
   p.num_n_tiles = (d.OC + plan->block_n - 1) / plan->block_n;
-  if (d.groups > 1) { p.grouped = 1; p.c = d.C / d.groups; }
+  if (d.groups > 1) { p.grouped = 1; p.c = d.C / d.groups; p.group_fold = d.group_fold > 1 ? d.group_fold : 1; }
   p.num_units = p.grouped ? d.KH * d.KW : d.KH * d.KW * (p.c / plan->block_k);
   p.num_kb = p.a_mode >= 3 ? (p.grouped ? 1 : p.c / plan->block_k) : (p.num_units + p.units - 1) / p.units;
   p.fd_n_tiles = make_fastdiv(p.num_n_tiles);

@@ -131,6 +131,14 @@ typedef struct {
    * than the CUDA-core form for 128 channels and more, which is bound by instruction issue.
    * cvmk_conv2d_tc_supported() says whether the 8 x 16 pixel tiles fit the image. */
   int32_t groups;
+  /* Grouped mode only, 0 or 1 = off.  F = 2 or 4: x and y are views of tensors F times as wide with
+   * C / F channels: a pixel here is F neighbouring pixels ("sub-pixels") of the real image side by
+   * side, and the 3 x 3 filter of an output channel moves in sub-pixel steps (C = OC = 128,
+   * pad_w = 1 real pixel; W and OW count folded pixels).  That is how a depthwise layer over 32 or
+   * 64 channels fills 128-column tiles: the group of sub-pixel a reads the 32-channel groups of
+   * sub-pixels a - 1, a, a + 1, the outer ones from the neighbouring folded pixel at the edges. */
+  int32_t group_fold;
+  int32_t reserved1;
   /* Optional scratch for reductions cut along K (dense layers of a few rows over a long K, whose
    * few output tiles would leave most SMs idle): cvmk_conv2d_tc_workspace_bytes() says how much the
    * shape wants (0: it is not cut).  With at least that much here, K slices run as separate tiles
