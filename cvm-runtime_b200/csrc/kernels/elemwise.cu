@@ -692,6 +692,74 @@ extern "C" int cvmk_reduce(const cvmk_reduce_desc* d, cvmk_stream_t stream) {
   return check_cuda(cudaGetLastError(), "reduce_kernel launch");
 }
 
+// int8 max pooling with a 3 x 3 or 2 x 2 window whose every position holds at least one pixel of
+// the image in each direction (padding smaller than the window, the usual case).  Taps outside
+// the image are then read from the nearest pixel inside it, which lies in the same window, so
+// the maximum does not change and no tap needs a select.  The signed bytes of a 16-byte channel
+// vector are compared as s16x2 (even and odd bytes moved into the high byte of each half), three
+// values per instruction: a row of taps is one __vimax3_s16x2, the rows another.
+template <int K, bool IDX32>
+__global__ void __launch_bounds__(256) pool_window_kernel(const __grid_constant__ PoolParams p) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+    int cv, ox, oy, n;
+    if (IDX32) {
+      const uint32_t u = (uint32_t)i;
+      const uint32_t pix = idx_div(u, p.d_cvec);
+      cv = (int)(u - pix * (uint32_t)p.cvec);
+      const uint32_t r1 = idx_div(pix, p.d_ow);
+      ox = (int)(pix - r1 * (uint32_t)p.OW);
+      const uint32_t r2 = idx_div(r1, p.d_oh);
+      oy = (int)(r1 - r2 * (uint32_t)p.OH);
+      n = (int)r2;
+    } else {
+      cv = (int)(i % p.cvec);
+      int64_t pix = i / p.cvec;
+      ox = (int)(pix % p.OW); pix /= p.OW;
+      oy = (int)(pix % p.OH);
+      n = (int)(pix / p.OH);
+    }
+    int xo[K];   // vector offsets of the window's columns inside a row
+#pragma unroll
+    for (int fx = 0; fx < K; ++fx) xo[fx] = min(max(ox * p.sw + fx - p.pw, 0), p.W - 1) * p.cvec;
+    uint32_t re[K][4], ro[K][4];
+#pragma unroll
+    for (int fy = 0; fy < K; ++fy) {
+      const int iy = min(max(oy * p.sh + fy - p.ph, 0), p.H - 1);
+      const int4* row = reinterpret_cast<const int4*>(p.x) + ((int64_t)n * p.H + iy) * p.W * p.cvec + cv;
+      uint32_t te[K][4], to[K][4];
+#pragma unroll
+      for (int fx = 0; fx < K; ++fx) {
+        const int4 v = __ldg(row + xo[fx]);
+        const uint32_t w[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {   // (0, b0, 0, b2) and (0, b1, 0, b3)
+          te[fx][q] = __byte_perm(w[q], 0u, 0x2404);
+          to[fx][q] = __byte_perm(w[q], 0u, 0x3414);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (K == 3) {
+          re[fy][q] = __vimax3_s16x2(te[0][q], te[1][q], te[2][q]);
+          ro[fy][q] = __vimax3_s16x2(to[0][q], to[1][q], to[2][q]);
+        } else {
+          re[fy][q] = __vmaxs2(te[0][q], te[1][q]);
+          ro[fy][q] = __vmaxs2(to[0][q], to[1][q]);
+        }
+      }
+    }
+    uint32_t r[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t me = K == 3 ? __vimax3_s16x2(re[0][q], re[1][q], re[2][q]) : __vmaxs2(re[0][q], re[1][q]);
+      const uint32_t mo = K == 3 ? __vimax3_s16x2(ro[0][q], ro[1][q], ro[2][q]) : __vmaxs2(ro[0][q], ro[1][q]);
+      r[q] = __byte_perm(me, mo, 0x7351);   // (me.b1, mo.b1, me.b3, mo.b3)
+    }
+    reinterpret_cast<int4*>(p.y)[i] = make_int4((int)r[0], (int)r[1], (int)r[2], (int)r[3]);
+  }
+}
+
 extern "C" int cvmk_max_pool2d(const cvmk_pool_desc* d, cvmk_stream_t stream) {
   if (!d || !d->x || !d->y || (d->dtype != CVMK_I8 && d->dtype != CVMK_I32)) {
     set_error("max_pool2d: bad argument");
@@ -709,7 +777,21 @@ extern "C" int cvmk_max_pool2d(const cvmk_pool_desc* d, cvmk_stream_t stream) {
     p.total = (int64_t)d->N * d->OH * d->OW * p.cvec;
     p.d_cvec = make_idx_div(p.cvec); p.d_ow = make_idx_div(d->OW); p.d_oh = make_idx_div(d->OH);
     const bool idx32 = p.total < ((int64_t)1 << 31);
-    if (d->dtype == CVMK_I8) {
+    // every window position holds a pixel of the image in both directions
+    const bool inside = d->pad_h < d->KH && d->pad_w < d->KW && (d->OH - 1) * d->stride_h - d->pad_h <= d->H - 1 &&
+                        (d->OW - 1) * d->stride_w - d->pad_w <= d->W - 1;
+    const bool window = d->dtype == CVMK_I8 && d->KH == d->KW && (d->KH == 3 || d->KH == 2) && inside &&
+                        !dev_env("CVM_B200_NO_POOL_WINDOW");
+    if (window) {
+      const int grid = grid_for(p.total, threads);
+      if (d->KH == 3) {
+        if (idx32) pool_window_kernel<3, true><<<grid, threads, 0, s>>>(p);
+        else pool_window_kernel<3, false><<<grid, threads, 0, s>>>(p);
+      } else {
+        if (idx32) pool_window_kernel<2, true><<<grid, threads, 0, s>>>(p);
+        else pool_window_kernel<2, false><<<grid, threads, 0, s>>>(p);
+      }
+    } else if (d->dtype == CVMK_I8) {
       if (idx32) pool_vec_kernel<CVMK_I8, true><<<grid_for(p.total, threads), threads, 0, s>>>(p);
       else pool_vec_kernel<CVMK_I8, false><<<grid_for(p.total, threads), threads, 0, s>>>(p);
     } else {

@@ -328,6 +328,12 @@ def op_cases():
     add("max_pool_2x2", pool(41, (1, 5, 8, 6), 2, 2, 0))
     add("max_pool_ceil", pool(42, (1, 16, 10, 10), 3, 2, 0, ceil=True))
     add("max_pool_int32", pool(43, (1, 4, 9, 9), 3, 1, 1, prec=20, pad1=True))
+    # channel-vector forms: 2x2 stride 2, 3x3 stride 1 with padding, 3x3 stride 2 over odd sizes,
+    # 2x2 in ceil mode (the last window reaches past the image)
+    add("max_pool_2x2_vec", pool(44, (2, 32, 12, 10), 2, 2, 0))
+    add("max_pool_3x3_s1_vec", pool(45, (1, 32, 7, 9), 3, 1, 1))
+    add("max_pool_3x3_s2_odd_vec", pool(46, (2, 64, 13, 15), 3, 2, 1))
+    add("max_pool_2x2_ceil_vec", pool(47, (1, 16, 9, 7), 2, 2, 0, ceil=True))
 
     add("upsampling", lambda: single_op("upsampling", rnd(np.random.RandomState(50), (2, 16, 4, 5), 8), 8,
                                         {"scale": 2}, [[2, 16, 8, 10]]))
