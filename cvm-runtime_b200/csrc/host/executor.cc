@@ -264,6 +264,35 @@ struct Lowering {
       buf[e].dtype = safe8[e] ? CVMK_I8 : CVMK_I32;
       buf[e].nhwc = wants_nhwc(g.shape[e]);
     }
+    // transpose(0, 2, 3, 1) of a tensor stored channels-last: the row-major bytes of the result ARE
+    // the input's bytes.  The result is therefore kept row-major (not channels-last again, which
+    // would shuffle it once here and once more at the reshape that usually follows: the detection
+    // heads of SSD do this twelve times per step) and the node becomes an alias.
+    for (uint32_t nid = 0; nid < g.nodes.size(); ++nid)
+      if (transpose_is_identity(nid)) buf[g.entry_id(nid, 0)].nhwc = false;
+  }
+
+  // true for transpose nodes with axes (0, 2, 3, 1) over a 4-D input that is stored channels-last
+  bool transpose_is_identity(uint32_t nid) {
+    const Node& n = g.nodes[nid];
+    if (n.is_variable() || n.op->name != "transpose" || n.inputs.size() != 1) return false;
+    const uint32_t ei = g.entry_id(n.inputs[0]);
+    if (g.shape[ei].size() != 4 || !buf[ei].nhwc || g.params.count(ei)) return false;
+    const Shape axes = n.attrs.t("axes");
+    if (!(axes.size() == 4 && axes[0] == 0 && axes[1] == 2 && axes[2] == 3 && axes[3] == 1)) return false;
+    // only when every reader takes the tensor by its layout flag: the reshape-like operators (and
+    // the output copy of a graph head); convolutions and pooling expect channels-last operands
+    const uint32_t eo = g.entry_id(nid, 0);
+    for (uint32_t m = nid + 1; m < g.nodes.size(); ++m) {
+      const Node& c = g.nodes[m];
+      if (c.is_variable()) continue;
+      for (const auto& e : c.inputs) {
+        if (g.entry_id(e) != eo) continue;
+        const std::string& op = c.op->name;
+        if (op != "flatten" && op != "reshape" && op != "squeeze" && op != "expand_dims") return false;
+      }
+    }
+    return true;
   }
 
   // ------------------------------------------------------------------ buffers
@@ -1213,6 +1242,15 @@ struct Lowering {
     const Node& n = g.nodes[nid];
     const std::string& op = n.op->name;
     const DevBuf x = materialize(g.entry_id(n.inputs[0]));
+    if (transpose_is_identity(nid) && !dev_env("CVM_B200_NO_TRANSPOSE_ALIAS")) {
+      DevBuf& out = buf[g.entry_id(nid, 0)];
+      bool written = false;   // an entry that non_max_suppression overwrites in place keeps its own memory
+      for (const auto& wv : input_writers) written |= wv.second == g.entry_id(nid, 0) || wv.second == g.entry_id(n.inputs[0]);
+      if (!out.ptr && !out.nhwc && out.dtype == x.dtype && !written) {
+        out.ptr = x.ptr;  // alias
+        return;
+      }
+    }
     const DevBuf y = materialize(g.entry_id(nid, 0));
     const Shape &xsh = x.shape, &ysh = y.shape;
     const auto xs = phys_strides(xsh, x.nhwc), ys = phys_strides(ysh, y.nhwc);

@@ -179,6 +179,26 @@ def op_cases():
         js, pb = g.finish(y)
         return js, pb, x
     add("conv_stem_fused_generic_chain", stem_generic)
+    def head_transpose(pool_after):
+        # conv -> transpose(0, 2, 3, 1) -> reshape, as detection heads do (the transpose of a
+        # channels-last buffer is an alias), and the same transpose read by max_pool2d (a real copy)
+        def f():
+            rng = np.random.RandomState(58)
+            g = wl.GraphBuilder(58)
+            x = rnd(rng, (2, 32, 6, 10), 8)
+            d = g.var("data", x.shape, 8)
+            y = g.conv(d, 48, 3, 1, 1, relu=False, shift=8)
+            t = g.op("transpose", [y], (2, 6, 10, 48), {"axes": (0, 2, 3, 1)})
+            if pool_after:
+                t = g.op("max_pool2d", [t], (2, 6, 5, 24), {"pool_size": (2, 2), "strides": (2, 2), "padding": (0, 0), "ceil_mode": False})
+                r = g.op("reshape", [t], (2, 720), {"shape": (2, 720)})
+            else:
+                r = g.op("reshape", [t], (2, 60, 48), {"shape": (2, 60, 48)})
+            js, pb = g.finish(r)
+            return js, pb, x
+        return f
+    add("head_transpose_reshape", head_transpose(False))
+    add("head_transpose_pool", head_transpose(True))
     add("conv_odd_channels", lambda: conv_case(7, 1, 5, 8, 8, 7, 3, 1, 1, shift=7))
     add("conv_depthwise", lambda: conv_case(8, 2, 32, 10, 10, 32, 3, 1, 1, groups=32, shift=6, relu=True))
     add("conv_depthwise_s2", lambda: conv_case(9, 1, 48, 9, 9, 48, 3, 2, 1, groups=48, shift=6))
