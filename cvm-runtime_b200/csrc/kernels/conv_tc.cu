@@ -94,6 +94,9 @@ struct ConvParams {
   int num_units, num_kb;          // (tap, channel block) pairs per tile; ring stages consumed per tile
   FastDiv fd_n_tiles, fd_tiles_w, fd_tiles_h, fd_ohow, fd_ow;
   int tmem_cols;
+  int two_issuers;      // halo modes: one producer warp is enough (a load or ten per tile), the other warp issues the
+                        // tensor-core instructions of every second tile, so that one warp's barrier checks and
+                        // commits run while the other's instructions keep the pipe busy
   int acc_bufs;         // accumulators in TMEM: 2, or 4 when block_n <= 128 (the MMA warp may then run three tiles ahead
                         // of the epilogue groups, each of which drains its tiles into accumulators g and g + 2 in turn)
   int* status;
@@ -388,12 +391,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // loads, whose latency then runs while the other ten warps allocate TMEM and stage the bias.
   // Warp 0 also ARRIVES (without waiting) at the barrier the other ten warps wait at, so that none
   // of them touches an mbarrier or the abort flag before thread 0 has initialised them.
-  const bool is_producer = warp == 0 || warp == PRODUCER2_WARP;
+  const bool two_issuers = p.two_issuers != 0;
+  const bool is_producer = warp == 0 || (warp == PRODUCER2_WARP && !two_issuers);
+  const int setup_threads = two_issuers ? NUM_THREADS : NUM_THREADS - 32;   // the waiting warps plus warp 0's arrival
   if (warp == 0) {
     __threadfence_block();
-    asm volatile("bar.arrive 1, %0;" ::"n"(NUM_THREADS - 32) : "memory");
+    asm volatile("bar.arrive 1, %0;" ::"r"(setup_threads) : "memory");
   }
-  if (is_producer) asm volatile("bar.sync 2, 64;" ::: "memory");
+  if (is_producer && !two_issuers) asm volatile("bar.sync 2, 64;" ::: "memory");
   auto stage_bias = [&]() {
     const int padded = min(MAX_BIAS, (p.oc + 31) & ~31);
     for (int i = (int)threadIdx.x - 32; i < padded; i += NUM_THREADS - 64) {   // warps 1..10
@@ -412,13 +417,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // Every role below finishes its own set-up arithmetic first and executes griddepcontrol.wait just
     // before its loop, so that the set-up overlaps the tail of the previous kernel.
     tc_fence_before();
-    asm volatile("bar.sync 1, %0;" ::"n"(NUM_THREADS - 32) : "memory");   // ten warps wait, warp 0 has arrived
+    asm volatile("bar.sync 1, %0;" ::"r"(setup_threads) : "memory");   // ten or eleven warps wait, warp 0 has arrived
     tc_fence_after();
     tmem_base = tmem_slot;
   }
   if (threadIdx.x == 0) TRACE(16, 2);
 
-  if (warp == 0 || warp == PRODUCER2_WARP) {
+  if (is_producer) {
     // ------------------------------------------------------------------ TMA producers
     // Producer `which` issues the K blocks whose running number (over all tiles of this CTA) is
     // congruent to it modulo 2; both walk the same sequence of ring slots.
@@ -485,7 +490,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (halo) {
           for (int cb = 0; cb < num_kb; ++cb) {
-            const bool my_stage = turn == 0;
+            const bool my_stage = two_issuers || turn == 0;   // (a single producer takes every stage)
             turn ^= 1;
             if (!my_stage) continue;
             TSTART(tw);
@@ -516,7 +521,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             if (leader) TRACE(which * 2 + 1, pseq);
             ++pseq;
-            stage += 2;
+            stage += two_issuers ? 1 : 2;
             if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
           }
           continue;
@@ -590,9 +595,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (which == 0 && leader) { TFLUSH(0); TFLUSH(12); }
 #endif
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == PRODUCER2_WARP) {
+    // ------------------------------------------------------------------ MMA issuer(s)
+    // One warp, or two that take the tiles of this CTA in turn (two_issuers): tiles are independent
+    // of each other (own ring stages, own accumulator), so the two warps need no ordering between
+    // them; each derives the stage and the accumulator of its tiles from the tile's running number.
     {
+      const int issuers = two_issuers ? 2 : 1;
+      const int me = warp == 1 ? 0 : 1;
       const bool leader = elect_one();
       const uint32_t idesc = umma_idesc_i8(p.grouped ? p.c : p.block_n);
       const uint64_t desc_a0 = umma_desc(smem_u32(ring), p.block_k);
@@ -631,10 +641,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           g_off[g][t] = (uint32_t)px * pix_q + (uint32_t)((b * cs + h * 32) >> 4);
         }
       }
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
+      // this issuer's first tile is the CTA's tile number `me`: me * num_kb stages and me accumulators in
+      int stage = (me * num_kb) % p.stages;
+      uint32_t phase = (uint32_t)((me * num_kb) / p.stages) & 1u;
+      int acc = me % p.acc_bufs;
+      uint32_t acc_phase = (uint32_t)(me / p.acc_bufs) & 1u;
       bool live = true;
       // tcgen05.commit keeps this thread until the instructions queued before it have left the
       // queue, so after a commit the tensor pipe stands idle until the next instruction has been
@@ -664,7 +675,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       TSTART(tl);
       asm volatile("griddepcontrol.wait;" ::: "memory");
       if ((w_resident || b_resident) && blockIdx.x < num_tiles && !mbar_wait(&bar_weights, 0u, &abort_flag, 7)) live = false;
-      for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x + me * (int)gridDim.x; live && tile < num_tiles; tile += issuers * (int)gridDim.x) {
         TSTART(tw);
         if (!ensure(&bar_acc_empty[acc], acc_phase ^ 1, 2)) { live = false; break; }
         TADD(1, tw);
@@ -751,7 +762,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (!live) break;
         owed_acc = acc;
         if (!halo) flush();
-        if (++acc == p.acc_bufs) { acc = 0; acc_phase ^= 1; }
+        // on to this issuer's next tile: past the other issuer's stages and accumulator
+        for (int k = 0; k < issuers; ++k)
+          if (++acc == p.acc_bufs) { acc = 0; acc_phase ^= 1; }
+        for (int k = 0; k < (issuers - 1) * num_kb; ++k)
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
       if (live) flush();
       TADD(3, tl);
@@ -1434,6 +1449,7 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.fd_ohow = make_fastdiv(d.OH * d.OW);
   p.fd_ow = make_fastdiv(d.OW);
   p.acc_bufs = (plan->block_n <= 128 && !dev_env("CVM_B200_TWO_ACCUMULATORS")) ? 4 : 2;
+  p.two_issuers = (p.a_mode >= 3 && !dev_env("CVM_B200_ONE_ISSUER")) ? 1 : 0;
   int cols = p.acc_bufs * plan->block_n;
   int pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
