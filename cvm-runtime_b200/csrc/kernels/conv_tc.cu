@@ -532,7 +532,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint32_t sa = 0, bar = 0;
         for (int unit = 0; unit < num_units; ++unit) {
           if (slot == 0) {
-            mine = turn == 0;
+            mine = two_issuers || turn == 0;
             turn ^= 1;
             if (mine) {
               if (which == 0 && pseq == 0 && leader) TRACE(16, 8);
@@ -584,7 +584,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (mine) {
               if (leader) TRACE(which * 2 + 1, pseq);
               ++pseq;
-              stage += 2;
+              stage += two_issuers ? 1 : 2;
               if (stage >= p.stages) { stage -= p.stages; phase ^= 1; }
             }
           }
@@ -1449,7 +1449,6 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
   p.fd_ohow = make_fastdiv(d.OH * d.OW);
   p.fd_ow = make_fastdiv(d.OW);
   p.acc_bufs = (plan->block_n <= 128 && !dev_env("CVM_B200_TWO_ACCUMULATORS")) ? 4 : 2;
-  p.two_issuers = (p.a_mode >= 3 && !dev_env("CVM_B200_ONE_ISSUER")) ? 1 : 0;
   int cols = p.acc_bufs * plan->block_n;
   int pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
@@ -1472,6 +1471,14 @@ extern "C" int cvmk_conv2d_tc_launch(const cvmk_conv_plan* plan, cvmk_stream_t s
     p.num_kb = (p.num_units + p.units - 1) / p.units;
     p.fd_n_tiles = make_fastdiv(p.num_n_tiles);
   }
+  // Two issuing warps (and one producer) in the halo modes, where a tile takes one or two ring
+  // stages and the ring has more: an issuer that waits for the first stage of its next tile is then
+  // never more than one lap of that stage's barrier ahead of the producer, which is what a parity
+  // wait can tell apart.  (The same rule applied to the short 1x1 reductions of the other modes
+  // passed every single-kernel check and gained 12 % on 64 -> 64 and 256 -> 64 layers, but a
+  // bounded wait ran out in ResNet-50's end-to-end loop, where per-chunk kernels follow each other
+  // closely; it stays off until that is understood.)
+  p.two_issuers = (p.a_mode >= 3 && p.num_kb < p.stages && !dev_env("CVM_B200_ONE_ISSUER")) ? 1 : 0;
 #ifdef CVMK_CONV_TIMING
   p.dbg = getenv("CVM_DBG") ? atoi(getenv("CVM_DBG")) : 0;
   if (getenv("CVM_HINT")) {
