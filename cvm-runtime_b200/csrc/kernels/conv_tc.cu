@@ -1,4 +1,5 @@
-// conv2d (groups = 1) and dense as an implicit GEMM on the sm_100a tensor cores.
+// conv2d (groups = 1) and dense as an implicit GEMM on the sm_100a tensor cores; grouped 3 x 3
+// convolutions with 32 channels per group as well (how depthwise layers are given to it).
 //
 //   D[pixel, oc] = sum_{kh,kw,c} X[n, oh*s-p+kh*d, ow*s-p+kw*d, c] * Wt[oc, kh, kw, c]
 //
@@ -8,8 +9,12 @@
 // is a 1x1 / dense) and of weights into a swizzled shared-memory ring; one thread issues
 // tcgen05.mma kind::i8 (int8 x int8 -> int32) into a TMEM accumulator; four warps drain the
 // accumulator with tcgen05.ld, run the fused element chain (bias, relu, round-shift, clip,
-// residual add ...) and store int8 / int32 NHWC.  Two accumulators alternate so the drain of tile
-// i overlaps the MMAs of tile i+1.  The int32 sum never reaches HBM.
+// residual add ...) and store int8 / int32 NHWC.  Two accumulators alternate (four, when a tile is
+// at most 128 columns wide) so the drain of tile i overlaps the MMAs of the tiles after it.  The
+// int32 sum never reaches HBM.  Stride-1 3 x 3 filters over at most 128 channels (and every
+// grouped layer) stage the input halo of a spatial patch once and let every filter tap multiply a
+// window of it; in those modes the second producer warp issues the instructions of every second
+// tile instead of loading.
 //
 // int8 outputs leave through shared memory: eight epilogue warps write their packed results into
 // a swizzled staging panel (128 rows x up to 128 bytes) that one thread hands to a TMA store, and
@@ -42,7 +47,7 @@ constexpr int NUM_EPI_WARPS = 8;
 // warp 0: TMA loads of the operands, warp 1: MMA + TMEM owner, warps 2..9: epilogue,
 // warp 10: TMA traffic of the staged output tiles (stores, residual-operand loads)
 // warp 11: second TMA producer (issuing a load costs its thread about a hundred cycles, so two
-// threads take alternate K blocks)
+// threads take alternate K blocks); in the halo modes, where a tile is one load, second MMA issuer
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS + 64;
 constexpr int IO_WARP = 2 + NUM_EPI_WARPS;
 constexpr int PRODUCER2_WARP = IO_WARP + 1;
